@@ -1,0 +1,631 @@
+// Block-select decode attention: FP16 old K + q4 old V + FP16 recent ring (and the
+// dense-FP16-backed form of the same selection).
+//
+// Reference algorithm (cuda/kernels.cu:2832-3096), per q head:
+//   score_b = (sum_{t in block b} q.K_t / len_b) / sqrt(hd) for every old block,
+//   keep the top_n by score (ties -> lower block index, NaN / <= -1e30 never kept),
+//   softmax-attend the tokens of the kept blocks plus the recent window.
+// Here this is three launches:
+//   1. block scores: one pass over old K per KV head (not per q head), using
+//      sum_t q.K_t = q.(sum_t K_t): the kernel adds K rows (1 add per element) and takes
+//      G dot products per block, so the scoring pass stays HBM-bound;
+//   2. top-k per q head (iterative arg-max over the scores in shared memory);
+//   3. attention over the selected tokens, split over CTAs, q4 V dequantised in registers
+//      (value = f16(nibble * scale), kernels.cu:3085-3086), then the merge kernel.
+#include <stdlib.h>
+#include <string.h>
+
+#include "attention.cuh"
+#include "common.cuh"
+
+namespace {
+
+struct SelArgs {
+    const __half* old_k;     // head-major [slot][kvh][max_seq][hd] (compressed: old region; dense: K)
+    const __half* ring_k;    // compressed: [slot][kvh][R][hd]; dense: null
+    const __half* ring_v;
+    const __half* dense_v;   // dense mode: V; compressed: null
+    const uint8_t* q4_v;     // [slot][kvh][max_seq][hd/2]
+    const float* q4_scale;   // [slot][kvh][max_seq]
+    const float* q;          // [q_heads][hd]
+    float* scores;           // [q_heads][score_stride]
+    uint32_t* sel_blocks;    // [q_heads][64]
+    float* sel_scores;       // [q_heads][64]
+    float* part_m;
+    float* part_l;
+    float* part_o;
+    uint32_t seq_id, max_seq_len, kv_heads, q_heads, hd;
+    uint32_t seq_len, old_len, recent_window, ring_size, block_size, nb, top_n;
+    uint32_t block_begin, block_end;  // blocks this call may read (split-K); [0, nb) otherwise
+    uint32_t score_stride, include_recent, splits;
+    float inv_sqrt;
+};
+
+// ---- 1. block scores. grid (ceil(blocks/4), kv_heads), 128 threads; a warp per block. ----
+template <int HD>
+__global__ void __launch_bounds__(128) block_score_kernel(SelArgs a) {
+    constexpr int LPT = HD / 8;        // lanes per token row (16-byte pieces)
+    constexpr int TPI = 32 / LPT;      // tokens per warp-wide load
+    extern __shared__ float sq[];      // q of this kv head's group: [G][HD]
+    const uint32_t kvh = blockIdx.y;
+    const uint32_t G = a.q_heads / a.kv_heads;
+    for (uint32_t i = threadIdx.x; i < G * HD; i += blockDim.x) sq[i] = a.q[(size_t)kvh * G * HD + i];
+    __syncthreads();
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+    const uint32_t b = a.block_begin + blockIdx.x * 4u + warp;
+    if (b >= a.block_end) return;
+    const uint32_t t0 = b * a.block_size;
+    const uint32_t t1 = min(t0 + a.block_size, a.old_len);
+    const __half* Kh = a.old_k + kv_row_offset(a.seq_id, kvh, 0, a.kv_heads, a.max_seq_len, HD);
+    const uint32_t sub = lane / LPT, piece = lane % LPT;
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.0f;
+#pragma unroll 4
+    for (uint32_t t = t0 + sub; t < t1; t += TPI) {
+        const uint4 w = *reinterpret_cast<const uint4*>(Kh + (size_t)t * HD + piece * 8);
+        const __half2* h = reinterpret_cast<const __half2*>(&w);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float2 f = __half22float2(h[j]);
+            acc[2 * j] += f.x;
+            acc[2 * j + 1] += f.y;
+        }
+    }
+    // fold the token sub-groups together: lanes with equal `piece` hold the same dims
+#pragma unroll
+    for (int o = 16; o >= LPT; o >>= 1)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] += __shfl_xor_sync(0xffffffffu, acc[j], o);
+    const float inv_len = 1.0f / (float)(t1 - t0);
+    for (uint32_t g = 0; g < G; ++g) {
+        float dot = 0.0f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) dot = fmaf(sq[g * HD + piece * 8 + j], acc[j], dot);
+        // reduce over the LPT lanes that hold distinct pieces
+#pragma unroll
+        for (int o = LPT / 2; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+        if (lane == 0) a.scores[(size_t)(kvh * G + g) * a.score_stride + (b - a.block_begin)] = (dot * inv_len) * a.inv_sqrt;
+    }
+}
+
+// ---- 2. top-k. grid q_heads, 128 threads. scores -> sel_blocks/sel_scores (descending). ----
+__global__ void __launch_bounds__(128) topk_blocks_kernel(SelArgs a) {
+    extern __shared__ float sc[];  // nb scores
+    __shared__ float wbest[4];
+    __shared__ uint32_t wbidx[4];
+    const uint32_t h = blockIdx.x;
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+    for (uint32_t i = threadIdx.x; i < a.nb; i += blockDim.x) sc[i] = a.scores[(size_t)h * a.score_stride + i];
+    for (uint32_t i = threadIdx.x; i < 64u; i += blockDim.x) {
+        a.sel_blocks[h * 64u + i] = 0xffffffffu;
+        a.sel_scores[h * 64u + i] = -1e30f;
+    }
+    __syncthreads();
+    for (uint32_t k = 0; k < a.top_n; ++k) {
+        // a candidate must compare greater than -1e30 (the reference's empty-slot score); NaN never does
+        float best = -1e30f;
+        uint32_t bidx = 0xffffffffu;
+        for (uint32_t i = threadIdx.x; i < a.nb; i += blockDim.x) {
+            const float s = sc[i];
+            if (s > best) {  // strided scan keeps the lowest index among equal scores per thread
+                best = s;
+                bidx = i;
+            }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const uint32_t oi = __shfl_xor_sync(0xffffffffu, bidx, o);
+            if (ob > best || (ob == best && oi < bidx)) {
+                best = ob;
+                bidx = oi;
+            }
+        }
+        if (lane == 0) {
+            wbest[warp] = best;
+            wbidx[warp] = bidx;
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            float fb = wbest[0];
+            uint32_t fi = wbidx[0];
+            for (int w = 1; w < 4; ++w)
+                if (wbest[w] > fb || (wbest[w] == fb && wbidx[w] < fi)) {
+                    fb = wbest[w];
+                    fi = wbidx[w];
+                }
+            if (fi != 0xffffffffu) {
+                a.sel_blocks[h * 64u + k] = fi;
+                a.sel_scores[h * 64u + k] = fb;
+                sc[fi] = -INFINITY;  // never compares greater than -1e30 again
+            }
+            wbidx[0] = fi;
+        }
+        __syncthreads();
+        if (wbidx[0] == 0xffffffffu) break;  // nothing selectable is left
+        __syncthreads();
+    }
+}
+
+// ---- 3. attention over the selected tokens. grid (splits, q_heads), 128 threads. ----
+// Slot space: [0, 64*block_size) = selected blocks in list order (empty entries and tokens past
+// old_len are skipped), then the recent tokens [old_len, seq_len). DENSE: K/V from the dense cache.
+template <int HD, bool DENSE>
+__global__ void __launch_bounds__(128) selected_attend_kernel(SelArgs a) {
+    constexpr int DPL = HD / 32;  // dims per lane (4 for 128, 2 for 64), contiguous
+    __shared__ uint32_t sblk[64];
+    __shared__ float sm_m[4], sm_l[4], sm_o[4][HD];
+    const uint32_t split = blockIdx.x, h = blockIdx.y;
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+    const uint32_t G = a.q_heads / a.kv_heads, kvh = h / G;
+    if (threadIdx.x < 64) {
+        uint32_t b = a.sel_blocks[h * 64u + threadIdx.x];
+        if (b != 0xffffffffu && (b < a.block_begin || b >= a.block_end)) b = 0xffffffffu;
+        sblk[threadIdx.x] = b;
+    }
+    __syncthreads();
+    const uint32_t sel_slots = 64u * a.block_size;
+    const uint32_t recent_n = a.include_recent ? a.seq_len - a.old_len : 0u;
+    const uint32_t total = sel_slots + recent_n;
+    uint32_t per = (total + a.splits - 1) / a.splits;
+    per = (per + 3u) & ~3u;
+    const uint32_t s0 = min(split * per, total), s1 = min(s0 + per, total);
+    const size_t head_base = kv_row_offset(a.seq_id, kvh, 0, a.kv_heads, a.max_seq_len, HD);
+    const size_t vec_base = ((size_t)a.seq_id * a.kv_heads + kvh) * (size_t)a.max_seq_len;
+    const size_t ring_base = DENSE ? 0 : kv_row_offset(a.seq_id, kvh, 0, a.kv_heads, a.ring_size, HD);
+    float qr[DPL], acc[DPL];
+#pragma unroll
+    for (int j = 0; j < DPL; ++j) {
+        qr[j] = a.q[(size_t)h * HD + lane * DPL + j];
+        acc[j] = 0.0f;
+    }
+    float m = -INFINITY, l = 0.0f;
+    for (uint32_t slot = s0 + warp; slot < s1; slot += 4u) {
+        uint32_t t;
+        bool old_tok;
+        if (slot < sel_slots) {
+            const uint32_t b = sblk[slot / a.block_size];
+            if (b == 0xffffffffu) continue;
+            t = b * a.block_size + slot % a.block_size;
+            if (t >= a.old_len) continue;
+            old_tok = true;
+        } else {
+            t = a.old_len + (slot - sel_slots);
+            old_tok = false;
+        }
+        const __half* kp;
+        if (DENSE || old_tok) kp = a.old_k + head_base + (size_t)t * HD;
+        else kp = a.ring_k + ring_base + (size_t)(t % a.ring_size) * HD;
+        float kx[DPL], vx[DPL];
+        if (DPL == 4) {
+            const uint2 w = *reinterpret_cast<const uint2*>(kp + lane * 4);
+            const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&w.x));
+            const float2 f1 = __half22float2(*reinterpret_cast<const __half2*>(&w.y));
+            kx[0] = f0.x; kx[1] = f0.y; kx[DPL - 2] = f1.x; kx[DPL - 1] = f1.y;
+        } else {
+            const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(kp + lane * 2));
+            kx[0] = f0.x; kx[1] = f0.y;
+        }
+        float dot = 0.0f;
+#pragma unroll
+        for (int j = 0; j < DPL; ++j) dot = fmaf(qr[j], kx[j], dot);
+        const float s = warp_sum(dot) * a.inv_sqrt;
+        if (!DENSE && old_tok) {
+            const float scale = a.q4_scale[vec_base + t];
+            const uint8_t* vp = a.q4_v + (vec_base + t) * (HD / 2) + lane * (DPL / 2);
+            uint32_t bytes;
+            if (DPL == 4) bytes = *reinterpret_cast<const uint16_t*>(vp);
+            else bytes = *vp;
+#pragma unroll
+            for (int j = 0; j < DPL; ++j) {
+                const uint32_t nib = (bytes >> (4 * j)) & 0xfu;
+                const int sv = nib >= 8u ? (int)nib - 16 : (int)nib;
+                vx[j] = __half2float(__float2half_rn((float)sv * scale));
+            }
+        } else {
+            const __half* vp = DENSE ? a.dense_v + head_base + (size_t)t * HD
+                                     : a.ring_v + ring_base + (size_t)(t % a.ring_size) * HD;
+            if (DPL == 4) {
+                const uint2 w = *reinterpret_cast<const uint2*>(vp + lane * 4);
+                const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&w.x));
+                const float2 f1 = __half22float2(*reinterpret_cast<const __half2*>(&w.y));
+                vx[0] = f0.x; vx[1] = f0.y; vx[DPL - 2] = f1.x; vx[DPL - 1] = f1.y;
+            } else {
+                const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(vp + lane * 2));
+                vx[0] = f0.x; vx[1] = f0.y;
+            }
+        }
+        const float mn = fmaxf(m, s);
+        const float corr = expf(m - mn);
+        const float p = expf(s - mn);
+        l = l * corr + p;
+#pragma unroll
+        for (int j = 0; j < DPL; ++j) acc[j] = fmaf(p, vx[j], acc[j] * corr);
+        m = mn;
+    }
+    if (lane == 0) {
+        sm_m[warp] = m;
+        sm_l[warp] = l;
+    }
+#pragma unroll
+    for (int j = 0; j < DPL; ++j) sm_o[warp][lane * DPL + j] = acc[j];
+    __syncthreads();
+    for (uint32_t d = threadIdx.x; d < HD; d += blockDim.x) {
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) M = fmaxf(M, sm_m[w]);
+        float L = 0.0f, O = 0.0f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const float e = sm_m[w] == -INFINITY ? 0.0f : expf(sm_m[w] - M);
+            L += sm_l[w] * e;
+            O += sm_o[w][d] * e;
+        }
+        const size_t pi = (size_t)h * a.splits + split;
+        if (d == 0) {
+            a.part_m[pi] = M;
+            a.part_l[pi] = L;
+        }
+        a.part_o[pi * HD + d] = O;
+    }
+}
+
+struct SelPlan {
+    uint32_t old_len, nb, top_n, recent_count;
+};
+
+int fill_common(const M40llmKVCache* kv, SelArgs* a, uint32_t seq_id, const void* q, uint32_t q_heads,
+                uint32_t seq_len, uint32_t recent_window, uint32_t block_size, uint32_t top_blocks, bool dense) {
+    a->seq_id = seq_id;
+    a->max_seq_len = kv->max_seq_len;
+    a->kv_heads = kv->num_heads;
+    a->q_heads = q_heads;
+    a->hd = kv->head_dim;
+    a->seq_len = seq_len;
+    a->recent_window = recent_window;
+    a->ring_size = dense ? 0u : kv->recent_window;
+    a->block_size = block_size;
+    a->old_len = seq_len > recent_window ? seq_len - recent_window : 0u;
+    a->nb = a->old_len == 0 ? 0u : (a->old_len + block_size - 1) / block_size;
+    a->top_n = top_blocks < a->nb ? top_blocks : a->nb;
+    a->block_begin = 0;
+    a->block_end = a->nb;
+    a->score_stride = a->nb ? a->nb : 1u;
+    a->include_recent = 1;
+    a->inv_sqrt = attn_inv_sqrt(kv->head_dim);
+    a->q = (const float*)q;
+    if (dense) {
+        a->old_k = kv->d_k;
+        a->dense_v = kv->d_v;
+        a->ring_k = a->ring_v = nullptr;
+        a->q4_v = nullptr;
+        a->q4_scale = nullptr;
+    } else {
+        a->old_k = kv->d_old_k;
+        a->dense_v = nullptr;
+        a->ring_k = kv->d_recent_k;
+        a->ring_v = kv->d_recent_v;
+        a->q4_v = kv->d_q4_v;
+        a->q4_scale = kv->d_q4_scale;
+    }
+    return 0;
+}
+
+int launch_scores(M40llmCudaContext* ctx, const SelArgs& a) {
+    const uint32_t blocks = a.block_end - a.block_begin;
+    if (blocks == 0) return 0;
+    const uint32_t G = a.q_heads / a.kv_heads;
+    dim3 grid((blocks + 3u) / 4u, a.kv_heads);
+    const size_t smem = (size_t)G * a.hd * sizeof(float);
+    if (a.hd == 128) block_score_kernel<128><<<grid, 128, smem, ctx->decode_stream>>>(a);
+    else block_score_kernel<64><<<grid, 128, smem, ctx->decode_stream>>>(a);
+    M40_COUNT_LAUNCH(ctx);
+    return cudaGetLastError() == cudaSuccess ? 0 : -8;
+}
+
+int launch_topk(M40llmCudaContext* ctx, const SelArgs& a) {
+    const size_t smem = (size_t)(a.nb ? a.nb : 1u) * sizeof(float);
+    if (smem > 200u * 1024u) return -7;
+    if (smem > 48u * 1024u)
+        cudaFuncSetAttribute(topk_blocks_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    topk_blocks_kernel<<<a.q_heads, 128, smem, ctx->decode_stream>>>(a);
+    M40_COUNT_LAUNCH(ctx);
+    return cudaGetLastError() == cudaSuccess ? 0 : -8;
+}
+
+int launch_attend(M40llmCudaContext* ctx, const SelArgs& a, bool dense) {
+    dim3 grid(a.splits, a.q_heads);
+    cudaStream_t s = ctx->decode_stream;
+    if (a.hd == 128) {
+        if (dense) selected_attend_kernel<128, true><<<grid, 128, 0, s>>>(a);
+        else selected_attend_kernel<128, false><<<grid, 128, 0, s>>>(a);
+    } else {
+        if (dense) selected_attend_kernel<64, true><<<grid, 128, 0, s>>>(a);
+        else selected_attend_kernel<64, false><<<grid, 128, 0, s>>>(a);
+    }
+    M40_COUNT_LAUNCH(ctx);
+    return cudaGetLastError() == cudaSuccess ? 0 : -8;
+}
+
+uint32_t attend_splits(const M40llmCudaContext* ctx, const SelArgs& a) {
+    const uint32_t total = 64u * a.block_size + (a.seq_len - a.old_len);
+    uint32_t splits = ((uint32_t)ctx->sm_count * 4u + a.q_heads - 1u) / a.q_heads;
+    const uint32_t max_splits = (total + 127u) / 128u;
+    if (splits > max_splits) splits = max_splits;
+    if (splits < 1u) splits = 1u;
+    if (splits > 64u) splits = 64u;
+    return splits;
+}
+
+// Whole block-select attention for one sequence (selection + attention + merge).
+int block_select_attention(M40llmCudaContext* ctx, const M40llmKVCache* kv, uint32_t seq_id, const void* q,
+                           uint32_t q_heads, uint32_t seq_len, uint32_t recent_window, uint32_t block_size,
+                           uint32_t top_blocks, void* out, bool dense) {
+    if (q_heads > ctx->selected_capacity_heads) return -7;
+    SelArgs a = {};
+    fill_common(kv, &a, seq_id, q, q_heads, seq_len, recent_window, block_size, top_blocks, dense);
+    a.splits = attend_splits(ctx, a);
+    const size_t n_scores = (size_t)q_heads * a.score_stride;
+    const size_t n_part = (size_t)q_heads * a.splits;
+    float* scratch = (float*)m40_ensure_scratch(ctx, 1, (n_scores + n_part * (2 + (size_t)a.hd)) * sizeof(float));
+    if (!scratch) return -8;
+    a.scores = scratch;
+    a.part_m = scratch + n_scores;
+    a.part_l = a.part_m + n_part;
+    a.part_o = a.part_l + n_part;
+    a.sel_blocks = ctx->d_selected_blocks;
+    a.sel_scores = ctx->d_selected_scores;
+    int rc = launch_scores(ctx, a);
+    if (rc != 0) return rc;
+    rc = launch_topk(ctx, a);
+    if (rc != 0) return rc;
+    rc = launch_attend(ctx, a, dense);
+    if (rc != 0) return rc;
+    return m40_attention_merge_rows(ctx, a.part_m, a.part_l, a.part_o, a.splits, q_heads, a.hd, (float*)out) == 0 ? 0 : -8;
+}
+
+// The reference reads its selection policy from the environment inside the hot entry point
+// (cuda/kernels.cu:4526-4534). Only the default policy (top-k, score order) is implemented;
+// any other setting is refused instead of silently differing.
+bool non_default_policy_requested() {
+    const char* p = getenv("M40LLM_KV_BLOCK_SELECT_POLICY");
+    if (p && p[0] != '\0' && strcmp(p, "topk") != 0) return true;
+    const char* o = getenv("M40LLM_KV_SELECTED_BLOCK_ORDER");
+    if (o && o[0] != '\0' && strcmp(o, "score") != 0) return true;
+    return false;
+}
+
+}  // namespace
+
+extern "C" {
+
+int m40llm_attention_last_token_f32_gqa_block_select_exact_fp16_k_q4_v_old_direct_async(
+    M40llmCudaContext* ctx, const M40llmKVCache* kv, uint32_t seq_id, const void* d_q_f32, uint32_t q_heads,
+    uint32_t seq_len, uint32_t recent_window, uint32_t block_size, uint32_t top_blocks, void* d_out_f32) {
+    if (!ctx || !kv || !d_q_f32 || !d_out_f32) return -1;
+    if (!kv->fp16_k_q4_v_backing || !kv->d_old_k || !kv->d_q4_v || !kv->d_q4_scale || !kv->d_recent_k ||
+        !kv->d_recent_v)
+        return -16;
+    if (seq_id >= kv->max_batch_size) return -2;
+    if (seq_len == 0 || seq_len > kv->max_seq_len) return -3;
+    if (q_heads == 0 || kv->num_heads == 0 || q_heads % kv->num_heads != 0) return -4;
+    if (kv->head_dim != 64 && kv->head_dim != 128) return -5;
+    if (recent_window == 0 || block_size == 0 || top_blocks == 0 || top_blocks > 64) return -6;
+    // The ring is addressed with the cache's own window (kernels.cu:3036 uses the argument for both;
+    // the reference host always passes the cache's configuration, src/infer/kv.rs:562-575).
+    if (recent_window != kv->recent_window) return -6;
+    if (non_default_policy_requested()) return M40LLM_ERR_UNSUPPORTED;
+    if (m40_ensure_device(ctx) != 0) return -1;
+    return block_select_attention(ctx, kv, seq_id, d_q_f32, q_heads, seq_len, recent_window, block_size, top_blocks,
+                                  d_out_f32, false);
+}
+
+int m40llm_attention_last_token_f32_gqa_block_select_exact_async(M40llmCudaContext* ctx, const M40llmKVCache* kv,
+                                                                 uint32_t seq_id, const void* d_q_f32,
+                                                                 uint32_t q_heads, uint32_t seq_len,
+                                                                 uint32_t recent_window, uint32_t block_size,
+                                                                 uint32_t top_blocks, void* d_out_f32) {
+    if (!ctx || !kv || !d_q_f32 || !d_out_f32) return -1;
+    if (seq_id >= kv->max_batch_size) return -2;
+    if (seq_len == 0 || seq_len > kv->max_seq_len) return -3;
+    if (q_heads == 0 || kv->num_heads == 0 || q_heads % kv->num_heads != 0) return -4;
+    if (kv->head_dim != 64 && kv->head_dim != 128) return -5;
+    if (recent_window == 0 || block_size == 0 || top_blocks == 0 || top_blocks > 64) return -6;
+    if (!kv->d_k || !kv->d_v) return -7;
+    if (non_default_policy_requested()) return M40LLM_ERR_UNSUPPORTED;
+    if (m40_ensure_device(ctx) != 0) return -1;
+    return block_select_attention(ctx, kv, seq_id, d_q_f32, q_heads, seq_len, recent_window, block_size, top_blocks,
+                                  d_out_f32, true);
+}
+
+int m40llm_kvcache_score_old_blocks_async(M40llmCudaContext* ctx, const M40llmKVCache* kv, uint32_t seq_id,
+                                          const void* d_q_f32, uint32_t q_heads, uint32_t seq_len,
+                                          uint32_t block_begin, uint32_t block_end, void* d_scores_f32) {
+    if (!ctx || !kv || !d_q_f32 || !d_scores_f32) return -1;
+    if (!kv->compressed || !kv->d_old_k) return -16;
+    if (seq_id >= kv->max_batch_size) return -2;
+    if (seq_len == 0 || seq_len > kv->max_seq_len) return -3;
+    if (q_heads == 0 || kv->num_heads == 0 || q_heads % kv->num_heads != 0) return -4;
+    if (kv->head_dim != 64 && kv->head_dim != 128) return -5;
+    if (m40_ensure_device(ctx) != 0) return -1;
+    SelArgs a = {};
+    fill_common(kv, &a, seq_id, d_q_f32, q_heads, seq_len, kv->recent_window, kv->block_size, 64, false);
+    if (block_begin > block_end || block_end > a.nb) return -6;
+    a.block_begin = block_begin;
+    a.block_end = block_end;
+    a.score_stride = block_end - block_begin ? block_end - block_begin : 1u;
+    a.scores = (float*)d_scores_f32;
+    return launch_scores(ctx, a);
+}
+
+int m40llm_attention_compressed_selected_partial_async(M40llmCudaContext* ctx, const M40llmKVCache* kv,
+                                                       uint32_t seq_id, const void* d_q_f32, uint32_t q_heads,
+                                                       uint32_t seq_len, const uint32_t* d_blocks,
+                                                       uint32_t block_begin, uint32_t block_end,
+                                                       uint32_t include_recent, void* d_m_f32, void* d_l_f32,
+                                                       void* d_o_f32) {
+    if (!ctx || !kv || !d_q_f32 || !d_blocks || !d_m_f32 || !d_l_f32 || !d_o_f32) return -1;
+    if (!kv->compressed || !kv->d_old_k || !kv->d_q4_v) return -16;
+    if (seq_id >= kv->max_batch_size) return -2;
+    if (seq_len == 0 || seq_len > kv->max_seq_len) return -3;
+    if (q_heads == 0 || kv->num_heads == 0 || q_heads % kv->num_heads != 0) return -4;
+    if (kv->head_dim != 64 && kv->head_dim != 128) return -5;
+    if (m40_ensure_device(ctx) != 0) return -1;
+    SelArgs a = {};
+    fill_common(kv, &a, seq_id, d_q_f32, q_heads, seq_len, kv->recent_window, kv->block_size, 64, false);
+    if (block_begin > block_end || block_end > a.nb) return -6;
+    a.block_begin = block_begin;
+    a.block_end = block_end;
+    a.include_recent = include_recent ? 1u : 0u;
+    a.sel_blocks = const_cast<uint32_t*>(d_blocks);
+    a.splits = attend_splits(ctx, a);
+    const size_t n_part = (size_t)q_heads * a.splits;
+    float* scratch = (float*)m40_ensure_scratch(ctx, 1, n_part * (2 + (size_t)a.hd) * sizeof(float));
+    if (!scratch) return -8;
+    a.part_m = scratch;
+    a.part_l = scratch + n_part;
+    a.part_o = scratch + 2 * n_part;
+    int rc = launch_attend(ctx, a, false);
+    if (rc != 0) return rc;
+    return m40_attention_fold_partials(ctx, a.part_m, a.part_l, a.part_o, a.splits, q_heads, a.hd, (float*)d_m_f32,
+                                       (float*)d_l_f32, (float*)d_o_f32) == 0 ? 0 : -8;
+}
+
+int m40llm_kvcache_debug_last_selected_blocks(M40llmCudaContext* ctx, uint32_t q_heads, uint32_t* out_blocks_host,
+                                              float* out_scores_host) {
+    if (!ctx || !out_blocks_host) return -1;
+    if (q_heads == 0 || q_heads > ctx->selected_capacity_heads) return -2;
+    if (m40_ensure_device(ctx) != 0) return -1;
+    if (cudaStreamSynchronize(ctx->decode_stream) != cudaSuccess) return -3;
+    if (cudaMemcpy(out_blocks_host, ctx->d_selected_blocks, (size_t)q_heads * 64 * sizeof(uint32_t),
+                   cudaMemcpyDeviceToHost) != cudaSuccess)
+        return -4;
+    if (out_scores_host && cudaMemcpy(out_scores_host, ctx->d_selected_scores, (size_t)q_heads * 64 * sizeof(float),
+                                      cudaMemcpyDeviceToHost) != cudaSuccess)
+        return -4;
+    return 0;
+}
+
+int m40llm_kvcache_debug_select_old_blocks(M40llmCudaContext* ctx, const M40llmKVCache* kv, uint32_t seq_id,
+                                           const void* d_q_f32, uint32_t q_heads, uint32_t seq_len,
+                                           uint32_t recent_window, uint32_t block_size, uint32_t top_blocks,
+                                           uint32_t* out_blocks_host, float* out_scores_host, uint32_t* out_start_host,
+                                           uint32_t* out_end_host, uint32_t* out_count, uint32_t max_out,
+                                           uint32_t* out_total_old_blocks) {
+    if (!ctx || !kv || !d_q_f32 || !out_blocks_host || !out_scores_host || !out_start_host || !out_end_host ||
+        !out_count || !out_total_old_blocks)
+        return -1;
+    if (seq_id >= kv->max_batch_size) return -2;
+    if (q_heads == 0 || kv->num_heads == 0 || kv->head_dim == 0) return -3;
+    if (seq_len == 0 || seq_len > kv->max_seq_len || block_size == 0 || max_out == 0) return -4;
+    const uint32_t eff_recent = kv->compressed ? kv->recent_window : recent_window;
+    const uint32_t eff_block = kv->compressed ? kv->block_size : block_size;
+    if (eff_recent == 0 || eff_block == 0) return -5;
+    if (kv->head_dim != 64 && kv->head_dim != 128) return -3;
+    if (q_heads % kv->num_heads != 0) return -3;
+    if (non_default_policy_requested()) return M40LLM_ERR_UNSUPPORTED;
+    if (m40_ensure_device(ctx) != 0) return -1;
+    const bool dense = !kv->compressed;
+    if (dense && !kv->d_k) return -9;
+    if (!dense && !kv->d_old_k) return -12;
+    SelArgs a = {};
+    fill_common(kv, &a, seq_id, d_q_f32, q_heads, seq_len, eff_recent, eff_block, 64, dense);
+    *out_total_old_blocks = a.nb;
+    *out_count = 0;
+    if (a.nb == 0) return 0;
+    uint32_t want = top_blocks == 0 ? a.nb : (top_blocks < a.nb ? top_blocks : a.nb);
+    if (want > max_out) want = max_out;
+    if (want > 64u) want = 64u;
+    a.top_n = want;
+    float* scratch = (float*)m40_ensure_scratch(ctx, 1, (size_t)q_heads * a.score_stride * sizeof(float));
+    if (!scratch) return -6;
+    a.scores = scratch;
+    a.sel_blocks = ctx->d_selected_blocks;
+    a.sel_scores = ctx->d_selected_scores;
+    if (launch_scores(ctx, a) != 0 || launch_topk(ctx, a) != 0) return -6;
+    if (cudaStreamSynchronize(ctx->decode_stream) != cudaSuccess) return -6;
+    uint32_t blocks[64];
+    float scores[64];
+    // the reference reports q head 0 / kv head 0 only (kernels.cu:6485-6486, 6533)
+    if (cudaMemcpy(blocks, ctx->d_selected_blocks, sizeof(blocks), cudaMemcpyDeviceToHost) != cudaSuccess) return -7;
+    if (cudaMemcpy(scores, ctx->d_selected_scores, sizeof(scores), cudaMemcpyDeviceToHost) != cudaSuccess) return -7;
+    uint32_t n = 0;
+    for (uint32_t i = 0; i < want; ++i) {
+        if (blocks[i] == 0xffffffffu) continue;
+        const uint32_t start = blocks[i] * eff_block;
+        const uint32_t end = start + eff_block < a.old_len ? start + eff_block : a.old_len;
+        out_blocks_host[n] = blocks[i];
+        out_scores_host[n] = scores[i];
+        out_start_host[n] = start;
+        out_end_host[n] = end;
+        ++n;
+    }
+    *out_count = n;
+    return 0;
+}
+
+// ---- compressed-cache modes outside the decode hot path ----
+#define M40_UNSUPPORTED_SELECT_BODY                                                          \
+    (void)recent_window; (void)block_size; (void)top_blocks;                                  \
+    if (!ctx || !kv || !d_q_f32 || !d_out_f32) return -1;                                     \
+    if (seq_id >= kv->max_batch_size) return -2;                                              \
+    if (seq_len == 0 || seq_len > kv->max_seq_len) return -3;                                 \
+    if (q_heads == 0 || kv->num_heads == 0 || q_heads % kv->num_heads != 0) return -4;        \
+    return M40LLM_ERR_UNSUPPORTED;
+
+int m40llm_attention_last_token_f32_gqa_block_select_exact_staged_async(
+    M40llmCudaContext* ctx, const M40llmKVCache* kv, uint32_t seq_id, const void* d_q_f32, uint32_t q_heads,
+    uint32_t seq_len, uint32_t recent_window, uint32_t block_size, uint32_t top_blocks, void* d_out_f32) {
+    M40_UNSUPPORTED_SELECT_BODY
+}
+int m40llm_attention_last_token_f32_gqa_block_select_exact_staged_with_buffers_async(
+    M40llmCudaContext* ctx, const M40llmKVCache* kv, uint32_t seq_id, const void* d_q_f32, uint32_t q_heads,
+    uint32_t seq_len, uint32_t recent_window, uint32_t block_size, uint32_t top_blocks, void* staged_k_dev,
+    void* staged_v_dev, void* staged_positions_dev, void* staged_counts_dev, uint32_t staged_capacity_tokens,
+    void* d_out_f32) {
+    (void)staged_k_dev; (void)staged_v_dev; (void)staged_positions_dev; (void)staged_counts_dev;
+    (void)staged_capacity_tokens;
+    M40_UNSUPPORTED_SELECT_BODY
+}
+int m40llm_attention_last_token_f32_gqa_block_select_exact_staged_q8_old_with_buffers_async(
+    M40llmCudaContext* ctx, const M40llmKVCache* kv, uint32_t seq_id, const void* d_q_f32, uint32_t q_heads,
+    uint32_t seq_len, uint32_t recent_window, uint32_t block_size, uint32_t top_blocks, void* staged_k_dev,
+    void* staged_v_dev, void* staged_positions_dev, void* staged_counts_dev, uint32_t staged_capacity_tokens,
+    void* d_out_f32) {
+    (void)staged_k_dev; (void)staged_v_dev; (void)staged_positions_dev; (void)staged_counts_dev;
+    (void)staged_capacity_tokens;
+    M40_UNSUPPORTED_SELECT_BODY
+}
+int m40llm_attention_last_token_f32_gqa_block_select_exact_staged_fp16_k_q4_v_old_with_buffers_async(
+    M40llmCudaContext* ctx, const M40llmKVCache* kv, uint32_t seq_id, const void* d_q_f32, uint32_t q_heads,
+    uint32_t seq_len, uint32_t recent_window, uint32_t block_size, uint32_t top_blocks, void* staged_k_dev,
+    void* staged_v_dev, void* staged_positions_dev, void* staged_counts_dev, uint32_t staged_capacity_tokens,
+    void* d_out_f32) {
+    (void)staged_k_dev; (void)staged_v_dev; (void)staged_positions_dev; (void)staged_counts_dev;
+    (void)staged_capacity_tokens;
+    M40_UNSUPPORTED_SELECT_BODY
+}
+int m40llm_attention_last_token_f32_gqa_block_select_exact_q8_old_direct_async(
+    M40llmCudaContext* ctx, const M40llmKVCache* kv, uint32_t seq_id, const void* d_q_f32, uint32_t q_heads,
+    uint32_t seq_len, uint32_t recent_window, uint32_t block_size, uint32_t top_blocks, void* d_out_f32) {
+    M40_UNSUPPORTED_SELECT_BODY
+}
+int m40llm_attention_last_token_f32_gqa_block_summary_lossy_async(
+    M40llmCudaContext* ctx, const M40llmKVCache* kv, uint32_t seq_id, const void* d_q_f32, uint32_t q_heads,
+    uint32_t seq_len, uint32_t recent_window, uint32_t block_size, uint32_t top_blocks, void* d_out_f32) {
+    M40_UNSUPPORTED_SELECT_BODY
+}
+int m40llm_attention_last_token_f32_gqa_compressed_recent_only_async(M40llmCudaContext* ctx, const M40llmKVCache* kv,
+                                                                     uint32_t seq_id, const void* d_q_f32,
+                                                                     uint32_t q_heads, uint32_t seq_len,
+                                                                     void* d_out_f32) {
+    if (!ctx || !kv || !d_q_f32 || !d_out_f32) return -1;
+    if (!kv->compressed) return -2;
+    if (seq_id >= kv->max_batch_size) return -3;
+    if (seq_len == 0 || seq_len > kv->max_seq_len) return -4;
+    if (q_heads == 0 || kv->num_heads == 0 || q_heads % kv->num_heads != 0) return -5;
+    return M40LLM_ERR_UNSUPPORTED;
+}
+
+}  // extern "C"

@@ -1,0 +1,96 @@
+// Fused attention prologue for a batch of decode rows:
+//   xn = rmsnorm(x, w);  q,k,v = xn.Wq/Wk/Wv (+bias);  q <- rope(q, pos);
+//   cache[seq][pos] <- f16(rope(k, pos)), f16(v)
+// The reference issues this as 1 norm + 3 GEMMs + 3 bias adds + per-row rope and append launches
+// with cross-stream waits between them (src/infer/forward.rs:307-421). Here it is five launches
+// on the decode stream for any number of rows: the norm, three projections that share the
+// normalised activations (bias folded into their epilogue), and one rope+append launch that
+// covers every row, q head and kv head.
+#include "common.cuh"
+#include "gemm.cuh"
+#include "kv_append.cuh"
+
+namespace {
+
+// grid (q_heads + kv_heads, rows), block 64.
+__global__ void __launch_bounds__(64) rope_q_append_kv_rows_kernel(float* __restrict__ q, const float* __restrict__ k,
+                                                                   const float* __restrict__ v, M40llmKVCache kv,
+                                                                   const uint32_t* __restrict__ seq_ids,
+                                                                   const uint32_t* __restrict__ positions,
+                                                                   uint32_t q_heads, float freq_base, float freq_scale,
+                                                                   uint32_t layout, uint32_t* status) {
+    __shared__ float red[32];
+    const uint32_t row = blockIdx.y, hsel = blockIdx.x;
+    const uint32_t hd = kv.head_dim, half = hd / 2u;
+    const uint32_t seq = seq_ids[row], pos = positions[row];
+    if (seq >= kv.max_batch_size || pos >= kv.max_seq_len) {
+        if (threadIdx.x == 0 && hsel == 0) atomicOr(status, 2u);
+        return;
+    }
+    if (hsel < q_heads) {
+        float* qh = q + ((size_t)row * q_heads + hsel) * hd;
+        for (uint32_t i = threadIdx.x; i < half; i += blockDim.x) {
+            const uint32_t i0 = layout == 1u ? i : 2u * i;
+            const uint32_t i1 = layout == 1u ? i + half : 2u * i + 1u;
+            float c, s;
+            rope_cs(pos, i, hd, freq_base, freq_scale, &c, &s);
+            const float a = qh[i0], b = qh[i1];
+            qh[i0] = a * c - b * s;
+            qh[i1] = a * s + b * c;
+        }
+        return;
+    }
+    const uint32_t kvh = hsel - q_heads;
+    const float* kh = k + ((size_t)row * kv.num_heads + kvh) * hd;
+    const float* vh = v + ((size_t)row * kv.num_heads + kvh) * hd;
+    if (kv.compressed) kv_append_compressed_head(kv, seq, kvh, pos, kh, vh, freq_base, freq_scale, layout, red);
+    else kv_append_dense_head(kv, seq, kvh, pos, kh, vh, freq_base, freq_scale, layout);
+}
+
+}  // namespace
+
+int m40_rms_norm_rows(M40llmCudaContext* ctx, const void* in, const void* w, void* out, uint32_t rows, uint32_t dim,
+                      float eps, uint32_t wdtype);
+
+extern "C" int m40llm_qkv_rmsnorm_rope_append_async(M40llmCudaContext* ctx, M40llmKVCache* kv, const void* d_x_f32,
+                                                    const void* d_norm_w, uint32_t norm_w_dtype, float eps,
+                                                    const void* d_wq_f16, const void* d_wk_f16, const void* d_wv_f16,
+                                                    const void* d_bq_f32, const void* d_bk_f32, const void* d_bv_f32,
+                                                    const uint32_t* d_seq_ids, const uint32_t* d_positions,
+                                                    uint32_t rows, uint32_t hidden, uint32_t q_heads, float freq_base,
+                                                    float freq_scale, uint32_t rope_layout, void* d_q_out_f32) {
+    if (!ctx || !kv || !d_x_f32 || !d_norm_w || !d_wq_f16 || !d_wk_f16 || !d_wv_f16 || !d_seq_ids || !d_positions ||
+        !d_q_out_f32)
+        return -1;
+    if (rows == 0 || hidden == 0 || q_heads == 0 || kv->num_heads == 0 || q_heads % kv->num_heads != 0) return -2;
+    if (norm_w_dtype > 1) return -4;
+    if (kv->head_dim == 0 || kv->head_dim % 2 != 0) return -3;
+    if (kv->compressed && kv->head_dim != 64 && kv->head_dim != 128) return -3;
+    if (!kv->compressed && (!kv->d_k || !kv->d_v)) return -3;
+    if (m40_ensure_device(ctx) != 0) return -1;
+    const uint32_t hd = kv->head_dim, QD = q_heads * hd, KD = kv->num_heads * hd;
+    // The decode-stream arena is shared with attention partials, which run later on the same stream.
+    const size_t need = (size_t)rows * ((size_t)hidden + 2 * (size_t)KD) * sizeof(float);
+    float* scratch = (float*)m40_ensure_scratch(ctx, 1, need);
+    if (!scratch) return -5;
+    float* xn = scratch;
+    float* kbuf = xn + (size_t)rows * hidden;
+    float* vbuf = kbuf + (size_t)rows * KD;
+    cudaStream_t s = ctx->decode_stream;
+    int rc = m40_rms_norm_rows(ctx, d_x_f32, d_norm_w, xn, rows, hidden, eps, norm_w_dtype);
+    if (rc != 0) return rc;
+    rc = m40_gemm_dispatch_f16(ctx, s, 1u, xn, (const __half*)d_wq_f16, (float*)d_q_out_f32, (int)rows, (int)QD,
+                               (int)hidden, (const float*)d_bq_f32, nullptr);
+    if (rc != 0) return rc;
+    rc = m40_gemm_dispatch_f16(ctx, s, 1u, xn, (const __half*)d_wk_f16, kbuf, (int)rows, (int)KD, (int)hidden,
+                               (const float*)d_bk_f32, nullptr);
+    if (rc != 0) return rc;
+    rc = m40_gemm_dispatch_f16(ctx, s, 1u, xn, (const __half*)d_wv_f16, vbuf, (int)rows, (int)KD, (int)hidden,
+                               (const float*)d_bv_f32, nullptr);
+    if (rc != 0) return rc;
+    dim3 grid(q_heads + kv->num_heads, rows);
+    rope_q_append_kv_rows_kernel<<<grid, 64, 0, s>>>((float*)d_q_out_f32, kbuf, vbuf, *kv, d_seq_ids, d_positions,
+                                                     q_heads, freq_base, freq_scale, rope_layout, ctx->d_status);
+    M40_COUNT_LAUNCH(ctx);
+    return cudaGetLastError() == cudaSuccess ? 0 : -6;
+}

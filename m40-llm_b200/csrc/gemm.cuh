@@ -1,0 +1,17 @@
+// Internal launch helpers of gemm.cu, shared with the fused layer paths.
+#pragma once
+#include "common.cuh"
+
+// C[m][n] = sum_k A[m][k] * W[n][k] (+ bias[n]) (+ residual[m][n]); W f16 GGUF rows.
+int m40_gemm_f32xf16_gguf(M40llmCudaContext* ctx, cudaStream_t s, const float* A, const __half* W, float* C, int M,
+                          int N, int K, const float* bias, const float* residual);
+int m40_gemm_dispatch_f16(M40llmCudaContext* ctx, cudaStream_t s, uint32_t stream_kind, const float* A,
+                          const __half* W, float* C, int M, int N, int K, const float* bias, const float* residual);
+// Same over Q8_0 rows (+ residual).
+int m40_gemm_f32xq80_gguf(M40llmCudaContext* ctx, cudaStream_t s, const float* A, const uint8_t* W, float* C, int M,
+                          int N, int K, const float* residual);
+// hid[m][n] = silu(A.Wg[n]) * (A.Wu[n])
+int m40_gate_up_swiglu_q80(M40llmCudaContext* ctx, cudaStream_t s, const float* A, const uint8_t* Wg,
+                           const uint8_t* Wu, float* hid, int M, int F, int K);
+int m40_gate_up_swiglu_f16(M40llmCudaContext* ctx, cudaStream_t s, const float* A, const __half* Wg, const __half* Wu,
+                           float* hid, int M, int F, int K);

@@ -1,0 +1,196 @@
+"""Shared test helpers: package loader, device buffers over the C ABI, tolerances, generators."""
+from __future__ import annotations
+
+import ctypes as C
+import importlib.util
+import os
+import sys
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+PKG_DIR = os.path.join(ROOT, "m40-llm_b200")
+REF_LIB = os.path.join(ROOT, "oracle", "_ref", "libm40llm_ref.so")
+GOLDEN = os.path.join(ROOT, "tests", "golden")
+
+# Parity tolerance for floating-point outputs: |a - e| <= ATOL + RTOL * |e|.
+ATOL = 1e-3
+RTOL = 2e-3
+# Two block scores closer than this are a tie for the selection comparison.
+TIE_EPS = 1e-6
+
+
+def load_package():
+    if "m40_llm_b200" in sys.modules:
+        return sys.modules["m40_llm_b200"]
+    spec = importlib.util.spec_from_file_location(
+        "m40_llm_b200", os.path.join(PKG_DIR, "__init__.py"), submodule_search_locations=[PKG_DIR])
+    mod = importlib.util.module_from_spec(spec)
+    sys.modules["m40_llm_b200"] = mod
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def assert_close(actual, expected, atol=ATOL, rtol=RTOL, what=""):
+    actual = np.asarray(actual, dtype=np.float64)
+    expected = np.asarray(expected, dtype=np.float64)
+    assert actual.shape == expected.shape, (actual.shape, expected.shape)
+    assert np.all(np.isfinite(actual)), f"{what}: non-finite output"
+    err = np.abs(actual - expected)
+    bound = atol + rtol * np.abs(expected)
+    bad = err > bound
+    if bad.any():
+        i = int(np.argmax(err - bound))
+        raise AssertionError(
+            f"{what}: {int(bad.sum())}/{err.size} outside |a-e| <= {atol} + {rtol}|e|; worst at flat index {i}: "
+            f"actual={actual.ravel()[i]!r} expected={expected.ravel()[i]!r} err={err.ravel()[i]:.3e}")
+
+
+def assert_selection_matches(sel_actual, sel_expected, scores_f64, what=""):
+    """Selected block sets must match exactly unless the symmetric difference only contains blocks
+    whose exact score is within TIE_EPS of the cut-off (the lowest selected) score. Order is not compared."""
+    a = set(int(b) for b in sel_actual if int(b) != 0xFFFFFFFF)
+    e = set(int(b) for b in sel_expected if int(b) != 0xFFFFFFFF)
+    assert len(a) == len(e), f"{what}: selected {len(a)} blocks, expected {len(e)}"
+    if a == e:
+        return
+    cutoff = min(scores_f64[b] for b in e)
+    for b in a ^ e:
+        assert abs(scores_f64[b] - cutoff) <= TIE_EPS, (
+            f"{what}: block {b} differs and is not a tie (score {scores_f64[b]!r}, cut-off {cutoff!r})")
+
+
+class DevBuf:
+    """A device allocation made and moved through the C ABI (m40llm_device_malloc / memcpy_*)."""
+
+    def __init__(self, nat: "Native", nbytes: int):
+        self.nat = nat
+        self.nbytes = max(int(nbytes), 4)
+        p = C.c_void_p()
+        rc = nat.lib.m40llm_device_malloc(nat.ctx, self.nbytes, C.byref(p))
+        assert rc == 0 and p.value, f"device_malloc rc={rc}"
+        self.ptr = p.value
+
+    def upload(self, arr: np.ndarray):
+        arr = np.ascontiguousarray(arr)
+        assert arr.nbytes <= self.nbytes
+        if arr.nbytes:
+            rc = self.nat.lib.m40llm_memcpy_h2d(self.nat.ctx, self.ptr, arr.ctypes.data_as(C.c_void_p), arr.nbytes)
+            assert rc == 0, rc
+        return self
+
+    def download(self, dtype, shape) -> np.ndarray:
+        out = np.empty(shape, dtype=dtype)
+        assert out.nbytes <= self.nbytes
+        if out.nbytes:
+            rc = self.nat.lib.m40llm_memcpy_d2h(self.nat.ctx, out.ctypes.data_as(C.c_void_p), self.ptr, out.nbytes)
+            assert rc == 0, rc
+        return out
+
+    def free(self):
+        if self.ptr:
+            self.nat.lib.m40llm_device_free(self.nat.ctx, self.ptr)
+            self.ptr = None
+
+
+class Native:
+    """One context on device 0 plus conveniences. `lib` may be the B200 library or the
+    reference's own translation unit built for sm_100a (same ABI)."""
+
+    def __init__(self, lib, device: int = 0):
+        self.lib = lib
+        self.ctx = lib.m40llm_create_context(device)
+        assert self.ctx, "m40llm_create_context failed (no CUDA device?)"
+        self._bufs: list[DevBuf] = []
+
+    def buf(self, arr_or_bytes) -> DevBuf:
+        if isinstance(arr_or_bytes, (int, np.integer)):
+            b = DevBuf(self, int(arr_or_bytes))
+        else:
+            arr = np.ascontiguousarray(arr_or_bytes)
+            b = DevBuf(self, arr.nbytes).upload(arr)
+        self._bufs.append(b)
+        return b
+
+    def sync(self, kind: int | None = None):
+        for k in ((0, 1) if kind is None else (kind,)):
+            rc = self.lib.m40llm_stream_synchronize(self.ctx, k)
+            assert rc == 0, rc
+
+    def free_all(self):
+        for b in self._bufs:
+            b.free()
+        self._bufs.clear()
+
+    # ---- KV cache conveniences -------------------------------------------------
+    def kv_dense(self, max_seq, slots, kv_heads, hd):
+        kv = self.lib.m40llm_kvcache_create(self.ctx, max_seq, slots, kv_heads, hd)
+        assert kv, "kvcache_create failed"
+        return kv
+
+    def kv_compressed(self, max_seq, slots, kv_heads, hd, recent, block, top):
+        kv = self.lib.m40llm_kvcache_create_compressed(self.ctx, max_seq, slots, kv_heads, hd, recent, block, top, 0, 0, 2)
+        assert kv, "kvcache_create_compressed failed"
+        return kv
+
+    def kv_fill(self, kv, seq_id, k_f16, v_f16, final_len=None, tok_begin=0):
+        """Bulk-load f16 K/V [tokens, kv_heads, hd] (K already rotated) through the harness loader."""
+        k_f16 = np.ascontiguousarray(k_f16)
+        v_f16 = np.ascontiguousarray(v_f16)
+        n = k_f16.shape[0]
+        rc = self.lib.m40llm_kvcache_debug_write_range(
+            self.ctx, kv, seq_id, tok_begin, n, k_f16.ctypes.data_as(C.c_void_p), v_f16.ctypes.data_as(C.c_void_p),
+            tok_begin + n if final_len is None else final_len)
+        assert rc == 0, rc
+
+    def kv_append_tokens(self, kv, seq_id, k_f32, v_f32, base=10000.0, scale=0.0, layout=0, start=0):
+        """Token-by-token append through m40llm_kvcache_append_token_f32_rope_k_at_layout_async."""
+        n = k_f32.shape[0]
+        dk = self.buf(k_f32.astype(np.float32))
+        dv = self.buf(v_f32.astype(np.float32))
+        stride = k_f32[0].size * 4
+        for t in range(n):
+            rc = self.lib.m40llm_kvcache_append_token_f32_rope_k_at_layout_async(
+                self.ctx, kv, seq_id, dk.ptr + t * stride, dv.ptr + t * stride, start + t, start + t, base, scale, layout)
+            assert rc == 0, rc
+        self.sync(1)
+
+
+def load_reference_lib(pkg):
+    """The reference project's own cuda/kernels.cu built for sm_100a (oracle/_ref), or None."""
+    if not os.path.exists(REF_LIB):
+        return None
+    dll = C.CDLL(REF_LIB)
+    sigs = pkg.native.parse_header()
+    for name, (restype, argtypes) in sigs.items():
+        try:
+            fn = getattr(dll, name)
+        except AttributeError:
+            continue
+        fn.restype = restype
+        fn.argtypes = argtypes
+    return dll
+
+
+def rope_rows_np(x, heads, hd, positions, base, scale, layout):
+    """Independent float64-angle-free restatement is not wanted here: this mirrors the f32 formula
+    (tests/rmsnorm_rope.rs:43-76) with numpy float32 ops, per row position."""
+    x = np.array(x, dtype=np.float32).reshape(len(positions), heads, hd).copy()
+    half = hd // 2
+    i = np.arange(half, dtype=np.float32)
+    inv = np.power(np.float32(base), (np.float32(-2.0) * i / np.float32(hd)).astype(np.float32)).astype(np.float32)
+    for r, pos in enumerate(positions):
+        theta = (np.float32(pos) * np.float32(scale)) * inv
+        c = np.cos(theta).astype(np.float32)
+        s = np.sin(theta).astype(np.float32)
+        if layout == 1:
+            a = x[r, :, :half].copy()
+            b = x[r, :, half:].copy()
+            x[r, :, :half] = a * c - b * s
+            x[r, :, half:] = a * s + b * c
+        else:
+            a = x[r, :, 0::2].copy()
+            b = x[r, :, 1::2].copy()
+            x[r, :, 0::2] = a * c - b * s
+            x[r, :, 1::2] = a * s + b * c
+    return x

@@ -1,0 +1,106 @@
+"""GEMV/GEMM entry points against the oracle (tests/gemm_mixed.rs, gemm_f16xf16_f32.rs, proj_wrappers.rs,
+mlp_wrappers.rs of the reference use 1e-3 absolute; here |a-e| <= 1e-3 + 2e-3|e|)."""
+import numpy as np
+import pytest
+
+from helpers import assert_close
+
+pytestmark = pytest.mark.gpu
+
+SHAPES = [(1, 10, 37), (3, 17, 64), (1, 256, 2048), (1, 2048, 2048), (2, 1024, 4096), (1, 4096, 4096),
+          (5, 520, 1032), (8, 4096, 4096), (1, 2048, 5632)]
+
+
+@pytest.mark.parametrize("M,N,K", SHAPES)
+def test_gemm_f32xf16_gguf(nat, O, M, N, K):
+    rng = np.random.default_rng(M * 31 + N + K)
+    a = rng.standard_normal((M, K)).astype(np.float32)
+    w = (rng.standard_normal((N, K)) * 0.05).astype(np.float16)
+    da, dw, dc = nat.buf(a), nat.buf(w), nat.buf(M * N * 4)
+    assert nat.lib.m40llm_gemm_f32xf16_gguf_f32(nat.ctx, da.ptr, dw.ptr, dc.ptr, M, N, K) == 0
+    exp = O.gemm_f32xf16_gguf(a, w)
+    assert_close(dc.download(np.float32, (M, N)), exp, what=f"gguf {M}x{N}x{K}")
+    for kind in (0, 1):
+        dc.upload(np.zeros(M * N, np.float32))
+        assert nat.lib.m40llm_gemm_f32xf16_gguf_f32_async(nat.ctx, da.ptr, dw.ptr, dc.ptr, M, N, K, kind) == 0
+        nat.sync(kind)
+        assert_close(dc.download(np.float32, (M, N)), exp, what=f"gguf async kind {kind}")
+    nat.free_all()
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 10, 37), (2, 64, 48), (1, 2048, 2048), (3, 1024, 4096), (1, 4096, 4096), (6, 136, 1000)])
+def test_gemm_rowmajor_forms(nat, O, M, N, K):
+    rng = np.random.default_rng(M + N * 3 + K)
+    a = rng.standard_normal((M, K)).astype(np.float32)
+    a16 = a.astype(np.float16)
+    b = (rng.standard_normal((K, N)) * 0.05).astype(np.float16)
+    da, da16, db, dc = nat.buf(a), nat.buf(a16), nat.buf(b), nat.buf(M * N * 4)
+    assert nat.lib.m40llm_gemm_f16xf16_f32(nat.ctx, da16.ptr, db.ptr, dc.ptr, M, N, K) == 0
+    assert_close(dc.download(np.float32, (M, N)), O.gemm_f16xf16_rowmajor(a16, b), what="f16xf16")
+    assert nat.lib.m40llm_gemm_f32xf16_f32(nat.ctx, da.ptr, db.ptr, dc.ptr, M, N, K) == 0
+    assert_close(dc.download(np.float32, (M, N)), O.gemm_f32xf16_rowmajor(a, b), what="f32xf16")
+    dc16 = nat.buf(M * N * 2)
+    assert nat.lib.m40llm_gemm_f16_storage_f32_compute(nat.ctx, da16.ptr, db.ptr, dc16.ptr, M, N, K) == 0
+    got = dc16.download(np.float16, (M, N)).astype(np.float32)
+    assert_close(got, O.gemm_f16_storage(a16, b).astype(np.float32), atol=2e-3, what="f16 storage")
+    nat.free_all()
+
+
+def test_materialize_and_f32_gemm(nat, O):
+    """The reference's default decode projection: expand GGUF f16 to f32 [K][N], then SGEMM (src/infer/gemm.rs:287-362)."""
+    rng = np.random.default_rng(8)
+    M, N, K = 2, 200, 333
+    a = rng.standard_normal((M, K)).astype(np.float32)
+    w = (rng.standard_normal((N, K)) * 0.05).astype(np.float16)
+    da, dw, dbt, dc = nat.buf(a), nat.buf(w), nat.buf(N * K * 4), nat.buf(M * N * 4)
+    assert nat.lib.m40llm_materialize_gguf_f16_to_f32_colmajor_nt(nat.ctx, dw.ptr, dbt.ptr, N, K) == 0
+    assert np.array_equal(dbt.download(np.float32, (K, N)), w.astype(np.float32).T)
+    assert nat.lib.m40llm_gemm_f32xf32_f32(nat.ctx, da.ptr, dbt.ptr, dc.ptr, M, N, K) == 0
+    assert_close(dc.download(np.float32, (M, N)), O.gemm_f32xf16_gguf(a, w), what="f32xf32")
+    assert nat.lib.m40llm_gemm_f32xf32_f32_async(nat.ctx, da.ptr, dbt.ptr, dc.ptr, 0, N, K) == -2
+    nat.free_all()
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 8, 32), (1, 64, 128), (1, 4096, 4096), (3, 1000, 1024), (1, 4096, 14336), (8, 512, 4096)])
+def test_gemm_q80(nat, O, M, N, K):
+    rng = np.random.default_rng(M + N + K)
+    a = rng.standard_normal((M, K)).astype(np.float32)
+    wq = O.q80_quantize((rng.standard_normal((N, K)) * 0.02).astype(np.float32))
+    da, dw, dc = nat.buf(a), nat.buf(wq), nat.buf(M * N * 4)
+    assert nat.lib.m40llm_gemm_f32xq80_gguf_f32_async(nat.ctx, da.ptr, dw.ptr, dc.ptr, M, N, K, 0) == 0
+    nat.sync(0)
+    assert_close(dc.download(np.float32, (M, N)), O.gemm_f32xq80_gguf(a, wq, N), what=f"q80 {M}x{N}x{K}")
+    assert nat.lib.m40llm_gemm_f32xq80_gguf_f32_async(nat.ctx, da.ptr, dw.ptr, dc.ptr, M, N, 33, 0) == -2
+    nat.free_all()
+
+
+@pytest.mark.parametrize("rows,H,F,q80", [(1, 256, 384, True), (1, 4096, 14336, True), (4, 1024, 2816, True),
+                                           (1, 2048, 5632, False), (3, 512, 1024, False)])
+def test_ffn_swiglu(nat, O, rows, H, F, q80):
+    """hid = silu(x.Wg) * (x.Wu); out = residual + hid.Wd  (src/infer/gemm.rs:91-163 + kernels.cu:880-891)."""
+    rng = np.random.default_rng(rows + H + F)
+    x = rng.standard_normal((rows, H)).astype(np.float32)
+    res = rng.standard_normal((rows, H)).astype(np.float32)
+    wg = (rng.standard_normal((F, H)) * 0.02).astype(np.float32)
+    wu = (rng.standard_normal((F, H)) * 0.02).astype(np.float32)
+    wd = (rng.standard_normal((H, F)) * 0.02).astype(np.float32)
+    if q80:
+        wg, wu, wd = O.q80_quantize(wg), O.q80_quantize(wu), O.q80_quantize(wd)
+        hid = O.swiglu(O.gemm_f32xq80_gguf(x, wg, F), O.gemm_f32xq80_gguf(x, wu, F))
+        exp = res + O.gemm_f32xq80_gguf(hid, wd, H)
+        fn = nat.lib.m40llm_ffn_swiglu_q80_f32_async
+    else:
+        wg, wu, wd = wg.astype(np.float16), wu.astype(np.float16), wd.astype(np.float16)
+        hid = O.swiglu(O.gemm_f32xf16_gguf(x, wg), O.gemm_f32xf16_gguf(x, wu))
+        exp = res + O.gemm_f32xf16_gguf(hid, wd)
+        fn = nat.lib.m40llm_ffn_swiglu_f16_f32_async
+    dx, dr, dg, du, dd = nat.buf(x), nat.buf(res), nat.buf(wg), nat.buf(wu), nat.buf(wd)
+    dh, do = nat.buf(rows * F * 4), nat.buf(rows * H * 4)
+    assert fn(nat.ctx, dx.ptr, dg.ptr, du.ptr, dd.ptr, dr.ptr, dh.ptr, do.ptr, rows, H, F, 0) == 0
+    nat.sync(0)
+    assert_close(dh.download(np.float32, (rows, F)), hid, what="hid")
+    assert_close(do.download(np.float32, (rows, H)), exp, what="ffn out")
+    assert fn(nat.ctx, dx.ptr, dg.ptr, du.ptr, dd.ptr, None, dh.ptr, do.ptr, rows, H, F, 1) == 0
+    nat.sync(1)
+    assert_close(do.download(np.float32, (rows, H)), exp - res, what="ffn out, no residual")
+    nat.free_all()

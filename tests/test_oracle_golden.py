@@ -1,0 +1,90 @@
+"""The oracle against golden vectors produced by the REFERENCE'S OWN CUDA code: cuda/kernels.cu of the reference,
+compiled unmodified for sm_100a (oracle/Makefile target `ref`) and run on an NVIDIA B200 by
+tests/golden/make_golden.py --lib ref. Runs on CPU. This is what pins the oracle to the reference."""
+import os
+import sys
+
+import numpy as np
+import pytest
+
+import helpers
+from helpers import assert_close, assert_selection_matches
+
+sys.path.insert(0, helpers.GOLDEN)
+import cases  # noqa: E402
+
+GOLD = os.path.join(helpers.GOLDEN, "ref_b200.npz")
+
+
+@pytest.fixture(scope="module")
+def gold():
+    if not os.path.exists(GOLD):
+        pytest.skip("tests/golden/ref_b200.npz not generated yet")
+    return dict(np.load(GOLD))
+
+
+def test_norm_rope_gemm_elementwise(O, gold):
+    for name in cases.NORM_CASES:
+        x, w = cases.norm_inputs(name)
+        np.testing.assert_allclose(O.rms_norm(x, None, 1e-5), gold[name + "/plain"], atol=1e-4, rtol=1e-5)
+        np.testing.assert_allclose(O.rms_norm(x, w, 1e-5), gold[name + "/weighted"], atol=1e-4, rtol=1e-5)
+    for name, (rows, heads, hd, past, base, layout) in cases.ROPE_CASES.items():
+        np.testing.assert_allclose(O.rope(cases.rope_inputs(name), heads, hd, past, base, 1.0, layout).reshape(rows, -1),
+                                   gold[name], atol=2e-4)
+    for name in cases.GEMM_CASES:
+        a, w = cases.gemm_inputs(name)
+        b = np.ascontiguousarray(w.T)
+        assert_close(O.gemm_f32xf16_gguf(a, w), gold[name + "/gguf"], what=name)
+        assert_close(O.gemm_f32xf16_rowmajor(a, b), gold[name + "/f32xf16"], what=name)
+        assert_close(O.gemm_f16xf16_rowmajor(a.astype(np.float16), b), gold[name + "/f16xf16"], what=name)
+    r = cases.rng_for("elementwise")
+    g = (r.standard_normal(5000) * 3).astype(np.float32)
+    u = r.standard_normal(5000).astype(np.float32)
+    np.testing.assert_allclose(O.swiglu(g, u), gold["swiglu"], atol=1e-5, rtol=1e-5)
+    q80 = O.q80_quantize((r.standard_normal((4, 256)) * 0.02).astype(np.float32))
+    assert np.array_equal(O.q80_to_f32(q80, 1024).reshape(4, 256), gold["q80_to_f32"])
+
+
+def _cache(O, k, v, kvh, hd, base, scale):
+    L = k.shape[0]
+    kr = np.stack([O.rope(k[t], kvh, hd, t, base, scale, 0) for t in range(L)]) if scale != 0.0 else k
+    return O.f32_to_f16(kr).reshape(L, kvh, hd), O.f32_to_f16(v).reshape(L, kvh, hd)
+
+
+def test_dense_attention_and_cache_bytes(O, gold):
+    for name, (qh, kvh, hd, L) in cases.ATTN_CASES.items():
+        k, v, q = cases.attn_inputs(name)
+        k16, v16 = _cache(O, k, v, kvh, hd, 1e4, 1.0)
+        toks = cases.cache_sample_tokens(L)
+        assert np.array_equal(v16[toks].view(np.uint16), gold[name + "/v_cache"]), name  # f32->f16 RNE: bit-exact
+        assert_close(k16[toks].astype(np.float32), gold[name + "/k_cache"].view(np.float16).astype(np.float32), atol=2e-3, what=name)
+        assert_close(O.attention_gqa(k16, v16, q, qh, L), gold[name + "/out"], what=name)
+        key = name + "/block_select_dense_R16_bs8_top4"
+        if key in gold:
+            assert_close(O.attention_block_select_dense(k16, v16, q, qh, L, 16, 8, 4), gold[key], what=key)
+
+
+def test_batched(O, gold):
+    for name, (qh, kvh, hd, lens) in cases.BATCH_CASES.items():
+        ks, vs, q = cases.batch_inputs(name)
+        mx = max(lens)
+        K = np.zeros((len(lens), mx, kvh, hd), np.float16)
+        V = np.zeros_like(K)
+        for b, n in enumerate(lens):
+            K[b, :n] = O.f32_to_f16(ks[b]).reshape(n, kvh, hd)
+            V[b, :n] = O.f32_to_f16(vs[b]).reshape(n, kvh, hd)
+        got = O.attention_gqa_batched(K, V, np.arange(len(lens), dtype=np.uint32), np.array(lens, np.uint32), q, qh)
+        assert_close(got, gold[name + "/out"], what=name)
+
+
+def test_q4_direct_and_selection(O, gold):
+    for name, (qh, kvh, hd, L, R, bs, top) in cases.Q4_CASES.items():
+        k, v, q = cases.q4_inputs(name)
+        k16, v16 = O.f32_to_f16(k).reshape(L, kvh, hd), O.f32_to_f16(v).reshape(L, kvh, hd)
+        old_k, q4, sc, rk, rv = O.compressed_state_from_dense(k16, v16, L, R)
+        out, sel, cnt, _ = O.attention_compressed(old_k, q4, sc, rk, rv, q, qh, L, R, bs, top)
+        assert_close(out, gold[name + "/out"], what=name)
+        blocks, bsc, s32, s64 = O.block_select_head(old_k, q[:hd], 0, max(L - R, 0), bs, top)
+        assert int(gold[name + "/total_blocks"][0]) == len(s64)
+        assert_selection_matches(gold[name + "/head0_blocks"], blocks, s64, what=name)
+        np.testing.assert_allclose(gold[name + "/head0_scores"], [s64[int(b)] for b in gold[name + "/head0_blocks"]], atol=2e-5)
