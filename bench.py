@@ -1,0 +1,446 @@
+"""Benchmark of the decode hot path: one Llama-3-8B-shaped decode layer step, batched variable-length.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+Workload (BASELINE.json configs[2]): hidden 4096, 32 q heads / 8 kv heads, head_dim 128, FFN 14336 with Q8_0
+weights, FP16 attention weights, batch 32 with per-sequence contexts uniform in [512, 8192], RoPE theta 5e5.
+One step = one pass of the layer over the batch (fused norm+QKV+RoPE+append, batched decode attention,
+output projection + residual, norm, Q8_0 SwiGLU FFN + residual): 32 tokens advance one layer.
+
+`value`   tokens/s with inputs resident in HBM, the layer replayed as one CUDA graph on the decode stream.
+`e2e`     the same metric through the C ABI with HOST buffers: per step the activations and the batch plan are
+          copied from pinned host memory, the layer runs, the result is copied back.
+`roofline` the dominant kernel (batched decode attention): algorithmic bytes / CUDA-event duration vs the
+          measured HBM copy bandwidth.
+`cpu_baseline` the oracle (CPU restatement of the reference math) timed on this box's host cores on a bounded
+          sample of the same batch.
+With N > 1 (torchrun) every rank runs its own batch of 32 sequences (weak scaling, no collective on the path).
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import importlib.util
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "tests"))
+
+H, QH, KVH, HD, F = 4096, 32, 8, 128, 14336
+B, LMIN, LMAX = 32, 512, 8192
+EPS, THETA = 1e-5, 500000.0
+N_WEIGHT_SETS = 2  # rotated between steps so no weight byte survives in L2 from one step to the next
+# Traffic of the dominant kernel from the committed ncu capture (profiles/): DRAM bytes per algorithmic byte.
+NCU_TRAFFIC_RATIO = None
+
+
+def layer_weight_bytes():
+    attn = (QH * HD * H + 2 * KVH * HD * H + H * QH * HD) * 2
+    ffn = (2 * F * (H // 32) * 34) + H * (F // 32) * 34
+    return attn + ffn
+
+
+def attention_bytes(lens):
+    # K and V once per kv head, q and out once (f32)
+    return int(sum(2 * int(l) * KVH * HD * 2 for l in lens) + len(lens) * 2 * QH * HD * 4)
+
+
+def step_bytes(lens):
+    rows = len(lens)
+    act = rows * H * 4 * 8  # x, xn, q, att, x1, x1n, out and the hid round trip are small next to weights
+    return layer_weight_bytes() + attention_bytes(lens) + act
+
+
+def measured_peak_gbs():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        try:
+            return float(json.load(open(p))["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.rows = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm = [float(r[0]) for r in self.rows if len(r) >= 6 and r[0].replace(".", "").isdigit()]
+        mx = [float(r[1]) for r in self.rows if len(r) >= 6 and r[1].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = sorted({names[i] for r in self.rows if len(r) >= 6 for i in range(4) if r[2 + i].lower().startswith("active")})
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(sm)}
+
+
+def make_inputs(O, seed):
+    rng = np.random.default_rng(seed)
+    lens = rng.integers(LMIN, LMAX + 1, size=B).astype(np.uint32)
+    sets = []
+    for _ in range(N_WEIGHT_SETS):
+        w = {}
+        for n, s in dict(wq=(QH * HD, H), wk=(KVH * HD, H), wv=(KVH * HD, H), wo=(H, QH * HD)).items():
+            w[n] = (rng.standard_normal(s, dtype=np.float32) * 0.02).astype(np.float16)
+        for n, s in dict(wg=(F, H), wu=(F, H), wd=(H, F)).items():
+            w[n] = O.q80_quantize(rng.standard_normal(s, dtype=np.float32) * np.float32(0.02))
+        w["attn_norm"] = np.ones(H, np.float32)
+        w["ffn_norm"] = np.ones(H, np.float32)
+        sets.append(w)
+    x = rng.standard_normal((B, H), dtype=np.float32)
+    return lens, sets, x
+
+
+def kv_for_sequence(rng, n):
+    k = rng.standard_normal((n, KVH, HD), dtype=np.float32).astype(np.float16)
+    v = rng.standard_normal((n, KVH, HD), dtype=np.float32).astype(np.float16)
+    return k, v
+
+
+class Layer:
+    """Issues one decode layer step through the C ABI (everything on the decode stream)."""
+
+    def __init__(self, nat, kv, dw, rows):
+        self.nat, self.kv, self.dw, self.rows = nat, kv, dw, rows
+        self.dx = nat.buf(rows * H * 4)
+        self.dq = nat.buf(rows * QH * HD * 4)
+        self.datt = nat.buf(rows * QH * HD * 4)
+        self.dx1 = nat.buf(rows * H * 4)
+        self.dx1n = nat.buf(rows * H * 4)
+        self.dhid = nat.buf(rows * F * 4)
+        self.dout = nat.buf(rows * H * 4)
+        self.dids = nat.buf(rows * 4)
+        self.dpos = nat.buf(rows * 4)
+        self.dlens = nat.buf(rows * 4)
+
+    def enqueue(self, wset):
+        L, ctx, d, r = self.nat.lib, self.nat.ctx, self.dw[wset], self.rows
+        rc = L.m40llm_qkv_rmsnorm_rope_append_async(ctx, self.kv, self.dx.ptr, d["attn_norm"].ptr, 1, EPS, d["wq"].ptr,
+                                                    d["wk"].ptr, d["wv"].ptr, None, None, None, self.dids.ptr,
+                                                    self.dpos.ptr, r, H, QH, THETA, 1.0, 0, self.dq.ptr)
+        assert rc == 0, rc
+        rc = L.m40llm_attention_last_token_f32_gqa_batched_async(ctx, self.kv, self.dids.ptr, self.dlens.ptr, r,
+                                                                 self.dq.ptr, QH, self.datt.ptr)
+        assert rc == 0, rc
+        assert L.m40llm_gemm_f32xf16_gguf_f32_async(ctx, self.datt.ptr, d["wo"].ptr, self.dx1.ptr, r, H, QH * HD, 1) == 0
+        assert L.m40llm_residual_add_f32_async(ctx, self.dx.ptr, self.dx1.ptr, self.dx1.ptr, r * H) == 0
+        assert L.m40llm_rms_norm_f32_weighted_async(ctx, self.dx1.ptr, d["ffn_norm"].ptr, self.dx1n.ptr, r, H, EPS, 1) == 0
+        rc = L.m40llm_ffn_swiglu_q80_f32_async(ctx, self.dx1n.ptr, d["wg"].ptr, d["wu"].ptr, d["wd"].ptr, self.dx1.ptr,
+                                               self.dhid.ptr, self.dout.ptr, r, H, F, 1)
+        assert rc == 0, rc
+
+    def attention_only(self):
+        L = self.nat.lib
+        rc = L.m40llm_attention_last_token_f32_gqa_batched_async(self.nat.ctx, self.kv, self.dids.ptr, self.dlens.ptr,
+                                                                 self.rows, self.dq.ptr, QH, self.datt.ptr)
+        assert rc == 0, rc
+
+    def capture(self, wset):
+        L, ctx = self.nat.lib, self.nat.ctx
+        assert L.m40llm_cuda_graph_begin_capture(ctx, 1) == 0
+        self.enqueue(wset)
+        g = C.c_void_p()
+        assert L.m40llm_cuda_graph_end_capture(ctx, 1, C.byref(g)) == 0 and g.value
+        return g
+
+
+class Events:
+    def __init__(self, nat):
+        self.nat = nat
+        self.e0, self.e1 = C.c_void_p(), C.c_void_p()
+        assert nat.lib.m40llm_cuda_event_create(nat.ctx, C.byref(self.e0)) == 0
+        assert nat.lib.m40llm_cuda_event_create(nat.ctx, C.byref(self.e1)) == 0
+
+    def start(self):
+        assert self.nat.lib.m40llm_cuda_event_record(self.nat.ctx, self.e0, 1) == 0
+
+    def stop_ms(self):
+        assert self.nat.lib.m40llm_cuda_event_record(self.nat.ctx, self.e1, 1) == 0
+        ms = C.c_float()
+        assert self.nat.lib.m40llm_cuda_event_elapsed_sync(self.nat.ctx, self.e0, self.e1, C.byref(ms)) == 0
+        return float(ms.value)
+
+
+def launches(nat):
+    n = C.c_uint64()
+    assert nat.lib.m40llm_context_launch_count(nat.ctx, C.byref(n)) == 0
+    return int(n.value)
+
+
+def cpu_layer_sample(O, sets, x, lens, seqs, threads=None):
+    """Oracle layer for a few sequences of the batch; returns (seconds, tokens)."""
+    if threads:
+        O.set_num_threads(threads)
+    cfg = O.LayerCfg(H, QH, KVH, HD, F, 1, 0, EPS, THETA, 1.0)
+    rng = np.random.default_rng(1234)
+    caches = []
+    for b in seqs:
+        n = int(lens[b])
+        k, v = kv_for_sequence(rng, n)
+        K = np.zeros((n + 1, KVH, HD), np.float16)
+        V = np.zeros((n + 1, KVH, HD), np.float16)
+        K[:n], V[:n] = k, v
+        caches.append((K, V))
+    t0 = time.perf_counter()
+    for i, b in enumerate(seqs):
+        O.decode_layer(cfg, x[b], sets[0], caches[i][0], caches[i][1], int(lens[b]))
+    return time.perf_counter() - t0, len(seqs)
+
+
+def run_reference_arm(args, rank, world):
+    """`--impl reference`: the reference's CPU path is Rust and cannot be built here (no cargo/rustc, no network),
+    so the timed stand-in is the oracle port of that math, on all host threads. Rank 0 only."""
+    if rank != 0:
+        return
+    from oracle import oracle as O
+    lens, sets, x = make_inputs(O, 0)
+    cores = O.num_threads()
+    seqs = [0]
+    times = []
+    for i in range(args.warmup + args.steps):
+        dt, n = cpu_layer_sample(O, sets, x, lens, seqs)
+        if i >= args.warmup:
+            times.append(dt / n)
+    per_tok = float(np.mean(times))
+    val = 1.0 / per_tok
+    line = {
+        "impl": "reference", "metric": "decode_layer_tokens_per_s", "value": val, "unit": "tokens/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": per_tok * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f16 storage / q8_0 / f32 compute", "data": "synthetic",
+        "config": {"workload": "llama3-8b-shaped decode layer, batch 32 varlen [512,8192], q8_0 FFN",
+                   "hidden": H, "q_heads": QH, "kv_heads": KVH, "head_dim": HD, "ffn": F, "batch": B},
+        "cpu_baseline": {"value": val, "unit": "tokens/s", "cores": cores, "kind": "port",
+                         "sample": f"oracle layer for 1 of the {B} sequences per step (context {int(lens[0])}), OpenMP over rows/heads"},
+        "e2e": {"value": val, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="b200")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.impl == "reference":
+        run_reference_arm(args, rank, world)
+        return
+
+    import torch
+    import helpers
+    from oracle import oracle as O
+
+    torch.cuda.set_device(local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    pkg = helpers.load_package()
+    nat = helpers.Native(pkg.native.lib(), device=local_rank)
+    L, ctx = nat.lib, nat.ctx
+
+    lens, sets, x = make_inputs(O, rank)
+    dw = [{n: nat.buf(a) for n, a in w.items()} for w in sets]
+    kv = nat.kv_dense(LMAX + 8, B, KVH, HD)
+    rng = np.random.default_rng(1000 + rank)
+    for b in range(B):
+        k, v = kv_for_sequence(rng, int(lens[b]))
+        nat.kv_fill(kv, b, k, v)
+    layer = Layer(nat, kv, dw, B)
+    ids = np.arange(B, dtype=np.uint32)
+    pos = lens.copy()          # the new token of sequence b sits at position lens[b]
+    att_lens = lens + 1
+    layer.dx.upload(x)
+    layer.dids.upload(ids)
+    layer.dpos.upload(pos)
+    layer.dlens.upload(att_lens)
+
+    # eager warm-up (sizes the scratch arenas), then capture one graph per weight set
+    for w in range(N_WEIGHT_SETS):
+        layer.enqueue(w)
+    nat.sync(1)
+    graphs = [layer.capture(w) for w in range(N_WEIGHT_SETS)]
+    ev = Events(nat)
+
+    def barrier():
+        nat.sync()
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+
+    # ---------------- device-resident timing
+    for i in range(args.warmup):
+        assert L.m40llm_cuda_graph_launch(ctx, graphs[i % N_WEIGHT_SETS], 1) == 0
+    barrier()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    n0 = launches(nat)
+    ev.start()
+    for i in range(args.steps):
+        assert L.m40llm_cuda_graph_launch(ctx, graphs[i % N_WEIGHT_SETS], 1) == 0
+    ms_total = ev.stop_ms()
+    barrier()
+    clocks = sampler.stop()
+    # kernels per graph replay = kernels enqueued by one eager step
+    n1 = launches(nat)
+    layer.enqueue(0)
+    nat.sync(1)
+    per_step_launches = launches(nat) - n1
+    ms_step = ms_total / args.steps
+
+    # ---------------- dominant kernel alone (batched decode attention), CUDA events on its stream
+    for _ in range(3):
+        layer.attention_only()
+    nat.sync(1)
+    # between timed launches the other sequences' KV (570 MB per pass) evicts any reuse: input > L2
+    ev.start()
+    reps = max(10, args.steps)
+    for _ in range(reps):
+        layer.attention_only()
+    attn_ms = ev.stop_ms() / reps
+    attn_bytes = attention_bytes(att_lens)
+    peak, peak_kind = measured_peak_gbs()
+    attn_gbs = attn_bytes / (attn_ms * 1e-3) / 1e9
+
+    # ---------------- end to end through the ABI with host buffers
+    hx = torch.from_numpy(x).pin_memory()
+    hout = torch.empty((B, H), dtype=torch.float32).pin_memory()
+    hids = torch.from_numpy(ids.astype(np.int32)).pin_memory()
+    hpos = torch.from_numpy(pos.astype(np.int32)).pin_memory()
+    hlens = torch.from_numpy(att_lens.astype(np.int32)).pin_memory()
+    h2d = hx.numel() * 4 + 3 * B * 4
+    d2h = hout.numel() * 4
+
+    def e2e_step(i):
+        assert L.m40llm_memcpy_h2d(ctx, layer.dx.ptr, hx.data_ptr(), hx.numel() * 4) == 0
+        assert L.m40llm_memcpy_h2d(ctx, layer.dids.ptr, hids.data_ptr(), B * 4) == 0
+        assert L.m40llm_memcpy_h2d(ctx, layer.dpos.ptr, hpos.data_ptr(), B * 4) == 0
+        assert L.m40llm_memcpy_h2d(ctx, layer.dlens.ptr, hlens.data_ptr(), B * 4) == 0
+        assert L.m40llm_cuda_graph_launch(ctx, graphs[i % N_WEIGHT_SETS], 1) == 0
+        assert L.m40llm_stream_synchronize(ctx, 1) == 0
+        assert L.m40llm_memcpy_d2h(ctx, hout.data_ptr(), layer.dout.ptr, d2h) == 0
+
+    for i in range(args.warmup):
+        e2e_step(i)
+    barrier()
+    t0 = time.perf_counter()
+    for i in range(args.steps):
+        e2e_step(i)
+    nat.sync()
+    e2e_s = (time.perf_counter() - t0) / args.steps
+
+    if dist is not None:
+        t = torch.tensor([ms_step, e2e_s], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_step, e2e_s = float(t[0]), float(t[1])
+
+    # ---------------- batch-1 step (the 70%-of-HBM target is stated on batch 1): own graph, rows = 1
+    extra = {}
+    if rank == 0:
+        l1 = Layer(nat, kv, dw, 1)
+        l1.dx.upload(x[:1])
+        longest = int(np.argmax(lens))
+        l1.dids.upload(np.array([longest], np.uint32))
+        l1.dpos.upload(np.array([lens[longest]], np.uint32))
+        l1.dlens.upload(np.array([lens[longest] + 1], np.uint32))
+        for w in range(N_WEIGHT_SETS):
+            l1.enqueue(w)
+        nat.sync(1)
+        g1 = [l1.capture(w) for w in range(N_WEIGHT_SETS)]
+        for i in range(5):
+            assert L.m40llm_cuda_graph_launch(ctx, g1[i % N_WEIGHT_SETS], 1) == 0
+        nat.sync(1)
+        ev.start()
+        for i in range(args.steps):
+            assert L.m40llm_cuda_graph_launch(ctx, g1[i % N_WEIGHT_SETS], 1) == 0
+        ms1 = ev.stop_ms() / args.steps
+        b1 = step_bytes([lens[longest] + 1])
+        extra["batch1"] = {"tokens_per_s": 1e3 / ms1, "ms_per_step": ms1, "context": int(lens[longest]) + 1,
+                           "algorithmic_bytes": b1, "achieved_gbs": b1 / (ms1 * 1e-3) / 1e9,
+                           "frac_of_hbm_peak": b1 / (ms1 * 1e-3) / 1e9 / peak, "peak_kind": peak_kind}
+
+    # ---------------- CPU baseline (rank 0, N = 1): the oracle on a bounded sample of this batch
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        seqs = [int(np.argmin(lens))]
+        dt, n = cpu_layer_sample(O, sets, x, lens, seqs)
+        cpu = {"value": n / dt, "unit": "tokens/s", "cores": O.num_threads(), "kind": "port",
+               "sample": f"oracle layer for {n} of the {B} sequences (context {int(lens[seqs[0]])}), {dt:.1f} s of wall time"}
+
+    if rank == 0:
+        sb = step_bytes(att_lens)
+        line = {
+            "metric": "decode_layer_tokens_per_s", "value": world * B / (ms_step * 1e-3), "unit": "tokens/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f16 storage / q8_0 / f32 compute", "data": "synthetic",
+            "config": {"workload": "llama3-8b-shaped decode layer, batch 32 varlen [512,8192], q8_0 FFN (BASELINE configs[2])",
+                       "hidden": H, "q_heads": QH, "kv_heads": KVH, "head_dim": HD, "ffn": F, "batch_per_gpu": B,
+                       "context_sum": int(att_lens.sum()), "parallelism": f"independent sequences x{world}",
+                       "l2": f"inputs larger than L2: {sb / 1e6:.0f} MB per step, {N_WEIGHT_SETS} weight sets rotated"},
+            "step_algorithmic_bytes": sb, "step_achieved_gbs": sb / (ms_step * 1e-3) / 1e9,
+            "step_frac_of_hbm_peak": sb / (ms_step * 1e-3) / 1e9 / peak,
+            "roofline": {"kernel": "batched decode attention (attention + split merge)", "bound": "hbm",
+                         "achieved": attn_gbs, "peak": peak, "unit": "GB/s", "frac": attn_gbs / peak,
+                         "peak_kind": f"of {peak_kind}", "algorithmic_bytes": attn_bytes, "ms_per_launch": attn_ms,
+                         "traffic": None if NCU_TRAFFIC_RATIO is None else NCU_TRAFFIC_RATIO * attn_bytes},
+            "e2e": {"value": world * B / e2e_s, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+            "gpu_launches": per_step_launches * args.steps,
+            "clocks": clocks,
+        }
+        line.update(extra)
+        if cpu is not None:
+            line["cpu_baseline"] = cpu
+        print(json.dumps(line), flush=True)
+    for g in graphs:
+        L.m40llm_cuda_graph_destroy(g)
+    L.m40llm_kvcache_destroy(kv)
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -354,6 +354,7 @@ static int batched_impl(M40llmCudaContext* ctx, const M40llmKVCache* kv, const u
         if (cudaMemcpy(&st, ctx->d_status, sizeof(uint32_t), cudaMemcpyDeviceToHost) != cudaSuccess) return -7;
         if (st & 1u) {
             cudaMemset(ctx->d_status, 0, sizeof(uint32_t));
+            cudaStreamSynchronize(cudaStreamLegacy);
             return -8;
         }
     }

@@ -123,11 +123,17 @@ __device__ __forceinline__ float warp_max(float v) {
     return v;
 }
 
-// RoPE angle exactly as the reference computes it (cuda/kernels.cu:7322-7327).
+// RoPE angle: theta = float(pos)*freq_scale * powf(base, -2 i / hd)  (cuda/kernels.cu:7322-7327,
+// CPU form tests/rmsnorm_rope.rs:43-76). At positions of 1e4..1e5 the angle reaches 1e4..1e5 rad, so one ulp of
+// the inverse frequency moves sin/cos by ~1e-3. The host libm's powf is correctly rounded while the device powf
+// is only good to a few ulp, so the inverse frequency is evaluated in double and rounded once: this makes the
+// device angle equal to the host reference's angle instead of merely close to it.
 __device__ __forceinline__ void rope_cs(uint32_t pos, uint32_t pair, uint32_t head_dim, float freq_base,
                                         float freq_scale, float* c, float* s) {
     const float p = static_cast<float>(pos) * freq_scale;
-    const float theta = p * powf(freq_base, -2.0f * static_cast<float>(pair) / static_cast<float>(head_dim));
+    const float e = -2.0f * static_cast<float>(pair) / static_cast<float>(head_dim);
+    const float inv_freq = static_cast<float>(pow(static_cast<double>(freq_base), static_cast<double>(e)));
+    const float theta = p * inv_freq;
     *c = cosf(theta);
     *s = sinf(theta);
 }

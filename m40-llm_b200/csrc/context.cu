@@ -80,6 +80,8 @@ M40llmCudaContext* m40llm_create_context(int device_id) {
         cudaMemset(ctx->d_selected_blocks, 0xff, (size_t)ctx->selected_capacity_heads * 64 * sizeof(uint32_t));
         cudaMemset(ctx->d_selected_scores, 0, (size_t)ctx->selected_capacity_heads * 64 * sizeof(float));
         ok = m40_ensure_scratch(ctx, 0, (size_t)32 << 20) != nullptr && m40_ensure_scratch(ctx, 1, (size_t)32 << 20) != nullptr;
+        // the memsets above ran on the legacy stream, which the non-blocking streams do not order against
+        ok = ok && cudaStreamSynchronize(cudaStreamLegacy) == cudaSuccess;
     }
     if (!ok) {
         cudaGetLastError();
@@ -145,7 +147,11 @@ int m40llm_device_free(M40llmCudaContext* ctx, void* ptr) {
 int m40llm_memcpy_h2d(M40llmCudaContext* ctx, void* dst_device, const void* src_host, size_t bytes) {
     if (!ctx || !dst_device || !src_host) return -1;
     if (m40_ensure_device(ctx) != 0) return -3;
-    return cudaMemcpy(dst_device, src_host, bytes, cudaMemcpyHostToDevice) == cudaSuccess ? 0 : -2;
+    if (cudaMemcpy(dst_device, src_host, bytes, cudaMemcpyHostToDevice) != cudaSuccess) return -2;
+    // A copy from pageable memory returns once the data is staged, possibly before the DMA lands. The
+    // context's streams are non-blocking (they do not order against the legacy stream the copy ran on),
+    // so wait here: a kernel enqueued right after this call must see the bytes.
+    return cudaStreamSynchronize(cudaStreamLegacy) == cudaSuccess ? 0 : -2;
 }
 
 int m40llm_memcpy_d2h(M40llmCudaContext* ctx, void* dst_host, const void* src_device, size_t bytes) {
@@ -181,7 +187,8 @@ int m40llm_upload_weights(M40llmCudaContext* ctx, const void* host_ptr, size_t n
         cudaGetLastError();
         return -2;
     }
-    if (cudaMemcpy(d, host_ptr, num_bytes, cudaMemcpyHostToDevice) != cudaSuccess) {
+    if (cudaMemcpy(d, host_ptr, num_bytes, cudaMemcpyHostToDevice) != cudaSuccess ||
+        cudaStreamSynchronize(cudaStreamLegacy) != cudaSuccess) {
         cudaGetLastError();
         cudaFree(d);
         return -3;
@@ -343,7 +350,10 @@ int m40llm_context_take_device_status(M40llmCudaContext* ctx, uint32_t* out_stat
     if (m40_ensure_device(ctx) != 0) return -2;
     if (cudaStreamSynchronize(ctx->decode_stream) != cudaSuccess) return -3;
     if (cudaMemcpy(out_status, ctx->d_status, sizeof(uint32_t), cudaMemcpyDeviceToHost) != cudaSuccess) return -4;
-    if (*out_status != 0) cudaMemset(ctx->d_status, 0, sizeof(uint32_t));
+    if (*out_status != 0) {
+        cudaMemset(ctx->d_status, 0, sizeof(uint32_t));
+        cudaStreamSynchronize(cudaStreamLegacy);
+    }
     return 0;
 }
 

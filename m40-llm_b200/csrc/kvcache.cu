@@ -134,6 +134,8 @@ M40llmKVCache* m40llm_kvcache_create(M40llmCudaContext* ctx, uint32_t max_seq_le
     bool ok = dev_alloc_zero(&kv->d_k, elems ? elems : 1);
     ok = ok && dev_alloc_zero(&kv->d_v, elems ? elems : 1);
     ok = ok && dev_alloc_zero(&kv->d_seq_map, max_batch_size ? max_batch_size : 1);
+    // zero-fill ran on the legacy stream; the context's non-blocking streams do not order against it
+    ok = ok && cudaStreamSynchronize(cudaStreamLegacy) == cudaSuccess;
     if (!ok) {
         m40llm_kvcache_destroy(kv);
         return nullptr;
@@ -175,6 +177,8 @@ M40llmKVCache* m40llm_kvcache_create_compressed(M40llmCudaContext* ctx, uint32_t
     ok = ok && dev_alloc_zero(&kv->d_q4_v, vectors * (head_dim / 2));
     ok = ok && dev_alloc_zero(&kv->d_q4_scale, vectors);
     ok = ok && dev_alloc_zero(&kv->d_seq_map, max_batch_size ? max_batch_size : 1);
+    // zero-fill ran on the legacy stream; the context's non-blocking streams do not order against it
+    ok = ok && cudaStreamSynchronize(cudaStreamLegacy) == cudaSuccess;
     if (!ok) {
         m40llm_kvcache_destroy(kv);
         return nullptr;

@@ -19,6 +19,7 @@ import sys
 import numpy as np
 
 HERE = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
 sys.path.insert(0, os.path.dirname(HERE))
 sys.path.insert(0, HERE)
 import cases  # noqa: E402
@@ -103,7 +104,7 @@ def main():
         assert L.m40llm_attention_last_token_f32_gqa_async(ctx, kv, 0, dq.ptr, qh, Ln, do.ptr) == 0
         nat.sync(1)
         out[name + "/out"] = do.download(np.float32, q.shape)
-        if args.lib == "mine" or hd == 64:  # the reference's block-select-over-dense kernel is head_dim 64 only
+        if hd == 64:  # the reference's block-select-over-dense kernel is head_dim 64 only
             assert L.m40llm_attention_last_token_f32_gqa_block_select_exact_async(ctx, kv, 0, dq.ptr, qh, Ln, 16, 8, 4, do.ptr) == 0
             nat.sync(1)
             out[name + "/block_select_dense_R16_bs8_top4"] = do.download(np.float32, q.shape)

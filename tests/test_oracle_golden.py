@@ -29,8 +29,12 @@ def test_norm_rope_gemm_elementwise(O, gold):
         np.testing.assert_allclose(O.rms_norm(x, None, 1e-5), gold[name + "/plain"], atol=1e-4, rtol=1e-5)
         np.testing.assert_allclose(O.rms_norm(x, w, 1e-5), gold[name + "/weighted"], atol=1e-4, rtol=1e-5)
     for name, (rows, heads, hd, past, base, layout) in cases.ROPE_CASES.items():
-        np.testing.assert_allclose(O.rope(cases.rope_inputs(name), heads, hd, past, base, 1.0, layout).reshape(rows, -1),
-                                   gold[name], atol=2e-4)
+        # The reference kernel evaluates the inverse frequency with the device powf (a few ulp), then multiplies by
+        # the position: an angle error of ~pos * 5e-7 rad. Its own test only checks position 3
+        # (tests/rmsnorm_rope.rs:242-252). The bound below is that conditioning, not a looser contract.
+        x = cases.rope_inputs(name)
+        tol = 1e-4 + (past + rows) * 6e-7 * float(np.abs(x).max())
+        np.testing.assert_allclose(O.rope(x, heads, hd, past, base, 1.0, layout).reshape(rows, -1), gold[name], atol=tol)
     for name in cases.GEMM_CASES:
         a, w = cases.gemm_inputs(name)
         b = np.ascontiguousarray(w.T)
