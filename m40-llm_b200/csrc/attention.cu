@@ -9,6 +9,8 @@
 // Semantics: softmax(q.K^T / sqrt(hd)) V over tokens [0, seq_len) with f16 storage and
 // f32 arithmetic, equal to the reference's three-pass host form (src/cuda.rs:4561-4628)
 // up to f32 summation order.
+#include <stdlib.h>
+
 #include "attention.cuh"
 #include "common.cuh"
 
@@ -189,16 +191,30 @@ int launch_generic(M40llmCudaContext* ctx, const DenseAttnArgs& a, uint32_t rows
 }  // namespace
 
 // ------------------------------------------------------------------ internal API
-uint32_t m40_attn_pick_splits(const M40llmCudaContext* ctx, uint32_t rows, uint32_t kv_heads, uint32_t max_tokens) {
-    // Aim for ~4 CTAs per SM; never make a split shorter than 128 tokens.
-    const uint32_t base = rows * kv_heads;
-    const uint32_t target = (uint32_t)ctx->sm_count * 4u;
-    uint32_t splits = base >= target ? 1u : (target + base - 1u) / base;
-    const uint32_t max_splits = (max_tokens + 127u) / 128u;
-    if (splits > max_splits) splits = max_splits;
-    if (splits < 1u) splits = 1u;
-    if (splits > 256u) splits = 256u;
-    return splits;
+void m40_attn_pick_chunk(const M40llmCudaContext* ctx, uint32_t rows, uint32_t kv_heads, uint32_t max_tokens,
+                         uint32_t* chunk, uint32_t* splits) {
+    // Aim for ~4 CTAs per SM over the whole launch. Chunks are fixed-size so that variable-length batches
+    // produce CTAs of equal cost (CTAs past a row's length exit at once); never shorter than 128 tokens.
+    static int min_chunk_env = -1;
+    if (min_chunk_env < 0) {
+        const char* e = getenv("M40LLM_ATTN_MIN_CHUNK");
+        min_chunk_env = e ? atoi(e) : 0;
+        if (min_chunk_env < 64) min_chunk_env = 128;
+    }
+    const uint64_t work = (uint64_t)rows * kv_heads * max_tokens;
+    const uint64_t target = (uint64_t)ctx->sm_count * 4u;
+    uint64_t c = (work + target - 1) / target;
+    if (c < (uint64_t)min_chunk_env) c = (uint64_t)min_chunk_env;
+    if (c > 1024) c = 1024;
+    c = (c + 63) & ~(uint64_t)63;
+    uint32_t s = (uint32_t)((max_tokens + c - 1) / c);
+    if (s > 128u) {
+        c = ((max_tokens + 127u) / 128u + 63u) & ~(uint64_t)63;
+        s = (uint32_t)((max_tokens + c - 1) / c);
+    }
+    if (s < 1u) s = 1u;
+    *chunk = (uint32_t)c;
+    *splits = s;
 }
 
 int m40_attention_dense(M40llmCudaContext* ctx, const M40llmKVCache* kv, const M40DenseAttnCall& c) {
@@ -223,8 +239,10 @@ int m40_attention_dense(M40llmCudaContext* ctx, const M40llmKVCache* kv, const M
     a.hd = kv->head_dim;
     a.inv_sqrt = attn_inv_sqrt(kv->head_dim);
     a.write_partials = c.partials_out ? 1u : 0u;
-    const uint32_t bound = c.token_bound ? c.token_bound : kv->max_seq_len;
-    a.splits = m40_attn_pick_splits(ctx, c.rows, kv->num_heads, bound);
+    uint32_t bound = c.token_bound ? c.token_bound : kv->max_seq_len;
+    if (c.range_mode && c.tok_end - c.tok_begin < bound) bound = c.tok_end - c.tok_begin;
+    if (bound == 0) bound = 1;
+    m40_attn_pick_chunk(ctx, c.rows, kv->num_heads, bound, &a.chunk, &a.splits);
     if (a.splits > 1 || c.partials_out) {
         const size_t n = (size_t)c.rows * c.q_heads * a.splits;
         float* scratch = (float*)m40_ensure_scratch(ctx, 1, n * (2 + (size_t)a.hd) * sizeof(float));

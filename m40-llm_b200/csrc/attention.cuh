@@ -19,6 +19,7 @@ struct DenseAttnArgs {
     uint32_t tok_begin, tok_end;  // absolute token range when range_mode != 0
     uint32_t range_mode;
     uint32_t max_seq_len, max_batch, kv_heads, q_heads, hd, splits;
+    uint32_t chunk;           // tokens per split (multiple of 64); split s covers [begin + s*chunk, +chunk)
     uint32_t write_partials;  // 1: always write (m,l,o) partials
     float inv_sqrt;
 };
@@ -40,7 +41,9 @@ struct M40DenseAttnCall {
     float* part_o;
 };
 
-uint32_t m40_attn_pick_splits(const M40llmCudaContext* ctx, uint32_t rows, uint32_t kv_heads, uint32_t max_tokens);
+// Chooses the tokens-per-CTA chunk (multiple of 64) and the number of splits covering `max_tokens`.
+void m40_attn_pick_chunk(const M40llmCudaContext* ctx, uint32_t rows, uint32_t kv_heads, uint32_t max_tokens,
+                         uint32_t* chunk, uint32_t* splits);
 int m40_attention_dense(M40llmCudaContext* ctx, const M40llmKVCache* kv, const M40DenseAttnCall& c);
 int m40_attention_merge(M40llmCudaContext* ctx, const float* m, const float* l, const float* o, uint32_t parts,
                         uint32_t q_heads, uint32_t hd, float* out);
@@ -69,12 +72,9 @@ __device__ __forceinline__ bool attn_resolve_row(const DenseAttnArgs& a, uint32_
         e = a.tok_end < len ? a.tok_end : len;
         if (b > e) b = e;
     }
-    const uint32_t n = e - b;
-    uint32_t per = (n + a.splits - 1) / a.splits;
-    per = (per + 63u) & ~63u;  // whole 64-token tiles per split
-    const uint32_t sb = b + split * per;
-    uint32_t se = sb + per;
-    if (se > e) se = e;
+    const uint32_t sb = b + split * a.chunk;
+    uint32_t se = sb + a.chunk;
+    if (se > e || se < sb) se = e;
     *seq = sid;
     *t0 = sb < e ? sb : e;
     *t1 = se > *t0 ? se : *t0;

@@ -1,3 +1,308 @@
-// Tiled decode attention for head_dim 64/128 (placeholder until the tensor-core kernel lands).
+// Tiled decode attention for head_dim 64 and 128 (the shapes of every model configuration).
+//
+// One CTA (4 warps) owns (row, kv head, token chunk). It streams its K and V rows once through a
+// multi-stage cp.async pipeline into XOR-swizzled shared memory (64-token tiles, 16-byte pieces,
+// fully coalesced: in the head-major cache a kv head's rows are contiguous). All q heads of the
+// kv head's group share that one read. The kernel is HBM-bound by design; the arithmetic runs on
+// the tensor cores so that it stays out of the way of the memory pipeline:
+//   S = Q K^T   mma.sync m16n8k16, rows = the group's q heads (padded to 16), q split into
+//               f16 hi + lo parts so that scores keep f32-level accuracy;
+//   softmax     online, base 2, per warp over its 16 tokens of the tile;
+//   O += P V    mma.sync with P rounded to f16 (relative error <= 2^-11 per weight).
+// Each warp keeps its own (m, l, O) and the four are merged once at the end, so the only CTA-wide
+// synchronisation per tile is the pipeline hand-over.
 #include "attention.cuh"
-int m40_attention_dense_tiled(M40llmCudaContext*, const DenseAttnArgs&, uint32_t) { return 1; }
+
+namespace {
+
+constexpr int TILE = 64;
+constexpr float LOG2E = 1.4426950408889634f;
+constexpr float LN2 = 0.6931471805599453f;
+
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
+    const uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(s), "l"(gmem));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N)); }
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* smem) {
+    const uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* smem) {
+    const uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+// D (f32, m16n8) += A (f16, m16k16) * B (f16, k16n8)
+__device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ uint32_t pack_h2(float lo, float hi) {
+    const __half2 h = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&h);
+}
+// f32 pair -> (hi, lo) f16 pairs with hi + lo == the f32 value to ~2^-22 relative
+__device__ __forceinline__ void split_h2(float x, float y, uint32_t* hi, uint32_t* lo) {
+    const __half hx = __float2half_rn(x), hy = __float2half_rn(y);
+    const __half2 h = __halves2half2(hx, hy);
+    *hi = *reinterpret_cast<const uint32_t*>(&h);
+    *lo = pack_h2(x - __half2float(hx), y - __half2float(hy));
+}
+
+template <int HD>
+struct TiledCfg {
+    static constexpr int CHUNKS = HD / 8;                  // 16-byte pieces per row
+    static constexpr int TILE_BYTES = TILE * HD * 2;       // one K (or V) tile
+    static constexpr int STAGES = HD == 128 ? 3 : 4;
+    static constexpr int SMEM = STAGES * 2 * TILE_BYTES;   // 96 KB (hd 128) / 64 KB (hd 64)
+};
+
+// G_HI: the group has more than 8 q heads (rows 8..15 of the MMA are live).
+template <int HD, bool G_HI>
+__global__ void __launch_bounds__(128, 2) attn_decode_tiled_kernel(DenseAttnArgs a) {
+    using Cfg = TiledCfg<HD>;
+    constexpr int KS = HD / 16;   // k-steps of Q K^T
+    constexpr int NT = HD / 8;    // n8 tiles of the output
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    __half* sK = reinterpret_cast<__half*>(smem_raw);
+    __half* sV = reinterpret_cast<__half*>(smem_raw + Cfg::STAGES * Cfg::TILE_BYTES);
+
+    const uint32_t split = blockIdx.x, kvh = blockIdx.y, row = blockIdx.z;
+    const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
+    const uint32_t g = lane >> 2, t4 = lane & 3u;
+    const uint32_t G = a.q_heads / a.kv_heads;
+    uint32_t seq = 0, t0 = 0, t1 = 0;
+    if (!attn_resolve_row(a, row, split, &seq, &t0, &t1)) return;
+    const bool partial = a.write_partials || a.splits > 1;
+    if (t0 >= t1) {  // nothing in this chunk: an empty partial (l = 0) that the merge ignores
+        if (partial) {
+            for (uint32_t i = tid; i < G; i += blockDim.x) {
+                const size_t pi = ((size_t)row * a.q_heads + kvh * G + i) * a.splits + split;
+                a.part_m[pi] = -INFINITY;
+                a.part_l[pi] = 0.0f;
+            }
+        }
+        return;
+    }
+    const __half* Kh = a.K + kv_row_offset(seq, kvh, 0, a.kv_heads, a.max_seq_len, HD);
+    const __half* Vh = a.V + kv_row_offset(seq, kvh, 0, a.kv_heads, a.max_seq_len, HD);
+
+    // ---- Q fragments (A operand), pre-scaled by 1/sqrt(hd) * log2(e), split into hi + lo f16
+    uint32_t qhi[KS][G_HI ? 4 : 2], qlo[KS][G_HI ? 4 : 2];
+    {
+        const float qs = a.inv_sqrt * LOG2E;
+        const float* q0 = a.q + ((size_t)row * a.q_heads + kvh * G + g) * HD;
+        const float* q1 = q0 + (size_t)8 * HD;
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks) {
+            const int k0 = ks * 16 + 2 * t4;
+            float2 x0 = make_float2(0.f, 0.f), x2 = x0, x1 = x0, x3 = x0;
+            if (g < G) {
+                x0 = *reinterpret_cast<const float2*>(q0 + k0);
+                x2 = *reinterpret_cast<const float2*>(q0 + k0 + 8);
+            }
+            split_h2(x0.x * qs, x0.y * qs, &qhi[ks][0], &qlo[ks][0]);
+            split_h2(x2.x * qs, x2.y * qs, &qhi[ks][G_HI ? 2 : 1], &qlo[ks][G_HI ? 2 : 1]);
+            if (G_HI) {
+                if (g + 8 < G) {
+                    x1 = *reinterpret_cast<const float2*>(q1 + k0);
+                    x3 = *reinterpret_cast<const float2*>(q1 + k0 + 8);
+                }
+                split_h2(x1.x * qs, x1.y * qs, &qhi[ks][1], &qlo[ks][1]);
+                split_h2(x3.x * qs, x3.y * qs, &qhi[ks][3], &qlo[ks][3]);
+            }
+        }
+    }
+
+    float o[NT][4];
+#pragma unroll
+    for (int n = 0; n < NT; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.0f;
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};
+
+    const uint32_t n_tiles = (t1 - t0 + TILE - 1) / TILE;
+    auto load_tile = [&](uint32_t tile, uint32_t stage) {
+        const uint32_t base = t0 + tile * TILE;
+        __half* dK = sK + (size_t)stage * TILE * HD;
+        __half* dV = sV + (size_t)stage * TILE * HD;
+#pragma unroll
+        for (int c = 0; c < (TILE * Cfg::CHUNKS) / 128; ++c) {
+            const uint32_t idx = c * 128 + tid;
+            const uint32_t r = idx / Cfg::CHUNKS, ch = idx % Cfg::CHUNKS;
+            uint32_t tok = base + r;
+            if (tok >= t1) tok = t1 - 1;  // rows past the end are masked later; keep the read in range
+            const size_t src = (size_t)tok * HD + ch * 8;
+            const uint32_t dst = r * HD + ((ch ^ (r & 7u)) * 8);
+            cp_async16(dK + dst, Kh + src);
+            cp_async16(dV + dst, Vh + src);
+        }
+    };
+#pragma unroll
+    for (int s = 0; s < Cfg::STAGES - 1; ++s) {
+        if ((uint32_t)s < n_tiles) load_tile(s, s);
+        cp_async_commit();
+    }
+
+    for (uint32_t tile = 0; tile < n_tiles; ++tile) {
+        cp_async_wait<Cfg::STAGES - 2>();
+        __syncthreads();
+        {
+            const uint32_t nxt = tile + Cfg::STAGES - 1;
+            if (nxt < n_tiles) load_tile(nxt, nxt % Cfg::STAGES);
+            cp_async_commit();
+        }
+        const uint32_t stage = tile % Cfg::STAGES;
+        const __half* tK = sK + (size_t)stage * TILE * HD;
+        const __half* tV = sV + (size_t)stage * TILE * HD;
+
+        // ---- S = Q K^T for this warp's 16 tokens
+        float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
+        {
+            const uint32_t j = lane >> 3;  // which 8x8 matrix this lane addresses
+            const uint32_t r = warp * 16 + (j >> 1) * 8 + (lane & 7u);
+#pragma unroll
+            for (int ks = 0; ks < KS; ++ks) {
+                const uint32_t ch = ks * 2 + (j & 1u);
+                uint32_t b[4];
+                ldmatrix_x4(b, tK + r * HD + ((ch ^ (r & 7u)) * 8));
+                const uint32_t a1h = G_HI ? qhi[ks][1] : 0u, a3h = G_HI ? qhi[ks][3] : 0u;
+                const uint32_t a1l = G_HI ? qlo[ks][1] : 0u, a3l = G_HI ? qlo[ks][3] : 0u;
+                const uint32_t a2h = qhi[ks][G_HI ? 2 : 1], a2l = qlo[ks][G_HI ? 2 : 1];
+                mma16816(s0, qhi[ks][0], a1h, a2h, a3h, b[0], b[1]);
+                mma16816(s0, qlo[ks][0], a1l, a2l, a3l, b[0], b[1]);
+                mma16816(s1, qhi[ks][0], a1h, a2h, a3h, b[2], b[3]);
+                mma16816(s1, qlo[ks][0], a1l, a2l, a3l, b[2], b[3]);
+            }
+        }
+        // ---- mask tokens past the end, online softmax (base 2)
+        const uint32_t tok0 = t0 + tile * TILE + warp * 16 + 2 * t4;
+        if (tok0 >= t1) { s0[0] = -INFINITY; s0[2] = -INFINITY; }
+        if (tok0 + 1 >= t1) { s0[1] = -INFINITY; s0[3] = -INFINITY; }
+        if (tok0 + 8 >= t1) { s1[0] = -INFINITY; s1[2] = -INFINITY; }
+        if (tok0 + 9 >= t1) { s1[1] = -INFINITY; s1[3] = -INFINITY; }
+        uint32_t pa[4];
+#pragma unroll
+        for (int h = 0; h < (G_HI ? 2 : 1); ++h) {
+            float mx = fmaxf(fmaxf(s0[2 * h], s0[2 * h + 1]), fmaxf(s1[2 * h], s1[2 * h + 1]));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+            const float m_new = fmaxf(m_run[h], mx);
+            const float m_use = m_new == -INFINITY ? 0.0f : m_new;
+            const float corr = fast_exp2(m_run[h] - m_use);
+            const float p00 = fast_exp2(s0[2 * h] - m_use), p01 = fast_exp2(s0[2 * h + 1] - m_use);
+            const float p10 = fast_exp2(s1[2 * h] - m_use), p11 = fast_exp2(s1[2 * h + 1] - m_use);
+            float rs = (p00 + p01) + (p10 + p11);
+            rs += __shfl_xor_sync(0xffffffffu, rs, 1);
+            rs += __shfl_xor_sync(0xffffffffu, rs, 2);
+            l_run[h] = l_run[h] * corr + rs;
+            m_run[h] = m_new;
+#pragma unroll
+            for (int n = 0; n < NT; ++n) {
+                o[n][2 * h] *= corr;
+                o[n][2 * h + 1] *= corr;
+            }
+            pa[h] = pack_h2(p00, p01);       // A[row g (+8h)][k = 2t, 2t+1]
+            pa[2 + h] = pack_h2(p10, p11);   // A[row g (+8h)][k = 8+2t, 9+2t]
+        }
+        if (!G_HI) { pa[1] = 0u; pa[3] = 0u; }
+        // ---- O += P V
+        {
+            const uint32_t j = lane >> 3;
+            const uint32_t r = warp * 16 + (j & 1u) * 8 + (lane & 7u);
+#pragma unroll
+            for (int nd = 0; nd < HD / 16; ++nd) {
+                const uint32_t ch = nd * 2 + (j >> 1);
+                uint32_t b[4];
+                ldmatrix_x4_trans(b, tV + r * HD + ((ch ^ (r & 7u)) * 8));
+                mma16816(o[2 * nd], pa[0], pa[1], pa[2], pa[3], b[0], b[1]);
+                mma16816(o[2 * nd + 1], pa[0], pa[1], pa[2], pa[3], b[2], b[3]);
+            }
+        }
+    }
+    cp_async_wait<0>();
+    __syncthreads();
+
+    // ---- merge the four warps through shared memory (reusing the pipeline buffers)
+    float* sm_m = reinterpret_cast<float*>(smem_raw);  // [4][16]
+    float* sm_l = sm_m + 64;                           // [4][16]
+    float* sm_o = sm_l + 64;                           // [4][16][HD]
+    if (t4 == 0) {
+        sm_m[warp * 16 + g] = m_run[0];
+        sm_l[warp * 16 + g] = l_run[0];
+        sm_m[warp * 16 + g + 8] = G_HI ? m_run[1] : -INFINITY;
+        sm_l[warp * 16 + g + 8] = G_HI ? l_run[1] : 0.0f;
+    }
+#pragma unroll
+    for (int n = 0; n < NT; ++n) {
+        float* dst = sm_o + ((size_t)warp * 16 + g) * HD + n * 8 + 2 * t4;
+        dst[0] = o[n][0];
+        dst[1] = o[n][1];
+        if (G_HI) {
+            dst[8 * HD] = o[n][2];
+            dst[8 * HD + 1] = o[n][3];
+        }
+    }
+    __syncthreads();
+    for (uint32_t idx = tid; idx < G * HD; idx += blockDim.x) {
+        const uint32_t hh = idx / HD, d = idx % HD;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) M = fmaxf(M, sm_m[w * 16 + hh]);
+        float L = 0.0f, O = 0.0f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const float mw = sm_m[w * 16 + hh];
+            const float e = mw == -INFINITY ? 0.0f : fast_exp2(mw - M);
+            L += sm_l[w * 16 + hh] * e;
+            O += sm_o[((size_t)w * 16 + hh) * HD + d] * e;
+        }
+        const uint32_t head = kvh * G + hh;
+        if (partial) {
+            const size_t pi = ((size_t)row * a.q_heads + head) * a.splits + split;
+            if (d == 0) {
+                a.part_m[pi] = M * LN2;  // back to the natural-log domain the merge kernels use
+                a.part_l[pi] = L;
+            }
+            a.part_o[pi * HD + d] = O;
+        } else {
+            a.out[((size_t)row * a.q_heads + head) * HD + d] = O / (L > 0.0f ? L : 1.0f);
+        }
+    }
+}
+
+template <int HD, bool G_HI>
+int launch(M40llmCudaContext* ctx, const DenseAttnArgs& a, uint32_t rows) {
+    auto kern = attn_decode_tiled_kernel<HD, G_HI>;
+    static unsigned long long configured = 0ull;  // per-device bit: the attribute is per device
+    const unsigned long long bit = 1ull << (ctx->device_id & 63);
+    if (!(configured & bit)) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, TiledCfg<HD>::SMEM) != cudaSuccess)
+            return -4;
+        configured |= bit;
+    }
+    dim3 grid(a.splits, a.kv_heads, rows);
+    kern<<<grid, 128, TiledCfg<HD>::SMEM, ctx->decode_stream>>>(a);
+    M40_COUNT_LAUNCH(ctx);
+    return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+}  // namespace
+
+int m40_attention_dense_tiled(M40llmCudaContext* ctx, const DenseAttnArgs& a, uint32_t rows) {
+    const uint32_t G = a.q_heads / a.kv_heads;
+    if ((a.hd != 64 && a.hd != 128) || G > 16) return 1;
+    if ((((uintptr_t)a.q) & 7u) != 0u) return 1;  // float2 loads of q
+    if (a.hd == 128) return G > 8 ? launch<128, true>(ctx, a, rows) : launch<128, false>(ctx, a, rows);
+    return G > 8 ? launch<64, true>(ctx, a, rows) : launch<64, false>(ctx, a, rows);
+}

@@ -71,7 +71,7 @@ def test_config_shapes(nat, O, qh, kvh, hd, L):
     dq, do, dl = nat.buf(q), nat.buf(q.nbytes), nat.buf(np.array([L], np.uint32))
     assert nat.lib.m40llm_attention_last_token_f32_gqa_seq_len_dev_async(nat.ctx, kv, 0, dq.ptr, qh, dl.ptr, do.ptr) == 0
     nat.sync(1)
-    assert_close(do.download(np.float32, q.shape), got, atol=1e-5, rtol=1e-5, what="seq_len_dev")
+    assert_close(do.download(np.float32, q.shape), got, what="seq_len_dev")
     assert nat.lib.m40llm_attention_last_token_f32_gqa(nat.ctx, kv, 0, dq.ptr, qh, L, do.ptr) == 0
     assert np.array_equal(do.download(np.float32, q.shape), got)
     # split-K: partial triples over token ranges merge to the same output
@@ -119,7 +119,9 @@ def test_batched_varlen(nat, O, qh, kvh, hd, lens):
     assert_close(got, O.attention_gqa_batched(K, V, ids, np.array(lens, np.uint32), q, qh), what="batched")
     for b in range(B):
         one = run_gqa(nat, kv, int(ids[b]), q[b].ravel().copy(), qh, lens[b])
-        assert_close(got[b].ravel(), one, atol=1e-5, rtol=1e-5, what=f"batched row {b} vs single")
+        # the two calls split the tokens into different chunks, so P is rounded to f16 against different running
+        # maxima: equal within the parity tolerance, not bit for bit
+        assert_close(got[b].ravel(), one, what=f"batched row {b} vs single")
     assert nat.lib.m40llm_attention_last_token_f32_gqa_batched(nat.ctx, kv, dids.ptr, dlens.ptr, B, dq.ptr, qh, do.ptr) == 0
     assert np.array_equal(do.download(np.float32, q.shape), got)
     # a row with a zero length or an out-of-range id is rejected (rc -8 in the reference, kernels.cu:4737-4747)
