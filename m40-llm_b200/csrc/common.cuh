@@ -23,10 +23,13 @@ struct M40llmCudaContext {
     cudaEvent_t decode_waits_prefill_event;
     int prefill_priority;
     int decode_priority;
-    // Scratch arenas, one per stream kind so work on the two streams never shares
-    // scratch. Grown (never shrunk) outside of stream capture by ensure_scratch().
-    void* scratch[2];
-    size_t scratch_bytes[2];
+    // Scratch arenas, indexed [stream kind][level]. One set per stream kind so work on the two
+    // streams never shares scratch; level 0 belongs to leaf operations (GEMM partials and
+    // activation copies, attention partials), level 1 to composite operations that call leaf
+    // operations while their own temporaries are live (the fused attention prologue).
+    // Grown (never shrunk) outside of stream capture by m40_ensure_scratch().
+    void* scratch[2][2];
+    size_t scratch_bytes[2][2];
     // Last block selection (u32 [q_heads][64] + f32 scores), for the debug read-back.
     uint32_t* d_selected_blocks;
     float* d_selected_scores;
@@ -107,7 +110,7 @@ static inline cudaStream_t m40_stream(M40llmCudaContext* ctx, uint32_t kind) {
 // arena when needed. Growth frees the old arena after synchronising that stream, so it
 // must not happen during stream capture: callers that may be captured size their needs
 // from static bounds so the arena is already large enough after the first call.
-void* m40_ensure_scratch(M40llmCudaContext* ctx, uint32_t kind, size_t bytes);
+void* m40_ensure_scratch(M40llmCudaContext* ctx, uint32_t kind, size_t bytes, uint32_t level = 0);
 
 #define M40_COUNT_LAUNCH(ctx) ((ctx)->launches++)
 

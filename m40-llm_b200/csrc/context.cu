@@ -6,27 +6,27 @@
 
 #include "common.cuh"
 
-void* m40_ensure_scratch(M40llmCudaContext* ctx, uint32_t kind, size_t bytes) {
-    if (!ctx || kind > 1) return nullptr;
-    if (ctx->scratch[kind] && ctx->scratch_bytes[kind] >= bytes) return ctx->scratch[kind];
+void* m40_ensure_scratch(M40llmCudaContext* ctx, uint32_t kind, size_t bytes, uint32_t level) {
+    if (!ctx || kind > 1 || level > 1) return nullptr;
+    if (ctx->scratch[kind][level] && ctx->scratch_bytes[kind][level] >= bytes) return ctx->scratch[kind][level];
     cudaStream_t s = m40_stream(ctx, kind);
     cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
     if (cudaStreamIsCapturing(s, &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone) return nullptr;
     size_t want = bytes < (size_t)(8u << 20) ? (size_t)(8u << 20) : bytes;
     want = (want + ((size_t)1 << 20) - 1) & ~(((size_t)1 << 20) - 1);
-    if (ctx->scratch[kind]) {
+    if (ctx->scratch[kind][level]) {
         cudaStreamSynchronize(s);
-        cudaFree(ctx->scratch[kind]);
-        ctx->scratch[kind] = nullptr;
-        ctx->scratch_bytes[kind] = 0;
+        cudaFree(ctx->scratch[kind][level]);
+        ctx->scratch[kind][level] = nullptr;
+        ctx->scratch_bytes[kind][level] = 0;
     }
     void* p = nullptr;
     if (cudaMalloc(&p, want) != cudaSuccess) {
         cudaGetLastError();
         return nullptr;
     }
-    ctx->scratch[kind] = p;
-    ctx->scratch_bytes[kind] = want;
+    ctx->scratch[kind][level] = p;
+    ctx->scratch_bytes[kind][level] = want;
     return p;
 }
 
@@ -97,7 +97,8 @@ void m40llm_destroy_context(M40llmCudaContext* ctx) {
     if (ctx->prefill_stream) cudaStreamSynchronize(ctx->prefill_stream);
     if (ctx->decode_stream) cudaStreamSynchronize(ctx->decode_stream);
     for (int k = 0; k < 2; ++k)
-        if (ctx->scratch[k]) cudaFree(ctx->scratch[k]);
+        for (int l = 0; l < 2; ++l)
+            if (ctx->scratch[k][l]) cudaFree(ctx->scratch[k][l]);
     if (ctx->d_status) cudaFree(ctx->d_status);
     if (ctx->d_selected_blocks) cudaFree(ctx->d_selected_blocks);
     if (ctx->d_selected_scores) cudaFree(ctx->d_selected_scores);

@@ -8,6 +8,7 @@
 // covers every row, q head and kv head.
 #include "common.cuh"
 #include "gemm.cuh"
+#include "gemm_tc.cuh"
 #include "kv_append.cuh"
 
 namespace {
@@ -69,9 +70,9 @@ extern "C" int m40llm_qkv_rmsnorm_rope_append_async(M40llmCudaContext* ctx, M40l
     if (!kv->compressed && (!kv->d_k || !kv->d_v)) return -3;
     if (m40_ensure_device(ctx) != 0) return -1;
     const uint32_t hd = kv->head_dim, QD = q_heads * hd, KD = kv->num_heads * hd;
-    // The decode-stream arena is shared with attention partials, which run later on the same stream.
+    // level-1 arena: the projections called below use the level-0 arena for their own temporaries
     const size_t need = (size_t)rows * ((size_t)hidden + 2 * (size_t)KD) * sizeof(float);
-    float* scratch = (float*)m40_ensure_scratch(ctx, 1, need);
+    float* scratch = (float*)m40_ensure_scratch(ctx, 1, need, 1);
     if (!scratch) return -5;
     float* xn = scratch;
     float* kbuf = xn + (size_t)rows * hidden;
@@ -79,15 +80,26 @@ extern "C" int m40llm_qkv_rmsnorm_rope_append_async(M40llmCudaContext* ctx, M40l
     cudaStream_t s = ctx->decode_stream;
     int rc = m40_rms_norm_rows(ctx, d_x_f32, d_norm_w, xn, rows, hidden, eps, norm_w_dtype);
     if (rc != 0) return rc;
-    rc = m40_gemm_dispatch_f16(ctx, s, 1u, xn, (const __half*)d_wq_f16, (float*)d_q_out_f32, (int)rows, (int)QD,
-                               (int)hidden, (const float*)d_bq_f32, nullptr);
-    if (rc != 0) return rc;
-    rc = m40_gemm_dispatch_f16(ctx, s, 1u, xn, (const __half*)d_wk_f16, kbuf, (int)rows, (int)KD, (int)hidden,
-                               (const float*)d_bk_f32, nullptr);
-    if (rc != 0) return rc;
-    rc = m40_gemm_dispatch_f16(ctx, s, 1u, xn, (const __half*)d_wv_f16, vbuf, (int)rows, (int)KD, (int)hidden,
-                               (const float*)d_bv_f32, nullptr);
-    if (rc != 0) return rc;
+    const void* wp[3] = {d_wq_f16, d_wk_f16, d_wv_f16};
+    if ((int)rows >= m40_tc_min_rows() && m40_gemm_tc_supported((int)rows, (int)hidden, 3, wp)) {
+        // one tensor-core launch over Wq | Wk | Wv (they share the normalised activations)
+        const __half* w[3] = {(const __half*)d_wq_f16, (const __half*)d_wk_f16, (const __half*)d_wv_f16};
+        const int n[3] = {(int)QD, (int)KD, (int)KD};
+        float* o[3] = {(float*)d_q_out_f32, kbuf, vbuf};
+        const float* b[3] = {(const float*)d_bq_f32, (const float*)d_bk_f32, (const float*)d_bv_f32};
+        rc = m40_gemm_tc_f16(ctx, s, 1u, xn, (int)rows, (int)hidden, 3, w, n, o, b, nullptr, 0);
+        if (rc != 0) return rc;
+    } else {
+        rc = m40_gemm_f32xf16_gguf(ctx, s, xn, (const __half*)d_wq_f16, (float*)d_q_out_f32, (int)rows, (int)QD,
+                                   (int)hidden, (const float*)d_bq_f32, nullptr);
+        if (rc != 0) return rc;
+        rc = m40_gemm_f32xf16_gguf(ctx, s, xn, (const __half*)d_wk_f16, kbuf, (int)rows, (int)KD, (int)hidden,
+                                   (const float*)d_bk_f32, nullptr);
+        if (rc != 0) return rc;
+        rc = m40_gemm_f32xf16_gguf(ctx, s, xn, (const __half*)d_wv_f16, vbuf, (int)rows, (int)KD, (int)hidden,
+                                   (const float*)d_bv_f32, nullptr);
+        if (rc != 0) return rc;
+    }
     dim3 grid(q_heads + kv->num_heads, rows);
     rope_q_append_kv_rows_kernel<<<grid, 64, 0, s>>>((float*)d_q_out_f32, kbuf, vbuf, *kv, d_seq_ids, d_positions,
                                                      q_heads, freq_base, freq_scale, rope_layout, ctx->d_status);

@@ -4,7 +4,10 @@
 // come from L1/L2. The kernels stream weights with 128-bit no-allocate loads, keep several
 // loads in flight per lane, accumulate in f32 and reduce with warp shuffles.
 #include "common.cuh"
+#include <stdlib.h>
+
 #include "gemm.cuh"
+#include "gemm_tc.cuh"
 
 namespace {
 
@@ -418,11 +421,30 @@ int m40_gate_up_swiglu_f16(M40llmCudaContext* ctx, cudaStream_t s, const float* 
     return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 
-// Chooses the kernel for a GGUF-f16 projection by batch size: CUDA-core GEMV for small M,
-// the tcgen05 tensor-core kernel for M >= M40_TCGEN05_MIN_ROWS when the shape allows it.
+// Rows at which projections switch from the CUDA-core GEMV to the tcgen05 kernel.
+int m40_tc_min_rows() {
+    static int v = -1;
+    if (v < 0) {
+        const char* e = getenv("M40LLM_TC_MIN_ROWS");
+        v = e ? atoi(e) : 2;
+        if (v < 2) v = 2;
+    }
+    return v;
+}
+
+// Chooses the kernel for a GGUF-f16 projection by batch size: CUDA-core GEMV for one row (or when the
+// shape does not fit the tensor-core kernel), the tcgen05 kernel for batched rows.
 int m40_gemm_dispatch_f16(M40llmCudaContext* ctx, cudaStream_t s, uint32_t stream_kind, const float* A,
                           const __half* W, float* C, int M, int N, int K, const float* bias, const float* residual) {
-    (void)stream_kind;
+    const void* wp[1] = {W};
+    if (M >= m40_tc_min_rows() && m40_gemm_tc_supported(M, K, 1, wp)) {
+        const __half* w[1] = {W};
+        const int n[1] = {N};
+        float* o[1] = {C};
+        const float* b[1] = {bias};
+        const float* r[1] = {residual};
+        return m40_gemm_tc_f16(ctx, s, stream_kind, A, M, K, 1, w, n, o, b, r, 0);
+    }
     return m40_gemm_f32xf16_gguf(ctx, s, A, W, C, M, N, K, bias, residual);
 }
 
@@ -590,8 +612,18 @@ int m40llm_ffn_swiglu_f16_f32_async(M40llmCudaContext* ctx, const void* d_x_f32,
     if (m40_ensure_device(ctx) != 0) return -1;
     cudaStream_t s = m40_stream(ctx, stream_kind);
     if (!s) return -4;
-    int rc = m40_gate_up_swiglu_f16(ctx, s, (const float*)d_x_f32, (const __half*)d_wg_f16, (const __half*)d_wu_f16,
+    int rc;
+    const void* wp[2] = {d_wg_f16, d_wu_f16};
+    if ((int)rows >= m40_tc_min_rows() && m40_gemm_tc_supported((int)rows, (int)hidden, 2, wp)) {
+        const __half* w[2] = {(const __half*)d_wg_f16, (const __half*)d_wu_f16};
+        const int n[2] = {(int)ffn, (int)ffn};
+        float* o[2] = {(float*)d_hid_f32, nullptr};
+        rc = m40_gemm_tc_f16(ctx, s, stream_kind, (const float*)d_x_f32, (int)rows, (int)hidden, 2, w, n, o, nullptr,
+                             nullptr, 1);
+    } else {
+        rc = m40_gate_up_swiglu_f16(ctx, s, (const float*)d_x_f32, (const __half*)d_wg_f16, (const __half*)d_wu_f16,
                                     (float*)d_hid_f32, (int)rows, (int)ffn, (int)hidden);
+    }
     if (rc != 0) return rc;
     return m40_gemm_dispatch_f16(ctx, s, stream_kind, (const float*)d_hid_f32, (const __half*)d_wd_f16,
                                  (float*)d_out_f32, (int)rows, (int)hidden, (int)ffn, nullptr,

@@ -15,3 +15,6 @@ int m40_gate_up_swiglu_q80(M40llmCudaContext* ctx, cudaStream_t s, const float* 
                            const uint8_t* Wu, float* hid, int M, int F, int K);
 int m40_gate_up_swiglu_f16(M40llmCudaContext* ctx, cudaStream_t s, const float* A, const __half* Wg, const __half* Wu,
                            float* hid, int M, int F, int K);
+
+// Rows at which projections switch to the tcgen05 kernel (default 2; env M40LLM_TC_MIN_ROWS).
+int m40_tc_min_rows();

@@ -1,0 +1,419 @@
+// Batched decode projections on the 5th-generation tensor cores (tcgen05 + TMEM + TMA).
+//
+// For M >= 2 activation rows the projection C[m][n] = sum_k X[m][k] W[n][k] is computed "swapped":
+// the streamed weight tile is the MMA's A operand (128 weight rows = the MMA M dimension) and the
+// small activation matrix is the B operand (MMA N = batch rows padded to 16..256), so the tensor core
+// runs at full height however small the batch is and every weight byte is read from HBM exactly once:
+//
+//   D[n_tile 128 x M_pad] (f32, in TMEM)  +=  W[128 x 64] (f16, smem, TMA 128B-swizzled)
+//                                            * Xt[64 x M_pad] (f16, smem, TMA 128B-swizzled)
+//
+// f32 activations are split into f16 hi + lo parts (two MMAs per k-step; tensor time is free while the
+// kernel is HBM-bound), so results keep f32-level accuracy for small batches.
+//
+// Roles inside a CTA (6 warps): warp 0 = TMA producer, warp 1 = MMA issuer + TMEM owner, warps 2..5 =
+// epilogue (TMEM -> registers -> global partials). Up to three weight matrices that share the
+// activations (Wq|Wk|Wv, Wgate|Wup) are one launch; K is split over grid.y so that about two CTAs per
+// SM are resident. Partials land in scratch and a small second kernel adds the K splits and applies the
+// epilogue (bias, residual, or SiLU(gate)*up).
+//
+// Every wait is bounded: a wait that runs out sets bit 2 of the context's device status word, the
+// CTA stops issuing work, frees its TMEM and returns.
+#include <cuda.h>
+
+#include "common.cuh"
+#include "gemm_tc.cuh"
+
+namespace {
+
+constexpr int BLOCK_N = 128;  // weight rows per CTA tile (MMA M)
+constexpr int BLOCK_K = 64;   // k per stage (one 128-byte swizzle atom of f16)
+constexpr int UMMA_K = 16;
+constexpr uint32_t WAIT_LIMIT = 1u << 22;  // polls per wait before giving up (order of a second)
+
+struct TcArgs {
+    float* partial;            // [k_splits][M][n_total]
+    uint32_t* status;
+    uint32_t M, M_pad, K;
+    uint32_t n_total;          // sum of padded tile rows over the problems (n_tiles_total * 128)
+    uint32_t tile_begin[4];    // first tile of each problem, tile_begin[problems] = total
+    uint32_t problems;
+    uint32_t kblocks_per_split, kblocks_total;
+    uint32_t use_lo;           // 1: activations carry a lo part (second MMA)
+    uint32_t stages;
+};
+
+// ------------------------------------------------------------------ PTX wrappers
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// Bounded wait on a phase parity. Returns false when the limit ran out.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+    const uint32_t addr = smem_u32(bar);
+    for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+        uint32_t done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_u32(smem_dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t* smem_dst, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_dst)), "r"(cols));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols));
+}
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tmem_ld8(uint32_t taddr, float* v) {
+    uint32_t r[8];
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+                 : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// Shared-memory matrix descriptor of a K-major, 128-byte-swizzled tile whose rows are 128 bytes
+// (64 f16): 8-row groups are 1024 bytes apart (SBO), the leading-dimension field is unused (1),
+// descriptor version 1 (sm_100), layout type 2 = SWIZZLE_128B.
+__device__ __forceinline__ uint64_t make_desc_sw128(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
+    d |= (uint64_t)1 << 16;
+    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+
+// kind::f16 instruction descriptor: f32 accumulate, f16 x f16, both operands K-major, M = 128, N = n.
+__device__ __forceinline__ uint32_t make_idesc(uint32_t n) {
+    return (1u << 4) | ((n >> 3) << 17) | ((uint32_t)(BLOCK_N >> 4) << 24);
+}
+
+__global__ void __launch_bounds__(192, 1) gemm_tc_f16_kernel(const __grid_constant__ CUtensorMap tmW0,
+                                                             const __grid_constant__ CUtensorMap tmW1,
+                                                             const __grid_constant__ CUtensorMap tmW2,
+                                                             const __grid_constant__ CUtensorMap tmXh,
+                                                             const __grid_constant__ CUtensorMap tmXl, TcArgs a) {
+    extern __shared__ unsigned char smem_unaligned[];
+    // the swizzled tiles must start on 1024-byte boundaries; the launch reserves the slack
+    unsigned char* smem = smem_unaligned + ((1024u - (smem_u32(smem_unaligned) & 1023u)) & 1023u);
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+    const uint32_t tile = blockIdx.x, ksplit = blockIdx.y;
+    const uint32_t a_bytes = BLOCK_N * BLOCK_K * 2;                 // 16 KB
+    const uint32_t b_bytes = a.M_pad * BLOCK_K * 2;                 // per hi / lo part
+    const uint32_t stage_bytes = a_bytes + (a.use_lo ? 2u : 1u) * b_bytes;
+    unsigned char* stage_base = smem;                                // stages * stage_bytes, 1024-aligned each
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + a.stages * stage_bytes);
+    uint64_t* full = bars;
+    uint64_t* empty = bars + a.stages;
+    uint64_t* accum = bars + 2 * a.stages;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * a.stages + 1);
+    volatile uint32_t* abort_flag = tmem_slot + 1;
+
+    uint32_t tmem_cols = 32;
+    while (tmem_cols < a.M_pad) tmem_cols <<= 1;
+
+    uint32_t problem = 0;
+    while (problem + 1 < a.problems && tile >= a.tile_begin[problem + 1]) ++problem;
+    const CUtensorMap* tmW = problem == 0 ? &tmW0 : (problem == 1 ? &tmW1 : &tmW2);
+    const uint32_t row0 = (tile - a.tile_begin[problem]) * BLOCK_N;
+    const uint32_t kb0 = ksplit * a.kblocks_per_split;
+    uint32_t kb1 = kb0 + a.kblocks_per_split;
+    if (kb1 > a.kblocks_total) kb1 = a.kblocks_total;
+    const uint32_t n_kb = kb1 > kb0 ? kb1 - kb0 : 0u;
+
+    if (threadIdx.x == 0) {
+        for (uint32_t s = 0; s < a.stages; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], 1);
+        }
+        mbar_init(accum, 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) tmem_alloc(tmem_slot, tmem_cols);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ---------------- TMA producer
+        if (lane == 0) {
+            for (uint32_t i = 0; i < n_kb; ++i) {
+                const uint32_t s = i % a.stages, round = i / a.stages;
+                if (round > 0 && !mbar_wait(&empty[s], (round - 1) & 1u)) { *abort_flag = 1; break; }
+                if (*abort_flag) break;
+                unsigned char* st = stage_base + s * stage_bytes;
+                mbar_expect_tx(&full[s], stage_bytes);
+                const int kx = (int)((kb0 + i) * BLOCK_K);
+                tma_load_2d(st, tmW, &full[s], kx, (int)row0);
+                tma_load_2d(st + a_bytes, &tmXh, &full[s], kx, 0);
+                if (a.use_lo) tma_load_2d(st + a_bytes + b_bytes, &tmXl, &full[s], kx, 0);
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer
+        if (lane == 0) {
+            const uint32_t idesc = make_idesc(a.M_pad);
+            bool ok = true;
+            for (uint32_t i = 0; i < n_kb && ok; ++i) {
+                const uint32_t s = i % a.stages, round = i / a.stages;
+                if (!mbar_wait(&full[s], round & 1u)) { *abort_flag = 1; ok = false; break; }
+                tc_fence_after();
+                const uint32_t sa = smem_u32(stage_base + s * stage_bytes);
+                const uint32_t sb = sa + a_bytes;
+#pragma unroll
+                for (uint32_t k = 0; k < BLOCK_K / UMMA_K; ++k) {
+                    const uint64_t da = make_desc_sw128(sa + k * UMMA_K * 2);
+                    umma_f16(tmem_base, da, make_desc_sw128(sb + k * UMMA_K * 2), idesc, (i | k) != 0u);
+                    if (a.use_lo) umma_f16(tmem_base, da, make_desc_sw128(sb + b_bytes + k * UMMA_K * 2), idesc, 1u);
+                }
+                umma_commit(&empty[s]);  // frees the stage once these MMAs have read it
+            }
+            if (ok) umma_commit(accum);  // accumulator complete
+        }
+    } else {
+        // ---------------- epilogue: warps 2..5 own TMEM lanes 32*(warp % 4) .. +31
+        const uint32_t lane_group = warp & 3u;
+        bool ok = n_kb > 0;
+        if (ok) {
+            if (!mbar_wait(accum, 0)) { *abort_flag = 1; ok = false; }
+        }
+        ok = __all_sync(0xffffffffu, ok);  // tcgen05.ld is warp-collective
+        tc_fence_after();
+        const uint32_t n_glob = tile * BLOCK_N + lane_group * 32 + lane;
+        float* dst = a.partial + (size_t)ksplit * a.M * a.n_total + n_glob;
+        for (uint32_t c = 0; c < a.M_pad; c += 8) {
+            float v[8];
+            if (ok) tmem_ld8(tmem_base + ((lane_group * 32u) << 16) + c, v);
+            else {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[j] = 0.0f;
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                if (c + j < a.M) dst[(size_t)(c + j) * a.n_total] = v[j];
+        }
+    }
+    if (*abort_flag && threadIdx.x == 64) atomicOr(a.status, 4u);
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, tmem_cols);
+    }
+}
+
+// f32 activations -> f16 hi (+ lo) copies, [M][K] row-major.
+__global__ void split_activations_kernel(const float* __restrict__ x, __half* __restrict__ hi, __half* __restrict__ lo,
+                                         size_t n) {
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+        const float v = x[i];
+        const __half h = __float2half_rn(v);
+        hi[i] = h;
+        if (lo) lo[i] = __float2half_rn(v - __half2float(h));
+    }
+}
+
+// Adds the K splits and applies the epilogue. One thread per (m, n) of one problem.
+// mode 0: C = sum (+ bias[n]) (+ residual[m][n]);  mode 1: problems 0/1 are gate/up, C = silu(gate) * up.
+struct EpiArgs {
+    const float* partial;
+    float* out[3];
+    const float* bias[3];
+    const float* residual[3];
+    uint32_t N[3];
+    uint32_t tile_begin[4];
+    uint32_t problems, M, n_total, k_splits, mode;
+};
+
+__global__ void gemm_tc_epilogue_kernel(EpiArgs e) {
+    const uint32_t p = blockIdx.z;
+    const uint32_t n = blockIdx.x * blockDim.x + threadIdx.x;
+    const uint32_t m = blockIdx.y;
+    if (n >= e.N[p]) return;
+    const size_t split_stride = (size_t)e.M * e.n_total;
+    const size_t idx = (size_t)m * e.n_total + (size_t)e.tile_begin[p] * BLOCK_N + n;
+    float acc = 0.0f;
+    for (uint32_t s = 0; s < e.k_splits; ++s) acc += e.partial[s * split_stride + idx];
+    if (e.mode == 1) {
+        const size_t idx_u = (size_t)m * e.n_total + (size_t)e.tile_begin[1] * BLOCK_N + n;
+        float up = 0.0f;
+        for (uint32_t s = 0; s < e.k_splits; ++s) up += e.partial[s * split_stride + idx_u];
+        e.out[0][(size_t)m * e.N[0] + n] = (acc / (1.0f + expf(-acc))) * up;
+        return;
+    }
+    if (e.bias[p]) acc += e.bias[p][n];
+    if (e.residual[p]) acc += e.residual[p][(size_t)m * e.N[p] + n];
+    e.out[p][(size_t)m * e.N[p] + n] = acc;
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode() {
+    static EncodeTiledFn fn = nullptr;
+    static bool tried = false;
+    if (!tried) {
+        tried = true;
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    }
+    return fn;
+}
+
+// 2D f16 tensor [rows][cols] row-major, box [box_rows][64], 128-byte swizzle, zero fill out of bounds.
+bool make_map_f16(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+    EncodeTiledFn enc = get_encode();
+    if (!enc) return false;
+    const cuuint64_t dims[2] = {cols, rows};
+    const cuuint64_t strides[1] = {cols * 2};
+    const cuuint32_t box[2] = {BLOCK_K, box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    return enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+}  // namespace
+
+bool m40_gemm_tc_supported(int M, int K, int problems, const void* const* W) {
+    if (M < 2 || M > 256 || K % 8 != 0 || K < BLOCK_K || problems < 1 || problems > 3) return false;
+    for (int p = 0; p < problems; ++p)
+        if ((((uintptr_t)W[p]) & 15u) != 0u) return false;
+    return get_encode() != nullptr;
+}
+
+int m40_gemm_tc_f16(M40llmCudaContext* ctx, cudaStream_t s, uint32_t stream_kind, const float* X, int M, int K,
+                    int problems, const __half* const* W, const int* N, float* const* out, const float* const* bias,
+                    const float* const* residual, int mode) {
+    const uint32_t M_pad = (uint32_t)((M + 15) / 16 * 16);
+    TcArgs a = {};
+    a.M = (uint32_t)M;
+    a.M_pad = M_pad;
+    a.K = (uint32_t)K;
+    a.problems = (uint32_t)problems;
+    // hi-only f16 activations miss the parity tolerance for outputs near zero (error ~3e-4 * |x| * sqrt(K) * |w|),
+    // so the lo part is always carried; above ~128 rows this makes the kernel tensor-bound instead of HBM-bound.
+    a.use_lo = 1u;
+    uint32_t tiles = 0;
+    for (int p = 0; p < problems; ++p) {
+        a.tile_begin[p] = tiles;
+        tiles += (uint32_t)((N[p] + BLOCK_N - 1) / BLOCK_N);
+    }
+    for (int p = problems; p < 4; ++p) a.tile_begin[p] = tiles;
+    a.n_total = tiles * BLOCK_N;
+    a.kblocks_total = (uint32_t)((K + BLOCK_K - 1) / BLOCK_K);
+    // stages from the shared-memory budget; two CTAs per SM when the stage is small
+    const uint32_t stage_bytes = BLOCK_N * BLOCK_K * 2 + (a.use_lo ? 2u : 1u) * M_pad * BLOCK_K * 2;
+    uint32_t stages = (100u * 1024u) / stage_bytes;
+    if (stages > 8) stages = 8;
+    if (stages < 2) stages = 2;
+    a.stages = stages;
+    const size_t smem = (size_t)stages * stage_bytes + (2 * stages + 1) * 8 + 16 + 1024;
+    const uint32_t ctas_per_sm = smem <= 110u * 1024u ? 2u : 1u;
+    // K splits: fill about one wave of resident CTAs, keep at least 4 k-blocks per split
+    uint32_t ks = ((uint32_t)ctx->sm_count * ctas_per_sm) / tiles;
+    if (ks < 1) ks = 1;
+    const uint32_t ks_max = a.kblocks_total / 4 ? a.kblocks_total / 4 : 1;
+    if (ks > ks_max) ks = ks_max;
+    if (ks > 16) ks = 16;
+    a.kblocks_per_split = (a.kblocks_total + ks - 1) / ks;
+    ks = (a.kblocks_total + a.kblocks_per_split - 1) / a.kblocks_per_split;
+
+    // scratch: [hi][lo] activation copies, then the partials
+    const size_t act_elems = (size_t)M * K;
+    const size_t act_bytes = ((act_elems * 2 + 255) / 256) * 256;
+    const size_t part_bytes = (size_t)ks * M * a.n_total * sizeof(float);
+    unsigned char* scratch = (unsigned char*)m40_ensure_scratch(ctx, stream_kind, 2 * act_bytes + part_bytes);
+    if (!scratch) return -2;
+    __half* xh = (__half*)scratch;
+    __half* xl = a.use_lo ? (__half*)(scratch + act_bytes) : nullptr;
+    a.partial = (float*)(scratch + 2 * act_bytes);
+    a.status = ctx->d_status;
+
+    CUtensorMap mW[3], mXh, mXl;
+    for (int p = 0; p < 3; ++p) {
+        const int q = p < problems ? p : 0;
+        if (!make_map_f16(&mW[p], W[q], (uint64_t)N[q], (uint64_t)K, BLOCK_N)) return -2;
+    }
+    if (!make_map_f16(&mXh, xh, (uint64_t)M, (uint64_t)K, M_pad)) return -2;
+    if (!make_map_f16(&mXl, a.use_lo ? xl : xh, (uint64_t)M, (uint64_t)K, M_pad)) return -2;
+
+    {
+        size_t blocks = (act_elems + 255) / 256;
+        if (blocks > (size_t)ctx->sm_count * 8) blocks = (size_t)ctx->sm_count * 8;
+        split_activations_kernel<<<(unsigned)blocks, 256, 0, s>>>(X, xh, xl, act_elems);
+        M40_COUNT_LAUNCH(ctx);
+    }
+    static unsigned long long configured = 0ull;
+    const unsigned long long bit = 1ull << (ctx->device_id & 63);
+    if (!(configured & bit)) {
+        if (cudaFuncSetAttribute(gemm_tc_f16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess)
+            return -2;
+        configured |= bit;
+    }
+    dim3 grid(tiles, ks);
+    gemm_tc_f16_kernel<<<grid, 192, smem, s>>>(mW[0], mW[1], mW[2], mXh, mXl, a);
+    M40_COUNT_LAUNCH(ctx);
+    if (cudaGetLastError() != cudaSuccess) return -2;
+
+    EpiArgs e = {};
+    e.partial = a.partial;
+    uint32_t maxN = 0;
+    for (int p = 0; p < problems; ++p) {
+        e.out[p] = out[p];
+        e.bias[p] = bias ? bias[p] : nullptr;
+        e.residual[p] = residual ? residual[p] : nullptr;
+        e.N[p] = (uint32_t)N[p];
+        if ((uint32_t)N[p] > maxN) maxN = (uint32_t)N[p];
+    }
+    for (int p = 0; p < 4; ++p) e.tile_begin[p] = a.tile_begin[p];
+    e.problems = (uint32_t)problems;
+    e.M = (uint32_t)M;
+    e.n_total = a.n_total;
+    e.k_splits = ks;
+    e.mode = (uint32_t)mode;
+    dim3 egrid((maxN + 255) / 256, (unsigned)M, mode == 1 ? 1u : (unsigned)problems);
+    gemm_tc_epilogue_kernel<<<egrid, 256, 0, s>>>(e);
+    M40_COUNT_LAUNCH(ctx);
+    return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}

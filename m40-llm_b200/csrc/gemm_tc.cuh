@@ -1,0 +1,13 @@
+// Tensor-core (tcgen05) weight-streaming GEMM for batched decode rows; see gemm_tc.cu.
+#pragma once
+#include "common.cuh"
+
+// True when the tcgen05 path can take this problem set (2 <= M <= 256, K % 8 == 0, 16-byte aligned weights).
+bool m40_gemm_tc_supported(int M, int K, int problems, const void* const* W);
+
+// Up to three GGUF-layout f16 weight matrices W[p] ([N[p]][K]) applied to the same activations X [M][K] f32.
+// mode 0: out[p][m][n] = X.W[p]^T (+ bias[p][n]) (+ residual[p][m][n]); bias / residual arrays or entries may be null.
+// mode 1: two problems (gate, up) of equal N: out[0][m][n] = silu(X.Wg^T) * (X.Wu^T).
+int m40_gemm_tc_f16(M40llmCudaContext* ctx, cudaStream_t s, uint32_t stream_kind, const float* X, int M, int K,
+                    int problems, const __half* const* W, const int* N, float* const* out, const float* const* bias,
+                    const float* const* residual, int mode);

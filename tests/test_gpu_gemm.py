@@ -8,7 +8,10 @@ from helpers import assert_close
 pytestmark = pytest.mark.gpu
 
 SHAPES = [(1, 10, 37), (3, 17, 64), (1, 256, 2048), (1, 2048, 2048), (2, 1024, 4096), (1, 4096, 4096),
-          (5, 520, 1032), (8, 4096, 4096), (1, 2048, 5632)]
+          (5, 520, 1032), (8, 4096, 4096), (1, 2048, 5632),
+          # batched rows: the tcgen05 path (M padded to 16..256, K tails, N tails, K splits)
+          (16, 128, 64), (17, 300, 200), (32, 4096, 4096), (33, 1000, 2048), (64, 1024, 512), (65, 256, 1024),
+          (100, 384, 520), (128, 2048, 2048), (256, 256, 4096), (32, 4096, 14336), (4, 24, 4096)]
 
 
 @pytest.mark.parametrize("M,N,K", SHAPES)
