@@ -9,6 +9,8 @@
 #include "gemm.cuh"
 #include "gemm_tc.cuh"
 
+int m40_tc_min_rows();
+
 namespace {
 
 __device__ __forceinline__ uint4 ldg_stream_u4(const void* p) {
@@ -399,6 +401,39 @@ int m40_gemm_f32xq80_gguf(M40llmCudaContext* ctx, cudaStream_t s, const float* A
     return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 
+// Q8_0 projections for batched rows on the tensor cores, 64 rows per pass. Returns 1 when not applicable.
+static int q80_tc_rows(M40llmCudaContext* ctx, cudaStream_t s, uint32_t stream_kind, const float* A, int M, int K,
+                       int problems, const uint8_t* const* W, const int* N, float* const* out, const float* residual,
+                       int mode) {
+    const void* wp[3] = {W[0], problems > 1 ? W[1] : W[0], problems > 2 ? W[2] : W[0]};
+    if (M < m40_tc_min_rows() || !m40_gemm_tc_q80_supported(M < 64 ? M : 64, K, problems, wp)) return 1;
+    for (int m0 = 0; m0 < M; m0 += 64) {
+        const int rows = M - m0 < 64 ? M - m0 : 64;
+        if (rows < 2) {  // a single trailing row: CUDA-core kernel
+            if (mode == 1) {
+                const int rc1 = m40_gate_up_swiglu_q80(ctx, s, A + (size_t)m0 * K, W[0], W[1], out[0] + (size_t)m0 * N[0], 1, N[0], K);
+                if (rc1 != 0) return rc1;
+            } else {
+                for (int p = 0; p < problems; ++p) {
+                    const int rc1 = m40_gemm_f32xq80_gguf(ctx, s, A + (size_t)m0 * K, W[p], out[p] + (size_t)m0 * N[p], 1, N[p], K,
+                                                          residual ? residual + (size_t)m0 * N[p] : nullptr);
+                    if (rc1 != 0) return rc1;
+                }
+            }
+            continue;
+        }
+        float* o[3];
+        const float* r[3];
+        for (int p = 0; p < problems; ++p) {
+            o[p] = out[p] ? out[p] + (size_t)m0 * N[p] : nullptr;
+            r[p] = residual ? residual + (size_t)m0 * N[p] : nullptr;
+        }
+        const int rc = m40_gemm_tc_q80(ctx, s, stream_kind, A + (size_t)m0 * K, rows, K, problems, W, N, o, r, mode);
+        if (rc != 0) return rc;
+    }
+    return 0;
+}
+
 int m40_gate_up_swiglu_q80(M40llmCudaContext* ctx, cudaStream_t s, const float* A, const uint8_t* Wg,
                            const uint8_t* Wu, float* hid, int M, int F, int K) {
     if (K % 128 != 0 || !aligned16(A) || ((((uintptr_t)Wg) | ((uintptr_t)Wu)) & 1u) != 0u) return -2;
@@ -550,6 +585,13 @@ int m40llm_gemm_f32xq80_gguf_f32_async(M40llmCudaContext* ctx, const void* d_A_f
     if (m40_ensure_device(ctx) != 0) return -1;
     cudaStream_t s = m40_stream(ctx, stream_kind);
     if (!s) return -4;
+    {
+        const uint8_t* w[1] = {(const uint8_t*)d_B_q80};
+        const int n[1] = {N};
+        float* o[1] = {(float*)d_C_f32};
+        const int rc = q80_tc_rows(ctx, s, stream_kind, (const float*)d_A_f32, M, K, 1, w, n, o, nullptr, 0);
+        if (rc != 1) return rc;
+    }
     return m40_gemm_f32xq80_gguf(ctx, s, (const float*)d_A_f32, (const uint8_t*)d_B_q80, (float*)d_C_f32, M, N, K,
                                  nullptr);
 }
@@ -596,9 +638,25 @@ int m40llm_ffn_swiglu_q80_f32_async(M40llmCudaContext* ctx, const void* d_x_f32,
     if (m40_ensure_device(ctx) != 0) return -1;
     cudaStream_t s = m40_stream(ctx, stream_kind);
     if (!s) return -4;
-    int rc = m40_gate_up_swiglu_q80(ctx, s, (const float*)d_x_f32, (const uint8_t*)d_wg_q80,
-                                    (const uint8_t*)d_wu_q80, (float*)d_hid_f32, (int)rows, (int)ffn, (int)hidden);
+    int rc;
+    {
+        const uint8_t* w[2] = {(const uint8_t*)d_wg_q80, (const uint8_t*)d_wu_q80};
+        const int n[2] = {(int)ffn, (int)ffn};
+        float* o[2] = {(float*)d_hid_f32, nullptr};
+        rc = q80_tc_rows(ctx, s, stream_kind, (const float*)d_x_f32, (int)rows, (int)hidden, 2, w, n, o, nullptr, 1);
+    }
+    if (rc == 1)
+        rc = m40_gate_up_swiglu_q80(ctx, s, (const float*)d_x_f32, (const uint8_t*)d_wg_q80, (const uint8_t*)d_wu_q80,
+                                    (float*)d_hid_f32, (int)rows, (int)ffn, (int)hidden);
     if (rc != 0) return rc;
+    {
+        const uint8_t* w[1] = {(const uint8_t*)d_wd_q80};
+        const int n[1] = {(int)hidden};
+        float* o[1] = {(float*)d_out_f32};
+        rc = q80_tc_rows(ctx, s, stream_kind, (const float*)d_hid_f32, (int)rows, (int)ffn, 1, w, n, o,
+                         (const float*)d_residual_f32, 0);
+    }
+    if (rc != 1) return rc;
     return m40_gemm_f32xq80_gguf(ctx, s, (const float*)d_hid_f32, (const uint8_t*)d_wd_q80, (float*)d_out_f32,
                                  (int)rows, (int)hidden, (int)ffn, (const float*)d_residual_f32);
 }

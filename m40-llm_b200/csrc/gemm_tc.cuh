@@ -11,3 +11,10 @@ bool m40_gemm_tc_supported(int M, int K, int problems, const void* const* W);
 int m40_gemm_tc_f16(M40llmCudaContext* ctx, cudaStream_t s, uint32_t stream_kind, const float* X, int M, int K,
                     int problems, const __half* const* W, const int* N, float* const* out, const float* const* bias,
                     const float* const* residual, int mode);
+
+// Same over Q8_0 GGUF rows (K % 256 == 0, 2 <= M <= 64 per call). mode 0: out[p] = X.W[p]^T (+ residual[p]);
+// mode 1: out[0] = silu(X.Wg^T) * (X.Wu^T).
+bool m40_gemm_tc_q80_supported(int M, int K, int problems, const void* const* W);
+int m40_gemm_tc_q80(M40llmCudaContext* ctx, cudaStream_t s, uint32_t stream_kind, const float* X, int M, int K,
+                    int problems, const uint8_t* const* W, const int* N, float* const* out,
+                    const float* const* residual, int mode);
