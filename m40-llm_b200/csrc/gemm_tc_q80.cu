@@ -1,18 +1,18 @@
 // Batched decode projections over Q8_0 GGUF rows on the tcgen05 tensor cores.
 //
 // Q8_0 stores 32 weights as {f16 d; int8 q[32]} (34 bytes, cuda/kernels.cu:856-867 of the reference):
-// w = d * q with a different d for every (row, 32-k block). The kernel keeps that structure exact:
+// w = d * q with a different d for every (row, 32-k block).
 //
 //   raw bytes   TMA (plain 2D box of 128 rows x 272 bytes = 8 blocks per row) straight from the GGUF layout;
-//   int8 -> f16 worker threads (one weight row each) turn q into exact f16 integers and write them into the
-//               128-byte-swizzled K-major tile the MMA reads; d stays in a register;
-//   MMA         per 32-k block a FRESH accumulator D_b[128 x M_pad] = Q_b . Xt_b in TMEM (activations as f16
-//               hi + lo parts, so D_b is exact to f32 rounding); four TMEM buffers rotate;
-//   scale       the same worker threads read their row of D_b back (tcgen05.ld) and do
-//               acc[m] += d * D_b[m] in f32 registers  -- the reference's d*q product, just re-associated.
+//   dequant     16 worker warps (4 threads per weight row) turn the bytes into TWO f16 tiles in the
+//               128-byte-swizzled K-major layout the MMA reads: hi = rn(d*q) and lo = d*q - hi (exact by FMA),
+//               so hi + lo carries the product to ~2^-22 -- the value the reference computes in f32;
+//   MMA         D[128 x M_pad] += hi.Xh + hi.Xl + lo.Xh with activations split the same way, f32 in TMEM,
+//               one accumulator per tile segment (two TMEM buffers alternate between segments);
+//   epilogue    the worker threads read their row of D back (tcgen05.ld) at the end of a segment.
 //
 // Work is split stream-K style: the (tile, 256-k unit) space is cut into one contiguous span per CTA
-// (one CTA per SM; shared memory holds two raw stages + rings), so every SM streams the same number of
+// (one CTA per SM; shared memory holds two raw stages, three dequantised tile pairs and the activation ring), so every SM streams the same number of
 // weight bytes. A span that crosses tile boundaries writes one partial per tile; the epilogue kernel adds
 // the partials of each tile and applies residual or SiLU(gate)*up.
 //
@@ -32,7 +32,8 @@ constexpr uint32_t UNIT_K = 256;                       // k per raw stage (8 Q8_
 constexpr uint32_t RAW_ROW_BYTES = UNIT_K / 32 * 34;   // 272
 constexpr uint32_t RAW_BYTES = BLOCK_N * RAW_ROW_BYTES; // 34816
 constexpr uint32_t A_BYTES = BLOCK_N * BLOCK_K * 2;    // 16384: one converted 64-k sub-block
-constexpr uint32_t RS = 2, AS = 2, BS = 4, TB = 4;     // ring depths: raw stages, A slots, B slots, TMEM buffers
+constexpr uint32_t RS = 2, AS = 3, TB = 2;             // ring depths: raw stages, (hi, lo) A tile pairs, TMEM accumulators
+__host__ __device__ constexpr uint32_t b_slots(int m_pad) { return m_pad <= 32 ? 4u : 2u; }  // activation sub-block slots
 
 struct Q80Args {
     float* partial;  // [ctas][seg_max][M][128]
@@ -48,18 +49,134 @@ __device__ __forceinline__ void span_of(const Q80Args& a, uint32_t cta, uint32_t
     *u1 = (uint32_t)(((uint64_t)(cta + 1) * a.units_total) / a.ctas);
 }
 
+struct Q80Smem {
+    unsigned char* s_raw;
+    unsigned char* s_a;
+    uint64_t *raw_full, *raw_empty, *a_full, *a_empty, *t_full, *t_empty;
+    volatile uint32_t* abort_flag;
+};
+
+constexpr uint32_t WORKER_WARPS = 16;                    // 4 threads per weight row
+constexpr uint32_t WORKER_THREADS = WORKER_WARPS * 32;   // 512
+constexpr uint32_t CTA_THREADS = 96 + WORKER_THREADS;    // + weight producer, MMA issuer, activation producer warps
+
+// One worker thread owns (weight row r, quarter C4): it dequantises weights [16*C4, 16*C4+16) of every 64-k
+// sub-block into the hi and lo f16 tiles, and at the end of a tile segment reads columns
+// [C4*M_PAD/4, +M_PAD/4) of its row of the accumulator.
+template <int M_PAD, int C4>
+__device__ __forceinline__ void q80_worker(const Q80Args& a, const Q80Smem& sm, uint32_t tmem_base, uint32_t u0,
+                                           uint32_t u1, uint32_t lane_group, uint32_t lane) {
+    constexpr int COLS = M_PAD / 4;
+    const uint32_t r = lane_group * 32 + lane;  // weight row of the tile == TMEM lane
+    bool ok = true;
+    uint32_t ucount = 0;
+    // every wait of a worker warp is made warp-uniform so the warp-collective tcgen05.ld stays converged
+    auto wwait = [&](uint64_t* bar, uint32_t parity) {
+        const bool r0 = mbar_wait(bar, parity);
+        return (bool)__all_sync(0xffffffffu, r0);
+    };
+    uint32_t pos = u0, seg = 0;
+    while (pos < u1 && ok) {
+        const uint32_t kb_begin = pos % a.units_per_tile;
+        uint32_t kb_end = kb_begin + (u1 - pos);
+        if (kb_end > a.units_per_tile) kb_end = a.units_per_tile;
+        for (uint32_t kb = kb_begin; kb < kb_end && ok; ++kb) {
+            const uint32_t i = ucount / 4, rs = i % RS;
+            if (!wwait(&sm.raw_full[rs], (i / RS) & 1u)) { ok = false; break; }
+            const unsigned char* row = sm.s_raw + rs * RAW_BYTES + r * RAW_ROW_BYTES;
+#pragma unroll
+            for (uint32_t sub = 0; sub < 4; ++sub) {
+                const uint32_t u = ucount, as = u % AS;
+                if (u >= AS && !wwait(&sm.a_empty[as], ((u / AS) - 1) & 1u)) { ok = false; break; }
+                // this thread's 16 weights: bytes [b0, b0+16) of the row (2-byte aligned), scale at the block start
+                const uint32_t blk_off = (2 * sub + (C4 >> 1)) * 34;
+                const __half d = *reinterpret_cast<const __half*>(row + blk_off);
+                const uint32_t b0 = blk_off + 2 + (C4 & 1) * 16;
+                const uint32_t bs = b0 & ~3u;             // 4-byte aligned start of the word window
+                const bool upper_first = (b0 & 2u) != 0u;  // first pair is the upper half of word 0
+                const uint32_t chunk = bs >> 4, wo = (bs & 15u) >> 2;
+                uint32_t w[8];
+                {
+                    const uint4 t0 = *reinterpret_cast<const uint4*>(row + chunk * 16);
+                    w[0] = t0.x; w[1] = t0.y; w[2] = t0.z; w[3] = t0.w;
+                    if (wo + (upper_first ? 5u : 4u) > 4u) {
+                        const uint4 t1 = *reinterpret_cast<const uint4*>(row + chunk * 16 + 16);
+                        w[4] = t1.x; w[5] = t1.y; w[6] = t1.z; w[7] = t1.w;
+                    } else {
+                        w[4] = w[5] = w[6] = w[7] = 0u;
+                    }
+                }
+                const __half2 bias = __float2half2_rn(1152.0f);
+                const __half2 d2 = __half2half2(d);
+                uint32_t hi[8], lo[8];
+#pragma unroll
+                for (uint32_t p = 0; p < 8; ++p) {
+                    // pair p sits at byte offset 2p from b0: word (p + upper_first) / 2, alternating halves
+                    const uint32_t q = p + (upper_first ? 1u : 0u);
+                    const uint32_t word = w[wo + (q >> 1)] ^ 0x80808080u;
+                    const uint32_t h = __byte_perm(word, 0x64646464u, (q & 1u) ? 0x7362 : 0x5140);  // (1024+u0, 1024+u1)
+                    const __half2 q2 = __hsub2(*reinterpret_cast<const __half2*>(&h), bias);          // exact ints
+                    const __half2 h2 = __hmul2(q2, d2);                                               // rn(d*q)
+                    const __half2 l2 = __hfma2(q2, d2, __hneg2(h2));                                  // d*q - hi, exact
+                    hi[p] = *reinterpret_cast<const uint32_t*>(&h2);
+                    lo[p] = *reinterpret_cast<const uint32_t*>(&l2);
+                }
+                unsigned char* dst = sm.s_a + as * 2 * A_BYTES + (r >> 3) * 1024 + (r & 7u) * 128;
+                const uint32_t c0 = ((2 * C4) ^ (r & 7u)) * 16, c1 = ((2 * C4 + 1) ^ (r & 7u)) * 16;
+                *reinterpret_cast<uint4*>(dst + c0) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+                *reinterpret_cast<uint4*>(dst + c1) = make_uint4(hi[4], hi[5], hi[6], hi[7]);
+                *reinterpret_cast<uint4*>(dst + A_BYTES + c0) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+                *reinterpret_cast<uint4*>(dst + A_BYTES + c1) = make_uint4(lo[4], lo[5], lo[6], lo[7]);
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                // one arrival per warp: hundreds of per-thread arrivals on one barrier word serialise in shared memory
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&sm.a_full[as]);
+                ++ucount;
+            }
+            if (!ok) break;
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&sm.raw_empty[rs]);
+        }
+        if (!ok) break;
+        // ---- end of the tile segment: read this row's accumulator columns and store the partial
+        const uint32_t tb = seg % TB;
+        if (!wwait(&sm.t_full[tb], (seg / TB) & 1u)) { ok = false; break; }
+        tc_fence_after();
+        uint32_t x[COLS];
+        const uint32_t taddr = tmem_base + ((lane_group * 32u) << 16) + tb * M_PAD + C4 * COLS;
+        if (COLS == 4) tmem_ld_x4(taddr, x);
+        else if (COLS == 8) tmem_ld_x8(taddr, x);
+        else tmem_ld_x16(taddr, x);
+        tmem_ld_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sm.t_empty[tb]);
+        float* dstp = a.partial + ((size_t)(blockIdx.x * a.seg_max + seg) * a.M) * BLOCK_N + r;
+#pragma unroll
+        for (int j = 0; j < COLS; ++j) {
+            const uint32_t m = C4 * COLS + j;
+            if (m < a.M) dstp[(size_t)m * BLOCK_N] = __uint_as_float(x[j]);
+        }
+        pos += kb_end - kb_begin;
+        ++seg;
+    }
+    if (!ok) *sm.abort_flag = 1;
+}
+
 template <int M_PAD>
-__global__ void __launch_bounds__(192, 1) gemm_tc_q80_kernel(const __grid_constant__ CUtensorMap tmW0,
-                                                             const __grid_constant__ CUtensorMap tmW1,
-                                                             const __grid_constant__ CUtensorMap tmW2,
-                                                             const __grid_constant__ CUtensorMap tmXh,
-                                                             const __grid_constant__ CUtensorMap tmXl, Q80Args a) {
+__global__ void __launch_bounds__(CTA_THREADS, 1) gemm_tc_q80_kernel(const __grid_constant__ CUtensorMap tmW0,
+                                                                     const __grid_constant__ CUtensorMap tmW1,
+                                                                     const __grid_constant__ CUtensorMap tmW2,
+                                                                     const __grid_constant__ CUtensorMap tmXh,
+                                                                     const __grid_constant__ CUtensorMap tmXl,
+                                                                     Q80Args a) {
     constexpr uint32_t B_BYTES = M_PAD * BLOCK_K * 2;  // one of hi / lo for a 64-k sub-block
+    constexpr uint32_t BS = b_slots(M_PAD);
     extern __shared__ unsigned char smem_unaligned[];
     unsigned char* smem = smem_unaligned + ((1024u - (smem_u32(smem_unaligned) & 1023u)) & 1023u);
     unsigned char* s_raw = smem;                             // RS x RAW_BYTES
-    unsigned char* s_a = s_raw + RS * RAW_BYTES;             // AS x A_BYTES (1024-aligned: RAW_BYTES = 34 * 1024)
-    unsigned char* s_b = s_a + AS * A_BYTES;                 // BS x (hi, lo)
+    unsigned char* s_a = s_raw + RS * RAW_BYTES;             // AS x (hi, lo) x A_BYTES (1024-aligned: RAW_BYTES = 34 KB)
+    unsigned char* s_b = s_a + AS * 2 * A_BYTES;             // BS x (hi, lo)
     uint64_t* bars = reinterpret_cast<uint64_t*>(s_b + BS * 2 * B_BYTES);
     uint64_t* raw_full = bars;
     uint64_t* raw_empty = raw_full + RS;
@@ -73,17 +190,17 @@ __global__ void __launch_bounds__(192, 1) gemm_tc_q80_kernel(const __grid_consta
     volatile uint32_t* abort_flag = tmem_slot + 1;
 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
-    constexpr uint32_t TMEM_COLS = TB * M_PAD < 32 ? 32 : TB * M_PAD;  // 64 / 128 / 256: powers of two
+    constexpr uint32_t TMEM_COLS = TB * M_PAD < 32 ? 32 : TB * M_PAD;  // 32 / 64 / 128: powers of two
 
     uint32_t u0, u1;
     span_of(a, blockIdx.x, &u0, &u1);
     const uint32_t n_units = u1 - u0;
 
     if (threadIdx.x == 0) {
-        for (uint32_t i = 0; i < RS; ++i) { mbar_init(&raw_full[i], 1); mbar_init(&raw_empty[i], 128); }
-        for (uint32_t i = 0; i < AS; ++i) { mbar_init(&a_full[i], 128); mbar_init(&a_empty[i], 1); }
+        for (uint32_t i = 0; i < RS; ++i) { mbar_init(&raw_full[i], 1); mbar_init(&raw_empty[i], WORKER_WARPS); }
+        for (uint32_t i = 0; i < AS; ++i) { mbar_init(&a_full[i], WORKER_WARPS); mbar_init(&a_empty[i], 1); }
         for (uint32_t i = 0; i < BS; ++i) { mbar_init(&b_full[i], 1); mbar_init(&b_empty[i], 1); }
-        for (uint32_t i = 0; i < TB; ++i) { mbar_init(&t_full[i], 1); mbar_init(&t_empty[i], 128); }
+        for (uint32_t i = 0; i < TB; ++i) { mbar_init(&t_full[i], 1); mbar_init(&t_empty[i], WORKER_WARPS); }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -94,7 +211,7 @@ __global__ void __launch_bounds__(192, 1) gemm_tc_q80_kernel(const __grid_consta
     const uint32_t tmem_base = *tmem_slot;
 
     if (warp == 0) {
-        // ---------------- TMA producer
+        // ---------------- weight producer: raw Q8_0 stages, running up to RS units ahead of the workers
         if (lane == 0) {
             bool ok = true;
             for (uint32_t i = 0; i < n_units && ok; ++i) {
@@ -109,9 +226,19 @@ __global__ void __launch_bounds__(192, 1) gemm_tc_q80_kernel(const __grid_consta
                 if (*abort_flag) { ok = false; break; }
                 mbar_expect_tx(&raw_full[rs], RAW_BYTES);
                 tma_load_2d(s_raw + rs * RAW_BYTES, tmW, &raw_full[rs], (int)(kb * (RAW_ROW_BYTES / 2)), (int)row0);
+            }
+            if (!ok) *abort_flag = 1;
+        }
+    } else if (warp == 2) {
+        // ---------------- activation producer: hi and lo f16 copies of X for every 64-k sub-block
+        if (lane == 0) {
+            bool ok = true;
+            for (uint32_t i = 0; i < n_units && ok; ++i) {
+                const uint32_t kb = (u0 + i) % a.units_per_tile;
                 for (uint32_t sub = 0; sub < 4; ++sub) {
                     const uint32_t u = i * 4 + sub, bs = u % BS;
                     if (u >= BS && !mbar_wait(&b_empty[bs], ((u / BS) - 1) & 1u)) { ok = false; break; }
+                    if (*abort_flag) { ok = false; break; }
                     mbar_expect_tx(&b_full[bs], 2 * B_BYTES);
                     const int kx = (int)(kb * UNIT_K + sub * BLOCK_K);
                     tma_load_2d(s_b + bs * 2 * B_BYTES, &tmXh, &b_full[bs], kx, 0);
@@ -121,143 +248,56 @@ __global__ void __launch_bounds__(192, 1) gemm_tc_q80_kernel(const __grid_consta
             if (!ok) *abort_flag = 1;
         }
     } else if (warp == 1) {
-        // ---------------- MMA issuer: per 32-k block a fresh accumulator in TMEM buffer v % TB
+        // ---------------- MMA issuer: one accumulator per tile segment, TMEM buffer = segment % TB
         if (lane == 0) {
             const uint32_t idesc = make_idesc(M_PAD);
             bool ok = true;
-            for (uint32_t u = 0; u < n_units * 4 && ok; ++u) {
-                const uint32_t as = u % AS, bs = u % BS;
-                if (!mbar_wait(&a_full[as], (u / AS) & 1u) || !mbar_wait(&b_full[bs], (u / BS) & 1u)) { ok = false; break; }
+            uint32_t pos = u0, seg = 0, u = 0;
+            while (pos < u1 && ok) {
+                const uint32_t kb_begin = pos % a.units_per_tile;
+                uint32_t kb_end = kb_begin + (u1 - pos);
+                if (kb_end > a.units_per_tile) kb_end = a.units_per_tile;
+                const uint32_t tb = seg % TB;
+                if (seg >= TB && !mbar_wait(&t_empty[tb], ((seg / TB) - 1) & 1u)) { ok = false; break; }
                 tc_fence_after();
-                const uint32_t sa = smem_u32(s_a + as * A_BYTES);
-                const uint32_t sb = smem_u32(s_b + bs * 2 * B_BYTES);
-                for (uint32_t blk = 0; blk < 2 && ok; ++blk) {
-                    const uint32_t v = u * 2 + blk, tb = v % TB;
-                    if (v >= TB && !mbar_wait(&t_empty[tb], ((v / TB) - 1) & 1u)) { ok = false; break; }
+                const uint32_t d_tmem = tmem_base + tb * M_PAD;
+                const uint32_t n_sub = (kb_end - kb_begin) * 4;
+                for (uint32_t j = 0; j < n_sub && ok; ++j, ++u) {
+                    const uint32_t as = u % AS, bs = u % BS;
+                    if (!mbar_wait(&a_full[as], (u / AS) & 1u) || !mbar_wait(&b_full[bs], (u / BS) & 1u)) { ok = false; break; }
                     tc_fence_after();
-                    const uint32_t d_tmem = tmem_base + tb * M_PAD;
+                    const uint32_t sa = smem_u32(s_a + as * 2 * A_BYTES);
+                    const uint32_t sb = smem_u32(s_b + bs * 2 * B_BYTES);
 #pragma unroll
-                    for (uint32_t kk = 0; kk < 2; ++kk) {
-                        const uint32_t off = (blk * 2 + kk) * UMMA_K * 2;
-                        const uint64_t da = make_desc_sw128(sa + off);
-                        umma_f16(d_tmem, da, make_desc_sw128(sb + off), idesc, kk);
-                        umma_f16(d_tmem, da, make_desc_sw128(sb + B_BYTES + off), idesc, 1u);
+                    for (uint32_t kk = 0; kk < BLOCK_K / UMMA_K; ++kk) {
+                        const uint32_t off = kk * UMMA_K * 2;
+                        const uint64_t a_hi = make_desc_sw128(sa + off), a_lo = make_desc_sw128(sa + A_BYTES + off);
+                        const uint64_t b_hi = make_desc_sw128(sb + off), b_lo = make_desc_sw128(sb + B_BYTES + off);
+                        umma_f16(d_tmem, a_hi, b_hi, idesc, (j | kk) != 0u);
+                        umma_f16(d_tmem, a_hi, b_lo, idesc, 1u);
+                        umma_f16(d_tmem, a_lo, b_hi, idesc, 1u);
                     }
-                    umma_commit(&t_full[tb]);
-                }
-                if (ok) {
                     umma_commit(&a_empty[as]);
                     umma_commit(&b_empty[bs]);
                 }
+                if (ok) umma_commit(&t_full[tb]);
+                pos += kb_end - kb_begin;
+                ++seg;
             }
             if (!ok) *abort_flag = 1;
         }
     } else {
-        // ---------------- workers: convert int8 -> f16 tiles, then scale-accumulate the block results
+        // ---------------- workers: warps 3..18; TMEM lane group = warp % 4, row quarter = (warp - 3) / 4
+        Q80Smem sm = {s_raw, s_a, raw_full, raw_empty, a_full, a_empty, t_full, t_empty, abort_flag};
         const uint32_t lane_group = warp & 3u;
-        const uint32_t r = lane_group * 32 + lane;  // weight row of the tile == TMEM lane
-        float acc[M_PAD];
-        float d_prev0 = 0.f, d_prev1 = 0.f;
-        bool ok = true;
-        uint32_t ucount = 0;  // sub-blocks handled so far by this CTA
-        // every wait of a worker warp is made warp-uniform so the warp-collective tcgen05.ld stays converged
-        auto wwait = [&](uint64_t* bar, uint32_t parity) {
-            const bool r0 = mbar_wait(bar, parity);
-            return (bool)__all_sync(0xffffffffu, r0);
-        };
-
-        auto accumulate = [&](uint32_t u, float d0, float d1) {
-#pragma unroll
-            for (uint32_t blk = 0; blk < 2; ++blk) {
-                const uint32_t v = u * 2 + blk, tb = v % TB;
-                if (!wwait(&t_full[tb], (v / TB) & 1u)) {
-                    ok = false;
-                    return;
-                }
-                tc_fence_after();
-                const float d = blk == 0 ? d0 : d1;
-#pragma unroll
-                for (uint32_t c = 0; c < M_PAD; c += 8) {
-                    float x[8];
-                    tmem_ld8(tmem_base + ((lane_group * 32u) << 16) + tb * M_PAD + c, x);
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) acc[c + j] = fmaf(d, x[j], acc[c + j]);
-                }
-                tc_fence_before();
-                mbar_arrive(&t_empty[tb]);
-            }
-        };
-
-        uint32_t pos = u0, seg = 0;
-        while (pos < u1 && ok) {
-            const uint32_t tile = pos / a.units_per_tile;
-            const uint32_t kb_begin = pos % a.units_per_tile;
-            uint32_t kb_end = kb_begin + (u1 - pos);
-            if (kb_end > a.units_per_tile) kb_end = a.units_per_tile;
-#pragma unroll
-            for (int m = 0; m < M_PAD; ++m) acc[m] = 0.0f;
-            const uint32_t seg_first = ucount;
-            for (uint32_t kb = kb_begin; kb < kb_end && ok; ++kb) {
-                const uint32_t i = ucount / 4, rs = i % RS;
-                if (!wwait(&raw_full[rs], (i / RS) & 1u)) { ok = false; break; }
-                const uint4* raw = reinterpret_cast<const uint4*>(s_raw + rs * RAW_BYTES + r * RAW_ROW_BYTES);
-#pragma unroll
-                for (uint32_t sub = 0; sub < 4; ++sub) {
-                    const uint32_t u = ucount, as = u % AS;
-                    if (u >= AS && !wwait(&a_empty[as], ((u / AS) - 1) & 1u)) { ok = false; break; }
-                    // 68 bytes of this row: {d0, q0[32], d1, q1[32]} = words W[0..16], starting at word 17*sub
-                    uint32_t buf[20];
-#pragma unroll
-                    for (int c = 0; c < 5; ++c) {
-                        const uint4 t = raw[4 * sub + c];
-                        buf[4 * c] = t.x; buf[4 * c + 1] = t.y; buf[4 * c + 2] = t.z; buf[4 * c + 3] = t.w;
-                    }
-                    const uint32_t* W = buf + sub;
-                    const float d0 = __half2float(__ushort_as_half((unsigned short)(W[0] & 0xffffu)));
-                    const float d1 = __half2float(__ushort_as_half((unsigned short)(W[8] >> 16)));
-                    unsigned char* dst = s_a + as * A_BYTES + (r >> 3) * 1024 + (r & 7u) * 128;
-                    const __half2 bias = __float2half2_rn(1152.0f);
-#pragma unroll
-                    for (uint32_t c = 0; c < 8; ++c) {
-                        uint32_t o[4];
-#pragma unroll
-                        for (uint32_t pp = 0; pp < 4; ++pp) {
-                            const uint32_t p = (c & 3u) * 4 + pp;  // pair index inside its Q8_0 block
-                            uint32_t word, upper;
-                            if (c < 4) { word = W[(p + 1) >> 1]; upper = (p & 1u) == 0u; }   // block 0: bytes 2 + 2p
-                            else { word = W[9 + (p >> 1)]; upper = (p & 1u) == 1u; }           // block 1: bytes 36 + 2p
-                            const uint32_t x = word ^ 0x80808080u;
-                            const uint32_t h = __byte_perm(x, 0x64646464u, upper ? 0x7362 : 0x5140);  // (1024+u0, 1024+u1)
-                            const __half2 q2 = __hsub2(*reinterpret_cast<const __half2*>(&h), bias);   // exact ints
-                            o[pp] = *reinterpret_cast<const uint32_t*>(&q2);
-                        }
-                        *reinterpret_cast<uint4*>(dst + ((c ^ (r & 7u)) * 16)) = make_uint4(o[0], o[1], o[2], o[3]);
-                    }
-                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                    mbar_arrive(&a_full[as]);
-                    if (u > seg_first) accumulate(u - 1, d_prev0, d_prev1);
-                    if (!ok) break;
-                    d_prev0 = d0;
-                    d_prev1 = d1;
-                    ++ucount;
-                }
-                if (!ok) break;
-                mbar_arrive(&raw_empty[rs]);
-            }
-            if (ok && ucount > seg_first) accumulate(ucount - 1, d_prev0, d_prev1);
-            if (ok) {
-                float* dst = a.partial + ((size_t)(blockIdx.x * a.seg_max + seg) * a.M) * BLOCK_N + r;
-#pragma unroll
-                for (int m = 0; m < M_PAD; ++m)
-                    if ((uint32_t)m < a.M) dst[(size_t)m * BLOCK_N] = acc[m];
-            }
-            (void)tile;
-            pos += kb_end - kb_begin;
-            ++seg;
+        switch ((warp - 3u) >> 2) {
+            case 0: q80_worker<M_PAD, 0>(a, sm, tmem_base, u0, u1, lane_group, lane); break;
+            case 1: q80_worker<M_PAD, 1>(a, sm, tmem_base, u0, u1, lane_group, lane); break;
+            case 2: q80_worker<M_PAD, 2>(a, sm, tmem_base, u0, u1, lane_group, lane); break;
+            default: q80_worker<M_PAD, 3>(a, sm, tmem_base, u0, u1, lane_group, lane); break;
         }
-        if (!ok) *abort_flag = 1;
     }
-    if (*abort_flag && threadIdx.x == 64) atomicOr(a.status, 4u);
+    if (*abort_flag && threadIdx.x == 96) atomicOr(a.status, 4u);
     tc_fence_before();
     __syncthreads();
     if (warp == 1) {
@@ -272,34 +312,48 @@ struct Q80EpiArgs {
     const float* residual[3];
     uint32_t N[3];
     uint32_t tile_begin[4];
-    uint32_t M, units_per_tile, units_total, ctas, seg_max, mode;
+    uint32_t M, units_per_tile, units_total, ctas, seg_max, mode, problems;
 };
 
-__device__ __forceinline__ float q80_tile_sum(const Q80EpiArgs& e, uint32_t tile, uint32_t m, uint32_t n_local) {
+// The CTAs whose spans hold a piece of `tile` are consecutive: [first, first + count). Only the first one can
+// have started in an earlier tile (its piece of this tile is its segment `seg_first`); the others start inside the
+// tile, so their piece is their segment 0. Every span is non-empty because ctas <= units_total.
+__device__ __forceinline__ void q80_tile_ctas(const Q80EpiArgs& e, uint32_t tile, uint32_t* first, uint32_t* count,
+                                              uint32_t* seg_first) {
     const uint32_t t0 = tile * e.units_per_tile, t1 = t0 + e.units_per_tile;
-    // first CTA whose span reaches into this tile
     uint32_t c = (uint32_t)(((uint64_t)t0 * e.ctas) / e.units_total);
-    while (c > 0 && (uint32_t)(((uint64_t)c * e.units_total) / e.ctas) > t0) --c;
     while ((uint32_t)(((uint64_t)(c + 1) * e.units_total) / e.ctas) <= t0) ++c;
-    float acc = 0.0f;
-    for (; c < e.ctas; ++c) {
-        const uint32_t u0 = (uint32_t)(((uint64_t)c * e.units_total) / e.ctas);
-        const uint32_t u1 = (uint32_t)(((uint64_t)(c + 1) * e.units_total) / e.ctas);
-        if (u0 >= t1) break;
-        if (u1 <= t0 || u1 == u0) continue;
-        const uint32_t seg = tile - u0 / e.units_per_tile;  // this tile's position among the CTA's tiles
-        acc += e.partial[((size_t)(c * e.seg_max + seg) * e.M + m) * BLOCK_N + n_local];
+    *first = c;
+    *seg_first = tile - (uint32_t)(((uint64_t)c * e.units_total) / e.ctas) / e.units_per_tile;
+    uint32_t n = 0;
+    while (c < e.ctas && (uint32_t)(((uint64_t)c * e.units_total) / e.ctas) < t1) {
+        ++c;
+        ++n;
     }
-    return acc;
+    *count = n;
 }
 
-__global__ void gemm_tc_q80_epilogue_kernel(Q80EpiArgs e) {
-    const uint32_t p = blockIdx.z, m = blockIdx.y;
-    const uint32_t n = blockIdx.x * blockDim.x + threadIdx.x;
+// grid (tiles of the widest problem, M, problems or 1), block 128 = one tile row per thread.
+__global__ void __launch_bounds__(128) gemm_tc_q80_epilogue_kernel(Q80EpiArgs e) {
+    __shared__ uint32_t first[2], count[2], seg0[2];
+    const uint32_t p = blockIdx.z, m = blockIdx.y, t = blockIdx.x;
+    const uint32_t n = t * BLOCK_N + threadIdx.x;
+    if (t * BLOCK_N >= e.N[p]) return;
+    if (threadIdx.x == 0) q80_tile_ctas(e, e.tile_begin[p] + t, &first[0], &count[0], &seg0[0]);
+    if (threadIdx.x == 32 && e.mode == 1) q80_tile_ctas(e, e.tile_begin[1] + t, &first[1], &count[1], &seg0[1]);
+    __syncthreads();
     if (n >= e.N[p]) return;
-    float acc = q80_tile_sum(e, e.tile_begin[p] + n / BLOCK_N, m, n % BLOCK_N);
+    auto tile_sum = [&](int w) {
+        float acc = 0.0f;
+        for (uint32_t i = 0; i < count[w]; ++i) {
+            const size_t slot = (size_t)(first[w] + i) * e.seg_max + (i == 0 ? seg0[w] : 0u);
+            acc += e.partial[(slot * e.M + m) * BLOCK_N + threadIdx.x];
+        }
+        return acc;
+    };
+    float acc = tile_sum(0);
     if (e.mode == 1) {
-        const float up = q80_tile_sum(e, e.tile_begin[1] + n / BLOCK_N, m, n % BLOCK_N);
+        const float up = tile_sum(1);
         e.out[0][(size_t)m * e.N[0] + n] = (acc / (1.0f + expf(-acc))) * up;
         return;
     }
@@ -363,7 +417,7 @@ __global__ void split_activations_q80_kernel(const float* __restrict__ x, __half
 template <int M_PAD>
 int launch_q80(M40llmCudaContext* ctx, cudaStream_t s, const CUtensorMap* mW, const CUtensorMap& mXh,
                const CUtensorMap& mXl, const Q80Args& a) {
-    constexpr size_t smem = RS * RAW_BYTES + AS * A_BYTES + BS * 2 * (M_PAD * BLOCK_K * 2) + 32 * 8 + 16 + 1024;
+    constexpr size_t smem = RS * RAW_BYTES + AS * 2 * A_BYTES + b_slots(M_PAD) * 2 * (M_PAD * BLOCK_K * 2) + 32 * 8 + 16 + 1024;
     auto kern = gemm_tc_q80_kernel<M_PAD>;
     static unsigned long long configured = 0ull;
     const unsigned long long bit = 1ull << (ctx->device_id & 63);
@@ -371,7 +425,7 @@ int launch_q80(M40llmCudaContext* ctx, cudaStream_t s, const CUtensorMap* mW, co
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return -2;
         configured |= bit;
     }
-    kern<<<a.ctas, 192, smem, s>>>(mW[0], mW[1], mW[2], mXh, mXl, a);
+    kern<<<a.ctas, CTA_THREADS, smem, s>>>(mW[0], mW[1], mW[2], mXh, mXl, a);
     M40_COUNT_LAUNCH(ctx);
     return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
@@ -452,8 +506,9 @@ int m40_gemm_tc_q80(M40llmCudaContext* ctx, cudaStream_t s, uint32_t stream_kind
     e.ctas = a.ctas;
     e.seg_max = a.seg_max;
     e.mode = (uint32_t)mode;
-    dim3 egrid((maxN + 255) / 256, (unsigned)M, mode == 1 ? 1u : (unsigned)problems);
-    gemm_tc_q80_epilogue_kernel<<<egrid, 256, 0, s>>>(e);
+    e.problems = (uint32_t)problems;
+    dim3 egrid((maxN + BLOCK_N - 1) / BLOCK_N, (unsigned)M, mode == 1 ? 1u : (unsigned)problems);
+    gemm_tc_q80_epilogue_kernel<<<egrid, 128, 0, s>>>(e);
     M40_COUNT_LAUNCH(ctx);
     return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
