@@ -40,6 +40,7 @@ EPS, THETA = 1e-5, 500000.0
 N_WEIGHT_SETS = 2  # rotated between steps so no weight byte survives in L2 from one step to the next
 # Traffic of the dominant kernel from the committed ncu capture (profiles/): DRAM bytes per algorithmic byte.
 NCU_TRAFFIC_RATIO = None
+CPU_BASELINE_SECONDS = 12.0  # wall time spent in the oracle for the cpu_baseline leg
 
 
 def layer_weight_bytes():
@@ -83,7 +84,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}",
-                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                          "--format=csv,noheader,nounits", "-lms", "20"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._read, daemon=True).start()
         except Exception:
@@ -91,9 +92,17 @@ class ClockSampler:
 
     def _read(self):
         for line in self.proc.stdout:
-            self.rows.append([c.strip() for c in line.split(",")])
+            self.rows.append([c.strip() for c in line.split(",")] + [time.perf_counter()])
 
-    def stop(self):
+    def wait_first_sample(self, timeout=5.0):
+        t0 = time.perf_counter()
+        while not self.rows and time.perf_counter() - t0 < timeout:
+            time.sleep(0.01)
+
+    def mark(self):
+        return time.perf_counter()
+
+    def stop(self, t_begin=None, t_end=None):
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         self.proc.terminate()
@@ -101,10 +110,14 @@ class ClockSampler:
             self.proc.wait(timeout=5)
         except Exception:
             self.proc.kill()
-        sm = [float(r[0]) for r in self.rows if len(r) >= 6 and r[0].replace(".", "").isdigit()]
-        mx = [float(r[1]) for r in self.rows if len(r) >= 6 and r[1].replace(".", "").isdigit()]
+        rows = self.rows
+        if t_begin is not None:  # samples taken while the timed loop ran (one sample of slack either side)
+            inside = [r for r in rows if t_begin - 0.03 <= r[-1] <= t_end + 0.03]
+            rows = inside or rows[-3:]
+        sm = [float(r[0]) for r in rows if len(r) >= 7 and r[0].replace(".", "").isdigit()]
+        mx = [float(r[1]) for r in rows if len(r) >= 7 and r[1].replace(".", "").isdigit()]
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        reasons = sorted({names[i] for r in self.rows if len(r) >= 6 for i in range(4) if r[2 + i].lower().startswith("active")})
+        reasons = sorted({names[i] for r in rows if len(r) >= 7 for i in range(4) if r[2 + i].lower().startswith("active")})
         return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
                 "reasons": reasons, "samples": len(sm)}
 
@@ -202,24 +215,43 @@ def launches(nat):
     return int(n.value)
 
 
-def cpu_layer_sample(O, sets, x, lens, seqs, threads=None):
-    """Oracle layer for a few sequences of the batch; returns (seconds, tokens)."""
-    if threads:
-        O.set_num_threads(threads)
-    cfg = O.LayerCfg(H, QH, KVH, HD, F, 1, 0, EPS, THETA, 1.0)
-    rng = np.random.default_rng(1234)
-    caches = []
-    for b in seqs:
-        n = int(lens[b])
-        k, v = kv_for_sequence(rng, n)
-        K = np.zeros((n + 1, KVH, HD), np.float16)
-        V = np.zeros((n + 1, KVH, HD), np.float16)
-        K[:n], V[:n] = k, v
-        caches.append((K, V))
-    t0 = time.perf_counter()
-    for i, b in enumerate(seqs):
-        O.decode_layer(cfg, x[b], sets[0], caches[i][0], caches[i][1], int(lens[b]))
-    return time.perf_counter() - t0, len(seqs)
+def workload_config(att_lens, world):
+    """The `config` object both arms print: BASELINE.json configs[2], the configuration the metric is quoted on."""
+    sb = step_bytes(att_lens)
+    return {"workload": "llama3-8b-shaped decode layer, batch 32 varlen [512,8192], q8_0 FFN (BASELINE configs[2])",
+            "hidden": H, "q_heads": QH, "kv_heads": KVH, "head_dim": HD, "ffn": F, "batch_per_gpu": B,
+            "context_sum": int(np.sum(att_lens)), "parallelism": f"independent sequences x{world}",
+            "l2": f"inputs larger than L2: {sb / 1e6:.0f} MB per step, {N_WEIGHT_SETS} weight sets rotated"}
+
+
+class CpuLayer:
+    """Oracle layer over a bounded sample of the batch: the first `n_seq` sequences, caches built once."""
+
+    def __init__(self, O, sets, x, lens, n_seq=8):
+        self.O, self.sets, self.x, self.lens = O, sets, x, lens
+        self.cfg = O.LayerCfg(H, QH, KVH, HD, F, 1, 0, EPS, THETA, 1.0)
+        rng = np.random.default_rng(1234)
+        self.seqs = list(range(min(n_seq, len(lens))))
+        self.caches = []
+        for b in self.seqs:
+            n = int(lens[b])
+            k, v = kv_for_sequence(rng, n)
+            K = np.zeros((n + 1, KVH, HD), np.float16)
+            V = np.zeros((n + 1, KVH, HD), np.float16)
+            K[:n], V[:n] = k, v
+            self.caches.append((K, V))
+
+    def step(self, i):
+        """One sequence's layer-step; returns seconds."""
+        j = i % len(self.seqs)
+        b = self.seqs[j]
+        t0 = time.perf_counter()
+        self.O.decode_layer(self.cfg, self.x[b], self.sets[0], self.caches[j][0], self.caches[j][1], int(self.lens[b]))
+        return time.perf_counter() - t0
+
+    def describe(self):
+        c = [int(self.lens[b]) for b in self.seqs]
+        return f"oracle layer, one sequence per call, cycling the first {len(c)} of the {B} sequences (contexts {min(c)}..{max(c)})"
 
 
 def run_reference_arm(args, rank, world):
@@ -230,22 +262,21 @@ def run_reference_arm(args, rank, world):
     from oracle import oracle as O
     lens, sets, x = make_inputs(O, 0)
     cores = O.num_threads()
-    seqs = [0]
+    cpu = CpuLayer(O, sets, x, lens)
     times = []
     for i in range(args.warmup + args.steps):
-        dt, n = cpu_layer_sample(O, sets, x, lens, seqs)
+        dt = cpu.step(i)
         if i >= args.warmup:
-            times.append(dt / n)
+            times.append(dt)
     per_tok = float(np.mean(times))
     val = 1.0 / per_tok
     line = {
         "impl": "reference", "metric": "decode_layer_tokens_per_s", "value": val, "unit": "tokens/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": per_tok * 1e3, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f16 storage / q8_0 / f32 compute", "data": "synthetic",
-        "config": {"workload": "llama3-8b-shaped decode layer, batch 32 varlen [512,8192], q8_0 FFN",
-                   "hidden": H, "q_heads": QH, "kv_heads": KVH, "head_dim": HD, "ffn": F, "batch": B},
+        "config": workload_config(lens + 1, world),
         "cpu_baseline": {"value": val, "unit": "tokens/s", "cores": cores, "kind": "port",
-                         "sample": f"oracle layer for 1 of the {B} sequences per step (context {int(lens[0])}), OpenMP over rows/heads"},
+                         "sample": cpu.describe() + ", one call per step, OpenMP over rows/heads"},
         "e2e": {"value": val, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -255,7 +286,7 @@ def run_reference_arm(args, rank, world):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--steps", type=int, default=1000)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -311,18 +342,21 @@ def main():
             dist.barrier()
 
     # ---------------- device-resident timing
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    sampler.wait_first_sample()
     for i in range(args.warmup):
         assert L.m40llm_cuda_graph_launch(ctx, graphs[i % N_WEIGHT_SETS], 1) == 0
     barrier()
-    sampler = ClockSampler(local_rank)
-    sampler.start()
     n0 = launches(nat)
+    t_begin = sampler.mark()
     ev.start()
     for i in range(args.steps):
         assert L.m40llm_cuda_graph_launch(ctx, graphs[i % N_WEIGHT_SETS], 1) == 0
     ms_total = ev.stop_ms()
+    t_end = sampler.mark()
     barrier()
-    clocks = sampler.stop()
+    clocks = sampler.stop(t_begin, t_end)
     # kernels per graph replay = kernels enqueued by one eager step
     n1 = launches(nat)
     layer.enqueue(0)
@@ -336,7 +370,7 @@ def main():
     nat.sync(1)
     # between timed launches the other sequences' KV (570 MB per pass) evicts any reuse: input > L2
     ev.start()
-    reps = max(10, args.steps)
+    reps = max(10, min(args.steps, 100))
     for _ in range(reps):
         layer.attention_only()
     attn_ms = ev.stop_ms() / reps
@@ -344,25 +378,35 @@ def main():
     peak, peak_kind = measured_peak_gbs()
     attn_gbs = attn_bytes / (attn_ms * 1e-3) / 1e9
 
-    # ---------------- end to end through the ABI with host buffers
+    # ---------------- end to end: the host-side layer driver (C++ mirror of the reference's batched layer forward)
+    # with HOST buffers. Per step it uploads the batch plan and the activations from pinned memory, runs the layer
+    # (graph replay after the first sight of a configuration), synchronises and copies the result back.
+    host = pkg.host
+    hl = host.DecodeLayer(ctx, host.LayerCfg(H, QH, KVH, HD, F, 0, EPS, THETA, 1.0), B)
+    hw = []
+    for d in dw:
+        W = host.Weights()
+        for n in ("attn_norm", "ffn_norm", "wq", "wk", "wv", "wo", "wg", "wu", "wd"):
+            setattr(W, n, d[n].ptr)
+        W.ffn_q80 = 1
+        hw.append(W)
+    kvcfg = host.dense_kv_cfg()
     hx = torch.from_numpy(x).pin_memory()
     hout = torch.empty((B, H), dtype=torch.float32).pin_memory()
-    hids = torch.from_numpy(ids.astype(np.int32)).pin_memory()
-    hpos = torch.from_numpy(pos.astype(np.int32)).pin_memory()
-    hlens = torch.from_numpy(att_lens.astype(np.int32)).pin_memory()
+    rid = np.arange(B, dtype=np.uint64)
+    sid = ids.copy()
+    kvl = att_lens.astype(np.uint32)
+    act = np.ones(B, np.uint32)
+    vp = lambda a: a.ctypes.data_as(C.c_void_p)
     h2d = hx.numel() * 4 + 3 * B * 4
     d2h = hout.numel() * 4
 
     def e2e_step(i):
-        assert L.m40llm_memcpy_h2d(ctx, layer.dx.ptr, hx.data_ptr(), hx.numel() * 4) == 0
-        assert L.m40llm_memcpy_h2d(ctx, layer.dids.ptr, hids.data_ptr(), B * 4) == 0
-        assert L.m40llm_memcpy_h2d(ctx, layer.dpos.ptr, hpos.data_ptr(), B * 4) == 0
-        assert L.m40llm_memcpy_h2d(ctx, layer.dlens.ptr, hlens.data_ptr(), B * 4) == 0
-        assert L.m40llm_cuda_graph_launch(ctx, graphs[i % N_WEIGHT_SETS], 1) == 0
-        assert L.m40llm_stream_synchronize(ctx, 1) == 0
-        assert L.m40llm_memcpy_d2h(ctx, hout.data_ptr(), layer.dout.ptr, d2h) == 0
+        rc = hl.forward_host_raw(kv, hw[i % N_WEIGHT_SETS], kvcfg, B, vp(rid), vp(sid), vp(kvl), vp(act),
+                                 C.c_void_p(hx.data_ptr()), C.c_void_p(hout.data_ptr()), True)
+        assert rc == 0, (rc, host.last_error())
 
-    for i in range(args.warmup):
+    for i in range(max(args.warmup, 2 * N_WEIGHT_SETS)):
         e2e_step(i)
     barrier()
     t0 = time.perf_counter()
@@ -370,6 +414,7 @@ def main():
         e2e_step(i)
     nat.sync()
     e2e_s = (time.perf_counter() - t0) / args.steps
+    e2e_replays = hl.graph_replays()
 
     if dist is not None:
         t = torch.tensor([ms_step, e2e_s], device="cuda", dtype=torch.float64)
@@ -404,10 +449,14 @@ def main():
     # ---------------- CPU baseline (rank 0, N = 1): the oracle on a bounded sample of this batch
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        seqs = [int(np.argmin(lens))]
-        dt, n = cpu_layer_sample(O, sets, x, lens, seqs)
-        cpu = {"value": n / dt, "unit": "tokens/s", "cores": O.num_threads(), "kind": "port",
-               "sample": f"oracle layer for {n} of the {B} sequences (context {int(lens[seqs[0]])}), {dt:.1f} s of wall time"}
+        cl = CpuLayer(O, sets, x, lens)
+        cl.step(0)
+        spent, n = 0.0, 0
+        while spent < CPU_BASELINE_SECONDS:
+            spent += cl.step(n)
+            n += 1
+        cpu = {"value": n / spent, "unit": "tokens/s", "cores": O.num_threads(), "kind": "port",
+               "sample": cl.describe() + f", {n} calls in {spent:.1f} s"}
 
     if rank == 0:
         sb = step_bytes(att_lens)
@@ -416,17 +465,15 @@ def main():
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "f16 storage / q8_0 / f32 compute", "data": "synthetic",
-            "config": {"workload": "llama3-8b-shaped decode layer, batch 32 varlen [512,8192], q8_0 FFN (BASELINE configs[2])",
-                       "hidden": H, "q_heads": QH, "kv_heads": KVH, "head_dim": HD, "ffn": F, "batch_per_gpu": B,
-                       "context_sum": int(att_lens.sum()), "parallelism": f"independent sequences x{world}",
-                       "l2": f"inputs larger than L2: {sb / 1e6:.0f} MB per step, {N_WEIGHT_SETS} weight sets rotated"},
+            "config": workload_config(att_lens, world),
             "step_algorithmic_bytes": sb, "step_achieved_gbs": sb / (ms_step * 1e-3) / 1e9,
             "step_frac_of_hbm_peak": sb / (ms_step * 1e-3) / 1e9 / peak,
             "roofline": {"kernel": "batched decode attention (attention + split merge)", "bound": "hbm",
                          "achieved": attn_gbs, "peak": peak, "unit": "GB/s", "frac": attn_gbs / peak,
                          "peak_kind": f"of {peak_kind}", "algorithmic_bytes": attn_bytes, "ms_per_launch": attn_ms,
                          "traffic": None if NCU_TRAFFIC_RATIO is None else NCU_TRAFFIC_RATIO * attn_bytes},
-            "e2e": {"value": world * B / e2e_s, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+            "e2e": {"value": world * B / e2e_s, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "graph_replays": e2e_replays},
             "gpu_launches": per_step_launches * args.steps,
             "clocks": clocks,
         }
@@ -434,6 +481,7 @@ def main():
         if cpu is not None:
             line["cpu_baseline"] = cpu
         print(json.dumps(line), flush=True)
+    hl.close()
     for g in graphs:
         L.m40llm_cuda_graph_destroy(g)
     L.m40llm_kvcache_destroy(kv)

@@ -60,7 +60,26 @@ def build(force: bool = False, verbose: bool = False) -> str:
         if r.returncode != 0:
             sys.stderr.write(r.stdout + r.stderr)
             raise RuntimeError("link failed")
+    build_host(force or bool(jobs))
     return LIB
+
+
+HOST_LIB = os.path.join(HERE, "libm40llm_host.so")
+
+
+def build_host(force: bool = False) -> str:
+    """The C++ host mirror (decode layer driver, batch plan, KV compression config); calls the C ABI only."""
+    srcs = sorted(glob.glob(os.path.join(HERE, "host", "*.cpp")))
+    deps = sorted(glob.glob(os.path.join(HERE, "host", "*.hpp"))) + [os.path.join(HERE, "..", "include", "m40llm_native.h")]
+    if force or not os.path.exists(HOST_LIB) or any(os.path.getmtime(p) > os.path.getmtime(HOST_LIB) for p in srcs + deps):
+        cxx = "/usr/bin/g++" if os.path.exists("/usr/bin/g++") else "g++"
+        cmd = [cxx, "-O2", "-std=c++17", "-fPIC", "-shared", "-o", HOST_LIB, *srcs, "-L" + HERE, "-lm40llm_native",
+               "-Wl,-rpath,$ORIGIN"]
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode != 0:
+            sys.stderr.write(r.stdout + r.stderr)
+            raise RuntimeError("host library build failed")
+    return HOST_LIB
 
 
 if __name__ == "__main__":
