@@ -254,6 +254,34 @@ class CpuLayer:
         return f"oracle layer, one sequence per call, cycling the first {len(c)} of the {B} sequences (contexts {min(c)}..{max(c)})"
 
 
+def attention_only_case(nat, args):
+    """The dominant kernel on a small batch (KV larger than L2, well under 1 GB on the device): the case the
+    committed profiler summaries are taken on. Prints its own one-line summary, not the bench line."""
+    n = args.attention_only
+    rng = np.random.default_rng(0)
+    lens = rng.integers(LMIN, LMAX + 1, size=B).astype(np.uint32)[:n]
+    kv = nat.kv_dense(LMAX + 8, n, KVH, HD)
+    for b in range(n):
+        k, v = kv_for_sequence(rng, int(lens[b]))
+        nat.kv_fill(kv, b, k, v)
+    layer = Layer(nat, kv, None, n)
+    layer.dq.upload(rng.standard_normal((n, QH * HD), dtype=np.float32))
+    layer.dids.upload(np.arange(n, dtype=np.uint32))
+    layer.dlens.upload(lens)
+    ev = Events(nat)
+    for _ in range(3):
+        layer.attention_only()
+    nat.sync(1)
+    ev.start()
+    for _ in range(args.steps):
+        layer.attention_only()
+    ms = ev.stop_ms() / args.steps
+    by = attention_bytes(lens)
+    print(json.dumps({"case": "attention_only", "sequences": n, "context_sum": int(lens.sum()),
+                      "algorithmic_bytes": by, "ms_per_launch": ms, "achieved_gbs": by / ms / 1e6}), flush=True)
+    nat.lib.m40llm_kvcache_destroy(kv)
+
+
 def run_reference_arm(args, rank, world):
     """`--impl reference`: the reference's CPU path is Rust and cannot be built here (no cargo/rustc, no network),
     so the timed stand-in is the oracle port of that math, on all host threads. Rank 0 only."""
@@ -290,6 +318,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--attention-only", type=int, default=0, metavar="N",
+                    help="small case for a profiler: the batched attention call alone over the first N sequences")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     rank = int(os.environ.get("RANK", "0"))
@@ -312,6 +342,9 @@ def main():
     nat = helpers.Native(pkg.native.lib(), device=local_rank)
     L, ctx = nat.lib, nat.ctx
 
+    if args.attention_only:
+        attention_only_case(nat, args)
+        return
     lens, sets, x = make_inputs(O, rank)
     dw = [{n: nat.buf(a) for n, a in w.items()} for w in sets]
     kv = nat.kv_dense(LMAX + 8, B, KVH, HD)

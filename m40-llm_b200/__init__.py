@@ -8,3 +8,11 @@ directory name), so harnesses load it by path:
                                                   submodule_search_locations=[".../m40-llm_b200"])
 """
 from . import host, native  # noqa: F401
+
+
+def __getattr__(name):
+    # `splitk` needs torch.distributed; loaded on first use so that the ctypes-only modules import without torch.
+    if name == "splitk":
+        import importlib
+        return importlib.import_module(".splitk", __name__)
+    raise AttributeError(name)

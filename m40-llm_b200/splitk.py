@@ -1,0 +1,248 @@
+"""Multi-GPU plumbing of the decode path: one process per GPU, `torch.distributed` for the exchange.
+
+Two ways the path shards (one 8-GPU box):
+
+* batched variable-length decode: independent sequences are dealt to ranks (`shard_sequences`); no data-path
+  collective at all;
+* one long sequence, split-K: every rank owns a contiguous range of the sequence's KV blocks, computes an
+  unnormalised (max, sum, out) triple per q head over its range and the triples are all-gathered and merged. With
+  the compressed cache (FP16 K / q4 V, top-k block selection) there is one more exchange before that: ranks
+  all-gather the block scores of their ranges so that every rank derives the same global top-k list.
+
+The exchange payloads are tiny (Qwen2.5-3B shape at 32K context: 16 heads x 504 scores = 32 KB; triples 16 x 130
+floats = 8 KB per rank), so they go through the library collective (NCCL over NVLink on GPUs, gloo on CPU ranks).
+Gathered data always lands in the receiving rank's own memory before a kernel reads it.
+
+The compute legs are callables so that the same orchestration runs over the CUDA entry points (`NativeLegs`, the
+product) and over any other implementation of the legs (the CPU tests pass a numpy restatement and run two gloo
+ranks). Nothing here falls back to a CPU computation by itself.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+from typing import Callable, Sequence
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+EMPTY_BLOCK = 0xFFFFFFFF
+MAX_TOP_BLOCKS = 64          # slots per q head in a block list (the reference's cap, cuda/kernels.cu:2861-2930)
+SCORE_FLOOR = -1.0e30        # scores at or below this are never selected
+
+
+# ----------------------------------------------------------------------------- plans (pure host logic)
+def block_ranges(n_blocks: int, world: int) -> list[tuple[int, int]]:
+    """Contiguous, balanced block ranges [begin, end) for ranks 0..world-1 (sizes differ by at most one,
+    larger ranges first; ranks beyond n_blocks get empty ranges)."""
+    if n_blocks < 0 or world <= 0:
+        raise ValueError("n_blocks must be >= 0 and world > 0")
+    base, extra = divmod(n_blocks, world)
+    out, b = [], 0
+    for r in range(world):
+        n = base + (1 if r < extra else 0)
+        out.append((b, b + n))
+        b += n
+    return out
+
+
+def token_ranges(seq_len: int, world: int, align: int = 64) -> list[tuple[int, int]]:
+    """Token ranges for dense split-K: whole `align`-token tiles per rank, the ragged tail on the last non-empty
+    rank."""
+    tiles = (seq_len + align - 1) // align
+    return [(min(b * align, seq_len), min(e * align, seq_len)) for b, e in block_ranges(tiles, world)]
+
+
+def shard_sequences(context_lens: Sequence[int], world: int) -> list[list[int]]:
+    """Deals independent sequences to ranks, longest first onto the least-loaded rank (decode attention cost is
+    linear in context length). Returns the sequence indices of every rank, each list in ascending order."""
+    loads = [0] * world
+    out: list[list[int]] = [[] for _ in range(world)]
+    order = sorted(range(len(context_lens)), key=lambda i: (-int(context_lens[i]), i))
+    for i in order:
+        r = min(range(world), key=lambda j: (loads[j], j))
+        out[r].append(i)
+        loads[r] += int(context_lens[i])
+    return [sorted(s) for s in out]
+
+
+def select_global_topk(scores: np.ndarray, top_blocks: int) -> np.ndarray:
+    """Global block list per q head from the gathered scores [q_heads, n_blocks] (f32): the `top_blocks` highest
+    scores in descending order, ties to the lower block index, NaN and scores <= -1e30 never selected, unused
+    slots EMPTY_BLOCK. Same rule as the single-GPU selection (cuda/kernels.cu:2861-2930, 6526-6600), so every rank
+    derives the identical list without a further exchange."""
+    if not 1 <= top_blocks <= MAX_TOP_BLOCKS:
+        raise ValueError(f"top_blocks must be in 1..{MAX_TOP_BLOCKS}")
+    scores = np.asarray(scores, dtype=np.float32)
+    q_heads, nb = scores.shape
+    out = np.full((q_heads, MAX_TOP_BLOCKS), EMPTY_BLOCK, dtype=np.uint32)
+    for h in range(q_heads):
+        s = scores[h]
+        ok = np.flatnonzero(~np.isnan(s) & (s > np.float32(SCORE_FLOOR)))
+        # stable sort of the negated scores keeps the lower index first among equals
+        order = ok[np.argsort(-s[ok], kind="stable")][:top_blocks]
+        out[h, :order.size] = order.astype(np.uint32)
+    return out
+
+
+def merge_triples(m: np.ndarray, l: np.ndarray, o: np.ndarray) -> np.ndarray:
+    """Host statement of the merge the device kernel performs (for plans and tests; the product merges on the
+    GPU): m, l [parts, heads], o [parts, heads, hd] unnormalised -> out [heads * hd]. Parts with l == 0 are
+    empty."""
+    m = np.asarray(m, np.float32)
+    l = np.asarray(l, np.float32)
+    o = np.asarray(o, np.float32)
+    live = l > 0
+    mm = np.where(live, m, -np.inf).max(axis=0)                       # [heads]
+    w = np.where(live, np.exp((m - mm[None, :]).astype(np.float32)), np.float32(0))
+    den = (w * l).sum(axis=0)
+    num = (w[:, :, None] * o).sum(axis=0)
+    out = np.where(den[:, None] > 0, num / np.maximum(den[:, None], np.float32(1e-38)), np.float32(0))
+    return out.astype(np.float32).reshape(-1)
+
+
+# ----------------------------------------------------------------------------- exchange
+def _world(group) -> tuple[int, int]:
+    return dist.get_rank(group), dist.get_world_size(group)
+
+
+def gather_scores(local: torch.Tensor, ranges: Sequence[tuple[int, int]], group=None) -> torch.Tensor:
+    """All-gathers the per-rank score slabs [q_heads, end-begin] into the full [q_heads, n_blocks] matrix on every
+    rank. Slabs are padded to the widest range so that one fixed-size all-gather does it."""
+    rank, world = _world(group)
+    q_heads = local.shape[0]
+    widest = max(max(e - b for b, e in ranges), 1)
+    b, e = ranges[rank]
+    assert local.shape == (q_heads, e - b), (tuple(local.shape), ranges[rank])
+    send = torch.full((q_heads, widest), float("-inf"), dtype=torch.float32, device=local.device)
+    send[:, :e - b] = local
+    # output = the ranks' slabs concatenated along dim 0 (the form both NCCL and gloo accept)
+    recv = torch.empty((world * q_heads, widest), dtype=torch.float32, device=local.device)
+    dist.all_gather_into_tensor(recv, send, group=group)
+    recv = recv.view(world, q_heads, widest)
+    n_blocks = ranges[-1][1]
+    full = torch.empty((q_heads, n_blocks), dtype=torch.float32, device=local.device)
+    for r, (rb, re) in enumerate(ranges):
+        full[:, rb:re] = recv[r, :, :re - rb]
+    return full
+
+
+def gather_triples(m: torch.Tensor, l: torch.Tensor, o: torch.Tensor, group=None):
+    """All-gathers one rank's triples (m, l [heads]; o [heads, hd]) as ONE message per rank; returns
+    (m [world, heads], l [world, heads], o [world, heads, hd]), each contiguous."""
+    _, world = _world(group)
+    heads, hd = o.shape
+    send = torch.cat([m.reshape(heads, 1), l.reshape(heads, 1), o], dim=1).contiguous()
+    recv = torch.empty((world * heads, hd + 2), dtype=torch.float32, device=o.device)
+    dist.all_gather_into_tensor(recv, send, group=group)
+    recv = recv.view(world, heads, hd + 2)
+    return recv[:, :, 0].contiguous(), recv[:, :, 1].contiguous(), recv[:, :, 2:].contiguous()
+
+
+# ----------------------------------------------------------------------------- orchestration
+@dataclass
+class Legs:
+    """The compute legs of one rank. `score(b0, b1) -> [q_heads, b1-b0]` f32 tensor; `attend_blocks(blocks
+    [q_heads, 64] u32 ndarray, b0, b1, include_recent) -> (m, l, o)` tensors; `attend_tokens(t0, t1) -> (m, l, o)`
+    for the dense cache; `merge(m, l, o) -> out [heads*hd]` tensor."""
+    score: Callable | None
+    attend_blocks: Callable | None
+    attend_tokens: Callable | None
+    merge: Callable
+
+
+def compressed_split_k(legs: Legs, n_old_blocks: int, top_blocks: int, group=None):
+    """One long sequence over the FP16-K / q4-V cache: score own blocks -> all-gather scores -> global top-k ->
+    attend own selected blocks (the last rank adds the recent ring) -> all-gather triples -> merge. Every rank
+    returns the full attention output and the block list."""
+    rank, world = _world(group)
+    ranges = block_ranges(n_old_blocks, world)
+    b0, b1 = ranges[rank]
+    scores = gather_scores(legs.score(b0, b1), ranges, group)
+    blocks = select_global_topk(scores.cpu().numpy(), top_blocks)
+    m, l, o = legs.attend_blocks(blocks, b0, b1, rank == world - 1)
+    gm, gl, go = gather_triples(m, l, o, group)
+    return legs.merge(gm, gl, go), blocks
+
+
+def dense_split_k(legs: Legs, seq_len: int, group=None):
+    """One long sequence over the dense FP16 cache: attend own token range -> all-gather triples -> merge."""
+    rank, world = _world(group)
+    t0, t1 = token_ranges(seq_len, world)[rank]
+    m, l, o = legs.attend_tokens(t0, t1)
+    gm, gl, go = gather_triples(m, l, o, group)
+    return legs.merge(gm, gl, go)
+
+
+class NativeLegs:
+    """The legs over the CUDA library's split-K entry points. `lib` is the loaded C ABI (ctypes), `ctx`/`kv` its
+    handles; `q` is a CUDA f32 tensor [q_heads * head_dim]. Kernels run on the context's decode stream, the
+    collectives on torch's stream: each leg synchronises its stream before handing a tensor to the other side."""
+
+    def __init__(self, lib, ctx, kv, q: torch.Tensor, q_heads: int, head_dim: int, seq_id: int, seq_len: int):
+        if not q.is_cuda:
+            raise RuntimeError("NativeLegs needs CUDA tensors: the library has no CPU path")
+        self.lib, self.ctx, self.kv, self.q = lib, ctx, kv, q.contiguous()
+        self.qh, self.hd, self.seq, self.len = q_heads, head_dim, seq_id, seq_len
+        self.dev = q.device
+
+    def _p(self, t: torch.Tensor):
+        return C.c_void_p(t.data_ptr())
+
+    def _sync(self):
+        rc = self.lib.m40llm_stream_synchronize(self.ctx, 1)
+        if rc != 0:
+            raise RuntimeError(f"m40llm_stream_synchronize failed: {rc}")
+
+    def _triples(self):
+        z = lambda *s: torch.empty(s, dtype=torch.float32, device=self.dev)
+        return z(self.qh), z(self.qh), z(self.qh, self.hd)
+
+    def score(self, b0: int, b1: int) -> torch.Tensor:
+        out = torch.empty((self.qh, b1 - b0), dtype=torch.float32, device=self.dev)
+        torch.cuda.current_stream(self.dev).synchronize()
+        if b1 > b0:
+            rc = self.lib.m40llm_kvcache_score_old_blocks_async(self.ctx, self.kv, self.seq, self._p(self.q), self.qh,
+                                                                self.len, b0, b1, self._p(out))
+            if rc != 0:
+                raise RuntimeError(f"m40llm_kvcache_score_old_blocks_async failed: {rc}")
+            self._sync()
+        return out
+
+    def attend_blocks(self, blocks: np.ndarray, b0: int, b1: int, include_recent: bool):
+        m, l, o = self._triples()
+        # u32 block ids travel as their int32 bit patterns (torch has no general uint32 arithmetic)
+        packed = torch.from_numpy(np.ascontiguousarray(blocks, dtype=np.uint32).view(np.int32).copy()).to(self.dev)
+        torch.cuda.current_stream(self.dev).synchronize()
+        rc = self.lib.m40llm_attention_compressed_selected_partial_async(
+            self.ctx, self.kv, self.seq, self._p(self.q), self.qh, self.len, self._p(packed), b0, b1,
+            1 if include_recent else 0, self._p(m), self._p(l), self._p(o))
+        if rc != 0:
+            raise RuntimeError(f"m40llm_attention_compressed_selected_partial_async failed: {rc}")
+        self._sync()
+        return m, l, o
+
+    def attend_tokens(self, t0: int, t1: int):
+        m, l, o = self._triples()
+        torch.cuda.current_stream(self.dev).synchronize()
+        rc = self.lib.m40llm_attention_last_token_f32_gqa_partial_async(
+            self.ctx, self.kv, self.seq, self._p(self.q), self.qh, t0, t1, self._p(m), self._p(l), self._p(o))
+        if rc != 0:
+            raise RuntimeError(f"m40llm_attention_last_token_f32_gqa_partial_async failed: {rc}")
+        self._sync()
+        return m, l, o
+
+    def merge(self, m: torch.Tensor, l: torch.Tensor, o: torch.Tensor) -> torch.Tensor:
+        parts = m.shape[0]
+        out = torch.empty(self.qh * self.hd, dtype=torch.float32, device=self.dev)
+        torch.cuda.current_stream(self.dev).synchronize()
+        rc = self.lib.m40llm_attention_merge_partials_async(self.ctx, self._p(m), self._p(l), self._p(o), parts,
+                                                            self.qh, self.hd, self._p(out))
+        if rc != 0:
+            raise RuntimeError(f"m40llm_attention_merge_partials_async failed: {rc}")
+        self._sync()
+        return out
+
+    def legs(self) -> Legs:
+        return Legs(self.score, self.attend_blocks, self.attend_tokens, self.merge)
