@@ -415,6 +415,17 @@ int m40llm_kvcache_debug_read_old_token(M40llmCudaContext* ctx, M40llmKVCache* k
 /* Device error word of the context: bit 0 = a batched-attention row carried an out-of-range
  * sequence id or length and was skipped. Reading clears it. */
 int m40llm_context_take_device_status(M40llmCudaContext* ctx, uint32_t* out_status);
+/* No counterpart in the reference. Same contract as m40llm_attention_last_token_f32_gqa_async (dense cache, one
+ * sequence, decode stream), but it never allocates or frees device or host memory: the per-split partials live in a
+ * fixed 4 MiB device array that belongs to the loaded library. For callers that cannot take an allocating call (all
+ * HBM already given to a KV pool; code that must not enter the allocator or its implicit device synchronisation).
+ * The first call on each device looks up the array's address (cudaGetSymbolAddress) and should come before any
+ * stream capture. Returns M40LLM_ERR_LIMIT when q_heads * splits * (2 + head_dim) floats exceed 2^20,
+ * M40LLM_ERR_UNSUPPORTED for head_dim other than 64/128 or more than 16 q heads per kv head. All calls on a device
+ * share the array: calls that overlap in time (other streams, other contexts) race and must be serialised. */
+int m40llm_attention_last_token_f32_gqa_static_async(M40llmCudaContext* ctx, const M40llmKVCache* kv,
+                                                     uint32_t seq_id, const void* d_q_f32, uint32_t q_heads,
+                                                     uint32_t seq_len, void* d_out_f32);
 /* Number of kernels this library has launched on `ctx` since creation (launch accounting for benchmarks). */
 int m40llm_context_launch_count(M40llmCudaContext* ctx, uint64_t* out_count);
 /* The raw CUDA stream handle of a stream kind, for harnesses that time with their own events. */
