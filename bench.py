@@ -170,11 +170,9 @@ class Layer:
         rc = L.m40llm_attention_last_token_f32_gqa_batched_async(ctx, self.kv, self.dids.ptr, self.dlens.ptr, r,
                                                                  self.dq.ptr, QH, self.datt.ptr)
         assert rc == 0, rc
-        assert L.m40llm_gemm_f32xf16_gguf_f32_async(ctx, self.datt.ptr, d["wo"].ptr, self.dx1.ptr, r, H, QH * HD, 1) == 0
-        assert L.m40llm_residual_add_f32_async(ctx, self.dx.ptr, self.dx1.ptr, self.dx1.ptr, r * H) == 0
-        assert L.m40llm_rms_norm_f32_weighted_async(ctx, self.dx1.ptr, d["ffn_norm"].ptr, self.dx1n.ptr, r, H, EPS, 1) == 0
-        rc = L.m40llm_ffn_swiglu_q80_f32_async(ctx, self.dx1n.ptr, d["wg"].ptr, d["wu"].ptr, d["wd"].ptr, self.dx1.ptr,
-                                               self.dhid.ptr, self.dout.ptr, r, H, F, 1)
+        rc = L.m40llm_attn_out_ffn_async(ctx, self.datt.ptr, d["wo"].ptr, self.dx.ptr, d["ffn_norm"].ptr, 1, EPS,
+                                         d["wg"].ptr, d["wu"].ptr, d["wd"].ptr, 1, self.dx1.ptr, self.dhid.ptr,
+                                         self.dout.ptr, r, H, QH * HD, F)
         assert rc == 0, rc
 
     def attention_only(self):

@@ -374,6 +374,15 @@ int m40llm_qkv_rmsnorm_rope_append_async(M40llmCudaContext* ctx, M40llmKVCache* 
                                          const uint32_t* d_positions, uint32_t rows, uint32_t hidden,
                                          uint32_t q_heads, float freq_base, float freq_scale, uint32_t rope_layout,
                                          void* d_q_out_f32);
+/* Fused second half of the layer for `rows` decode rows (steps 9-13 of src/infer/forward.rs:470-667):
+ * x1 = x + att.Wo; xn = rmsnorm(x1, ffn_norm_w); hid = silu(xn.Wg) * (xn.Wu); out = x1 + hid.Wd.
+ * att [rows][q_dim], x/x1/out [rows][hidden], hid [rows][ffn] (x1 and hid are caller-provided work buffers that hold
+ * the intermediate values afterwards). Wo f16 GGUF rows; Wg/Wu/Wd Q8_0 (ffn_q80 != 0) or f16. norm_w_dtype: 0 f16,
+ * 1 f32. Decode stream. */
+int m40llm_attn_out_ffn_async(M40llmCudaContext* ctx, const void* d_att_f32, const void* d_wo_f16, const void* d_x_f32,
+                              const void* d_ffn_norm_w, uint32_t norm_w_dtype, float eps, const void* d_wg,
+                              const void* d_wu, const void* d_wd, uint32_t ffn_q80, void* d_x1_f32, void* d_hid_f32,
+                              void* d_out_f32, uint32_t rows, uint32_t hidden, uint32_t q_dim, uint32_t ffn);
 /* Split-K attention for one long sequence sharded over ranks: attends tokens [tok_begin, tok_end) of a dense
  * cache and writes the unnormalised triple per q head: m [q_heads], l [q_heads], o [q_heads][head_dim]. */
 int m40llm_attention_last_token_f32_gqa_partial_async(M40llmCudaContext* ctx, const M40llmKVCache* kv,

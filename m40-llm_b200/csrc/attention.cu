@@ -145,6 +145,80 @@ __global__ void __launch_bounds__(128) attn_merge_kernel(const float* __restrict
     }
 }
 
+// The same merge with the work spread over the CTA: split s's weight exp(m_s - M) is computed once by thread s,
+// the output accumulation runs as 8 split groups x (hd/4) float4 lanes with independent loads, and the groups
+// meet in shared memory in a fixed order. Takes hd % 4 == 0, hd <= 128, splits <= 256 and 16-byte aligned partials.
+__global__ void __launch_bounds__(256) attn_merge_wide_kernel(const float* __restrict__ pm, const float* __restrict__ pl,
+                                                              const float* __restrict__ po, float* __restrict__ out,
+                                                              uint32_t q_heads, uint32_t hd, uint32_t splits,
+                                                              size_t part_stride_m, size_t part_stride_o,
+                                                              uint32_t strided) {
+    __shared__ float sw[256];
+    __shared__ float sred[8];
+    __shared__ float4 sacc[8][32];
+    const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
+    const uint32_t h = blockIdx.x, row = blockIdx.y;
+    const size_t base = ((size_t)row * q_heads + h) * splits;
+    float m = -INFINITY, l = 0.0f;
+    if (tid < splits) {
+        const size_t i = strided ? (size_t)tid * part_stride_m + h : base + tid;
+        l = pl[i];
+        m = l > 0.0f ? pm[i] : -INFINITY;
+    }
+    float M = m;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+    if (lane == 0) sred[warp] = M;
+    __syncthreads();
+    M = sred[0];
+#pragma unroll
+    for (int i = 1; i < 8; ++i) M = fmaxf(M, sred[i]);
+    const float e = l > 0.0f ? expf(m - M) : 0.0f;
+    sw[tid] = e;
+    float L = warp_sum(l * e);
+    __syncthreads();  // everyone has read sred (max) before it is reused for the sum
+    if (lane == 0) sred[warp] = L;
+    __syncthreads();
+    L = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) L += sred[i];
+    const float inv = 1.0f / (L > 0.0f ? L : 1.0f);
+    const uint32_t vl = hd / 4u;            // float4 lanes per split (<= 32)
+    const uint32_t g = tid / 32u, v = lane;  // split group, float4 lane
+    float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    if (v < vl) {
+#pragma unroll 4
+        for (uint32_t s = g; s < splits; s += 8u) {
+            const float w = sw[s];
+            const size_t oi = strided ? ((size_t)s * part_stride_o + (size_t)h * hd) : ((base + s) * hd);
+            const float4 x = *reinterpret_cast<const float4*>(po + oi + 4u * v);
+            if (w != 0.0f) {  // empty splits may hold anything
+                acc.x = fmaf(w, x.x, acc.x);
+                acc.y = fmaf(w, x.y, acc.y);
+                acc.z = fmaf(w, x.z, acc.z);
+                acc.w = fmaf(w, x.w, acc.w);
+            }
+        }
+    }
+    sacc[g][v] = acc;
+    __syncthreads();
+    if (g == 0 && v < vl) {
+        float4 t = sacc[0][v];
+#pragma unroll
+        for (int i = 1; i < 8; ++i) {
+            const float4 u = sacc[i][v];
+            t.x += u.x, t.y += u.y, t.z += u.z, t.w += u.w;
+        }
+        t.x *= inv, t.y *= inv, t.z *= inv, t.w *= inv;
+        *reinterpret_cast<float4*>(out + ((size_t)row * q_heads + h) * hd + 4u * v) = t;
+    }
+}
+
+static bool merge_wide_ok(const float* o, const float* out, uint32_t hd, uint32_t splits, size_t stride_o) {
+    return hd % 4u == 0u && hd <= 128u && splits <= 256u && stride_o % 4u == 0u &&
+           ((((uintptr_t)o) | ((uintptr_t)out)) & 15u) == 0u;
+}
+
 // Fold split partials of one row into ONE unnormalised triple per head (split-K rank output).
 // grid q_heads, block 128. In: [head][split] ; out: m[head], l[head], o[head][hd].
 __global__ void __launch_bounds__(128) attn_fold_kernel(const float* __restrict__ pm, const float* __restrict__ pl,
@@ -267,7 +341,10 @@ int m40_attention_dense(M40llmCudaContext* ctx, const M40llmKVCache* kv, const M
 int m40_attention_merge_rows(M40llmCudaContext* ctx, const float* m, const float* l, const float* o, uint32_t splits,
                              uint32_t q_heads, uint32_t hd, float* out, uint32_t rows) {
     dim3 grid(q_heads, rows);
-    attn_merge_kernel<<<grid, 128, 0, ctx->decode_stream>>>(m, l, o, out, q_heads, hd, splits, 0, 0, 0u);
+    if (merge_wide_ok(o, out, hd, splits, 0))
+        attn_merge_wide_kernel<<<grid, 256, 0, ctx->decode_stream>>>(m, l, o, out, q_heads, hd, splits, 0, 0, 0u);
+    else
+        attn_merge_kernel<<<grid, 128, 0, ctx->decode_stream>>>(m, l, o, out, q_heads, hd, splits, 0, 0, 0u);
     M40_COUNT_LAUNCH(ctx);
     return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
@@ -283,8 +360,12 @@ int m40_attention_fold_partials(M40llmCudaContext* ctx, const float* m, const fl
 int m40_attention_merge(M40llmCudaContext* ctx, const float* m, const float* l, const float* o, uint32_t parts,
                         uint32_t q_heads, uint32_t hd, float* out) {
     dim3 grid(q_heads, 1);
-    attn_merge_kernel<<<grid, 128, 0, ctx->decode_stream>>>(m, l, o, out, q_heads, hd, parts, (size_t)q_heads,
-                                                           (size_t)q_heads * hd, 1u);
+    if (merge_wide_ok(o, out, hd, parts, (size_t)q_heads * hd))
+        attn_merge_wide_kernel<<<grid, 256, 0, ctx->decode_stream>>>(m, l, o, out, q_heads, hd, parts, (size_t)q_heads,
+                                                                    (size_t)q_heads * hd, 1u);
+    else
+        attn_merge_kernel<<<grid, 128, 0, ctx->decode_stream>>>(m, l, o, out, q_heads, hd, parts, (size_t)q_heads,
+                                                               (size_t)q_heads * hd, 1u);
     M40_COUNT_LAUNCH(ctx);
     return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }

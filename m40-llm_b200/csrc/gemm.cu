@@ -8,6 +8,7 @@
 
 #include "gemm.cuh"
 #include "gemm_tc.cuh"
+#include "gemv_stream.cuh"
 
 int m40_tc_min_rows();
 
@@ -371,6 +372,11 @@ int launch_gemv_f16(M40llmCudaContext* ctx, cudaStream_t s, const float* A, cons
 int m40_gemm_f32xf16_gguf(M40llmCudaContext* ctx, cudaStream_t s, const float* A, const __half* W, float* C, int M,
                           int N, int K, const float* bias, const float* residual) {
     if (M <= 0 || N <= 0 || K <= 0) return 0;
+    if (M == 1) {  // one row: the bulk-copy streaming kernel, when the shape is one it takes
+        const M40GemvSeg seg = {W, nullptr, C, bias, residual, N};
+        const int rc = m40_gemv_stream(ctx, s, A, K, M40_GEMV_F16, 0, 1, &seg, nullptr);
+        if (rc != 1) return rc;
+    }
     if (K % 8 == 0 && aligned16(A) && aligned16(W)) {
         // Two rows per warp once there are enough rows to fill the machine with 256-thread CTAs.
         if (N >= ctx->sm_count * 16) return launch_gemv_f16<2>(ctx, s, A, W, C, M, N, K, bias, residual);
@@ -386,6 +392,11 @@ int m40_gemm_f32xq80_gguf(M40llmCudaContext* ctx, cudaStream_t s, const float* A
                           int N, int K, const float* residual) {
     if (M <= 0 || N <= 0 || K <= 0) return 0;
     if (K % 32 != 0) return -2;
+    if (M == 1) {
+        const M40GemvSeg seg = {W, nullptr, C, nullptr, residual, N};
+        const int rc = m40_gemv_stream(ctx, s, A, K, M40_GEMV_Q80, 0, 1, &seg, nullptr);
+        if (rc != 1) return rc;
+    }
     if (K % 128 == 0 && aligned16(A) && (((uintptr_t)W) & 1u) == 0u) {
         const int blocks = (N + 7) / 8;
         if (M == 1) gemv_q80_gguf_kernel<1, 0><<<blocks, 256, 0, s>>>(A, W, nullptr, C, M, N, K, residual);
@@ -436,6 +447,11 @@ static int q80_tc_rows(M40llmCudaContext* ctx, cudaStream_t s, uint32_t stream_k
 
 int m40_gate_up_swiglu_q80(M40llmCudaContext* ctx, cudaStream_t s, const float* A, const uint8_t* Wg,
                            const uint8_t* Wu, float* hid, int M, int F, int K) {
+    if (M == 1) {
+        const M40GemvSeg seg = {Wg, Wu, hid, nullptr, nullptr, F};
+        const int rc = m40_gemv_stream(ctx, s, A, K, M40_GEMV_Q80, 1, 1, &seg, nullptr);
+        if (rc != 1) return rc;
+    }
     if (K % 128 != 0 || !aligned16(A) || ((((uintptr_t)Wg) | ((uintptr_t)Wu)) & 1u) != 0u) return -2;
     const int blocks = (F + 7) / 8;
     if (M == 1) gemv_q80_gguf_kernel<1, 1><<<blocks, 256, 0, s>>>(A, Wg, Wu, hid, M, F, K, nullptr);
@@ -447,6 +463,11 @@ int m40_gate_up_swiglu_q80(M40llmCudaContext* ctx, cudaStream_t s, const float* 
 
 int m40_gate_up_swiglu_f16(M40llmCudaContext* ctx, cudaStream_t s, const float* A, const __half* Wg, const __half* Wu,
                            float* hid, int M, int F, int K) {
+    if (M == 1) {
+        const M40GemvSeg seg = {Wg, Wu, hid, nullptr, nullptr, F};
+        const int rc = m40_gemv_stream(ctx, s, A, K, M40_GEMV_F16, 1, 1, &seg, nullptr);
+        if (rc != 1) return rc;
+    }
     if (K % 8 != 0 || !aligned16(A) || !aligned16(Wg) || !aligned16(Wu)) return -2;
     const int blocks = (F + 7) / 8;
     if (M == 1) gemv_f16_gate_up_kernel<1><<<blocks, 256, 0, s>>>(A, Wg, Wu, hid, M, F, K);

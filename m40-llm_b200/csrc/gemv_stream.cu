@@ -1,0 +1,464 @@
+// Single-row GEMV over streamed weights (decode batch 1): out[n] = x . W[n].
+//
+// At one activation row every weight byte is read once and nothing is reused, so the only thing that matters is
+// keeping HBM busy. The kernel is persistent (one CTA per SM) and warp-specialised:
+//
+//   * a producer thread streams groups of whole weight rows into a shared-memory ring with 1-D bulk async copies
+//     (cp.async.bulk ... mbarrier::complete_tx), 16-40 KB per stage and up to 200 KB in flight per SM,
+//     independent of how fast the consumers issue instructions;
+//   * eight consumer warps read the rows from shared memory. A thread owns fixed column pieces of every row, so
+//     its slice of the activation vector stays in registers for the whole launch:
+//       - f16 weights: 16-byte pieces, f32 activations, f32 FMAs;
+//       - Q8_0 weights: 68-byte pieces (two raw 34-byte GGUF blocks: 4-byte aligned although single blocks are
+//         not), int8 dot products with dp4a against the activations held as three signed 8-bit digits per value
+//         and one scale per 32-block (x = s/128 * (128 a + b + c/128), error <= 2^-22 of the block maximum, i.e.
+//         f32 rounding level), then one f32 multiply-add per block with d * s;
+//   * row sums meet by warp shuffle, then across the warps that share a row through shared memory in a fixed
+//     order (no atomics: results are deterministic).
+// Up to three matrices that share x go in one launch (Wq | Wk | Wv), gate and up are streamed side by side with
+// the SwiGLU epilogue, bias/residual are folded into the store, and the RMSNorm of x can be applied on the fly.
+//
+// Every wait is bounded: a wait that runs out raises bit 4 of the context's status word, the CTA stops consuming
+// (all warps still pass the same barriers) and drains its own copies before it returns.
+#include "gemv_stream.cuh"
+
+#include "tc_ptx.cuh"
+
+namespace {
+using namespace tc;
+
+constexpr int CWARPS = 8;                 // consumer warps
+constexpr int CONSUMERS = CWARPS * 32;
+constexpr int THREADS = CONSUMERS + 32;   // + the producer warp
+constexpr int MAX_SEGS = 3;
+constexpr int MAX_STAGES = 8;
+constexpr int MAX_ROWS = 16;              // rows of one matrix per stage
+constexpr uint32_t STAGE_MAX = 40u * 1024u;
+constexpr uint32_t RING_MAX = 200u * 1024u;
+
+struct SegDev {
+    const uint8_t* W;
+    const uint8_t* W2;
+    float* out;
+    const float* bias;
+    const float* residual;
+    int N;
+    int group0;  // id of this matrix's first row group
+};
+
+struct GemvArgs {
+    SegDev seg[MAX_SEGS];
+    const float* x;
+    const void* norm_w;
+    float* xn_out;
+    uint32_t* status;
+    float eps;
+    int norm_f32;
+    int nseg, K, pieces, cw, R, nstages, total_groups;
+    uint32_t row_bytes, stage_bytes;
+};
+
+__device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void consumer_barrier() { asm volatile("bar.sync 1, %0;" ::"n"(CONSUMERS) : "memory"); }
+
+__device__ __forceinline__ void locate_group(const GemvArgs& a, int g, int* seg, int* row0, int* rows) {
+    int s = 0;
+#pragma unroll
+    for (int i = 1; i < MAX_SEGS; ++i)
+        if (i < a.nseg && g >= a.seg[i].group0) s = i;
+    const int r0 = (g - a.seg[s].group0) * a.R;
+    const int left = a.seg[s].N - r0;
+    *seg = s;
+    *row0 = r0;
+    *rows = left < a.R ? left : a.R;
+}
+
+__device__ __forceinline__ float dot8(const uint4& w, const float* x) {
+    const __half2* h = reinterpret_cast<const __half2*>(&w);
+    float acc = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 f = __half22float2(h[i]);
+        acc = fmaf(x[2 * i], f.x, acc);
+        acc = fmaf(x[2 * i + 1], f.y, acc);
+    }
+    return acc;
+}
+
+// Activations of one 64-value piece as three int8 digits per value (packed 4 per word) and a scale per 32-block.
+struct Q80X {
+    int d[3][16];
+    float s[2];
+};
+
+__device__ __forceinline__ void q80_quantise_x(const float* v, Q80X& q) {
+#pragma unroll
+    for (int b = 0; b < 2; ++b) {
+        float mx = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) mx = fmaxf(mx, fabsf(v[b * 32 + i]));
+        const float inv = mx > 0.0f ? 127.0f / mx : 0.0f;
+        q.s[b] = mx * (1.0f / (127.0f * 128.0f));
+#pragma unroll
+        for (int w = 0; w < 8; ++w) {
+            uint32_t pa = 0, pb = 0, pc = 0;
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float t = v[b * 32 + w * 4 + e] * inv;
+                const float fa = rintf(t);
+                const float r1 = (t - fa) * 128.0f;
+                const float fb = rintf(r1);
+                const float fc = rintf((r1 - fb) * 128.0f);
+                pa |= ((uint32_t)(int)fa & 0xffu) << (8 * e);
+                pb |= ((uint32_t)(int)fb & 0xffu) << (8 * e);
+                pc |= ((uint32_t)(int)fc & 0xffu) << (8 * e);
+            }
+            q.d[0][b * 8 + w] = (int)pa;
+            q.d[1][b * 8 + w] = (int)pb;
+            q.d[2][b * 8 + w] = (int)pc;
+        }
+    }
+}
+
+// x . (two raw Q8_0 blocks at a 4-byte aligned shared-memory address).
+__device__ __forceinline__ float q80_pair_dot(const uint32_t* wp, const Q80X& x) {
+    uint32_t w[17];
+#pragma unroll
+    for (int i = 0; i < 17; ++i) w[i] = wp[i];
+    int sa = 0, sb = 0, sc = 0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {  // first block: scale in the low half of w[0], weights from byte 2
+        const int q = (int)__funnelshift_r(w[i], w[i + 1], 16);
+        sa = __dp4a(q, x.d[0][i], sa);
+        sb = __dp4a(q, x.d[1][i], sb);
+        sc = __dp4a(q, x.d[2][i], sc);
+    }
+    const float d0 = __half2float(__ushort_as_half((unsigned short)(w[0] & 0xffffu)));
+    float r = fmaf((float)sc, 1.0f / 128.0f, (float)(sa * 128 + sb)) * (d0 * x.s[0]);
+    sa = sb = sc = 0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {  // second block: scale in the high half of w[8], weights word aligned
+        const int q = (int)w[9 + i];
+        sa = __dp4a(q, x.d[0][8 + i], sa);
+        sb = __dp4a(q, x.d[1][8 + i], sb);
+        sc = __dp4a(q, x.d[2][8 + i], sc);
+    }
+    const float d1 = __half2float(__ushort_as_half((unsigned short)(w[8] >> 16)));
+    return fmaf(fmaf((float)sc, 1.0f / 128.0f, (float)(sa * 128 + sb)), d1 * x.s[1], r);
+}
+
+// bias[n] + residual[n]: loaded at the top of a stage so that the latency hides behind the dot products.
+__device__ __forceinline__ float load_addend(const SegDev& sg, int n) {
+    float add = 0.0f;
+    if (sg.bias) add = sg.bias[n];
+    if (sg.residual) add += sg.residual[n];
+    return add;
+}
+
+template <int GATE_UP>
+__device__ __forceinline__ void store_row(const SegDev& sg, int n, float v, float v2, float add) {
+    if (GATE_UP) v = (v / (1.0f + expf(-v))) * v2;
+    sg.out[n] = v + add;
+}
+
+template <int FMT, int GATE_UP, int CPT>
+__global__ void __launch_bounds__(THREADS, 1) gemv_stream_kernel(const __grid_constant__ GemvArgs a) {
+    extern __shared__ __align__(128) uint8_t ring[];
+    __shared__ uint64_t full[MAX_STAGES], empty[MAX_STAGES];
+    __shared__ float red[2][2][MAX_ROWS][CWARPS];
+    __shared__ float ssq[CWARPS];
+    __shared__ volatile uint32_t abort_flag;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    if (tid == 0) {
+        for (int s = 0; s < a.nstages; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], CWARPS);
+        }
+        abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    const int my_groups = ((int)blockIdx.x < a.total_groups)
+                              ? (a.total_groups - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
+    const uint32_t mat2_off = (uint32_t)a.R * a.row_bytes;
+
+    if (warp == CWARPS) {
+        // ------------------------------------------------------------ producer
+        if (lane != 0) return;
+        int issued = 0;
+        for (int i = 0; i < my_groups; ++i) {
+            const int s = i % a.nstages;
+            if (i >= a.nstages && !mbar_wait(&empty[s], (uint32_t)((i / a.nstages) & 1) ^ 1u)) {
+                abort_flag = 1;
+                atomicOr(a.status, 4u);
+                break;
+            }
+            if (abort_flag) break;
+            int sidx, row0, rows;
+            locate_group(a, (int)blockIdx.x + i * (int)gridDim.x, &sidx, &row0, &rows);
+            const SegDev& sg = a.seg[sidx];
+            const uint32_t bytes = (uint32_t)rows * a.row_bytes;
+            uint8_t* dst = ring + (size_t)s * a.stage_bytes;
+            mbar_expect_tx(&full[s], GATE_UP ? 2u * bytes : bytes);
+            bulk_load(dst, sg.W + (size_t)row0 * a.row_bytes, bytes, &full[s]);
+            if (GATE_UP) bulk_load(dst + mat2_off, sg.W2 + (size_t)row0 * a.row_bytes, bytes, &full[s]);
+            issued = i + 1;
+        }
+        if (abort_flag) {
+            // the consumers have stopped: wait (bounded) for the copies still in flight before the CTA goes away
+            const int first = issued > a.nstages ? issued - a.nstages : 0;
+            for (int i = first; i < issued; ++i) mbar_wait(&full[i % a.nstages], (uint32_t)((i / a.nstages) & 1));
+        }
+        return;
+    }
+
+    // ---------------------------------------------------------------- consumers
+    const int cw = a.cw, lanes_of_rows = CWARPS / cw;
+    const int rl = warp / cw, cwi = warp % cw;
+    const int c = cwi * 32 + lane, cols = cw * 32;
+
+    float scale = 1.0f;
+    if (a.norm_w) {
+        float ss = 0.0f;
+        for (int k = tid * 4; k < a.K; k += CONSUMERS * 4) {
+            const float4 v = *reinterpret_cast<const float4*>(a.x + k);
+            ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+        }
+        ss = warp_sum(ss);
+        if (lane == 0) ssq[warp] = ss;
+        consumer_barrier();
+        float tot = 0.0f;
+#pragma unroll
+        for (int i = 0; i < CWARPS; ++i) tot += ssq[i];
+        scale = rsqrtf(tot / (float)a.K + a.eps);
+    }
+
+    constexpr int XV = FMT == M40_GEMV_Q80 ? 64 : 8;  // activation values per piece
+    float xr[FMT == M40_GEMV_Q80 ? 1 : CPT][8];
+    Q80X xq[FMT == M40_GEMV_Q80 ? CPT : 1];
+#pragma unroll
+    for (int j = 0; j < CPT; ++j) {
+        const int p = c + j * cols;
+        float v[XV];
+#pragma unroll
+        for (int i = 0; i < XV; ++i) v[i] = 0.0f;
+        if (p < a.pieces) {
+            const int k0 = p * XV;
+#pragma unroll
+            for (int i = 0; i < XV; i += 4) {
+                const float4 t = *reinterpret_cast<const float4*>(a.x + k0 + i);
+                v[i] = t.x, v[i + 1] = t.y, v[i + 2] = t.z, v[i + 3] = t.w;
+            }
+            if (a.norm_w) {
+#pragma unroll
+                for (int i = 0; i < XV; ++i) {
+                    const float w = a.norm_f32 ? reinterpret_cast<const float*>(a.norm_w)[k0 + i]
+                                               : __half2float(reinterpret_cast<const __half*>(a.norm_w)[k0 + i]);
+                    v[i] = v[i] * scale * w;
+                }
+                if (a.xn_out && blockIdx.x == 0 && rl == 0) {
+#pragma unroll
+                    for (int i = 0; i < XV; i += 4)
+                        *reinterpret_cast<float4*>(a.xn_out + k0 + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+                }
+            }
+        }
+        if (FMT == M40_GEMV_Q80) {
+            q80_quantise_x(v, xq[j]);
+        } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) xr[j][i] = v[i];
+        }
+    }
+
+    constexpr uint32_t PIECE_BYTES = FMT == M40_GEMV_Q80 ? 68u : 16u;
+    for (int i = 0; i < my_groups; ++i) {
+        const int s = i % a.nstages;
+        bool ok = abort_flag == 0;
+        if (ok && !mbar_wait(&full[s], (uint32_t)((i / a.nstages) & 1))) {
+            abort_flag = 1;
+            if (lane == 0) atomicOr(a.status, 4u);
+            ok = false;
+        }
+        int sidx, row0, rows;
+        locate_group(a, (int)blockIdx.x + i * (int)gridDim.x, &sidx, &row0, &rows);
+        const SegDev& sg = a.seg[sidx];
+        const uint8_t* st = ring + (size_t)s * a.stage_bytes;
+        float add_final = 0.0f;
+        if (cw > 1 && ok && tid < rows) add_final = load_addend(sg, row0 + tid);
+        if (ok) {
+            for (int r = rl; r < rows; r += lanes_of_rows) {
+                const uint8_t* rowp = st + (size_t)r * a.row_bytes;
+                float acc = 0.0f, acc2 = 0.0f, add = 0.0f;
+                if (cw == 1 && lane == 0) add = load_addend(sg, row0 + r);
+#pragma unroll
+                for (int j = 0; j < CPT; ++j) {
+                    const int p = c + j * cols;
+                    if (p < a.pieces) {
+                        if (FMT == M40_GEMV_Q80) {
+                            acc += q80_pair_dot(reinterpret_cast<const uint32_t*>(rowp + (size_t)p * PIECE_BYTES), xq[j]);
+                            if (GATE_UP)
+                                acc2 += q80_pair_dot(
+                                    reinterpret_cast<const uint32_t*>(rowp + mat2_off + (size_t)p * PIECE_BYTES), xq[j]);
+                        } else {
+                            acc += dot8(*reinterpret_cast<const uint4*>(rowp + (size_t)p * PIECE_BYTES), xr[j]);
+                            if (GATE_UP)
+                                acc2 += dot8(*reinterpret_cast<const uint4*>(rowp + mat2_off + (size_t)p * PIECE_BYTES), xr[j]);
+                        }
+                    }
+                }
+                acc = warp_sum(acc);
+                if (GATE_UP) acc2 = warp_sum(acc2);
+                if (lane == 0) {
+                    if (cw == 1) {
+                        store_row<GATE_UP>(sg, row0 + r, acc, acc2, add);
+                    } else {
+                        red[i & 1][0][r][cwi] = acc;
+                        if (GATE_UP) red[i & 1][1][r][cwi] = acc2;
+                    }
+                }
+            }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty[s]);  // this warp has finished reading the stage
+        if (cw > 1) {
+            consumer_barrier();
+            if (ok && tid < rows) {
+                float v = 0.0f, v2 = 0.0f;
+                for (int k = 0; k < cw; ++k) {
+                    v += red[i & 1][0][tid][k];
+                    if (GATE_UP) v2 += red[i & 1][1][tid][k];
+                }
+                store_row<GATE_UP>(sg, row0 + tid, v, v2, add_final);
+            }
+        }
+    }
+}
+
+template <int FMT, int GATE_UP, int CPT>
+int launch(M40llmCudaContext* ctx, cudaStream_t s, const GemvArgs& a, int grid) {
+    static bool attr_set[64] = {};
+    const size_t smem = (size_t)a.nstages * a.stage_bytes;
+    const int dev = ctx->device_id;
+    if (dev < 0 || dev >= 64 || !attr_set[dev]) {
+        if (cudaFuncSetAttribute(gemv_stream_kernel<FMT, GATE_UP, CPT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)RING_MAX) != cudaSuccess)
+            return -2;
+        if (dev >= 0 && dev < 64) attr_set[dev] = true;
+    }
+    gemv_stream_kernel<FMT, GATE_UP, CPT><<<grid, THREADS, smem, s>>>(a);
+    M40_COUNT_LAUNCH(ctx);
+    return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+template <int FMT, int GATE_UP>
+int launch_cpt(M40llmCudaContext* ctx, cudaStream_t s, const GemvArgs& a, int grid, int cpt) {
+    if (cpt == 1) return launch<FMT, GATE_UP, 1>(ctx, s, a, grid);
+    if (cpt == 2) return launch<FMT, GATE_UP, 2>(ctx, s, a, grid);
+    if (FMT == M40_GEMV_F16) {
+        if (cpt == 4) return launch<M40_GEMV_F16, GATE_UP, 4>(ctx, s, a, grid);
+        if (cpt == 8) return launch<M40_GEMV_F16, GATE_UP, 8>(ctx, s, a, grid);
+    }
+    return 1;
+}
+
+bool aligned16(const void* p) { return (((uintptr_t)p) & 15u) == 0u; }
+
+}  // namespace
+
+int m40_gemv_stream(M40llmCudaContext* ctx, cudaStream_t s, const float* x, int K, int fmt, int gate_up, int nseg,
+                    const M40GemvSeg* segs, const M40GemvNorm* norm) {
+    if (nseg < 1 || nseg > MAX_SEGS || K <= 0 || !aligned16(x)) return 1;
+    GemvArgs a = {};
+    int cpt_max;
+    if (fmt == M40_GEMV_F16) {
+        if (K % 8 != 0) return 1;
+        a.row_bytes = (uint32_t)K * 2u;
+        a.pieces = K / 8;
+        cpt_max = 8;
+    } else if (fmt == M40_GEMV_Q80) {
+        if (K % 256 != 0) return 1;  // whole block pairs and 16-byte row pitch
+        a.row_bytes = (uint32_t)(K / 32) * 34u;
+        a.pieces = K / 64;
+        cpt_max = 2;
+    } else {
+        return 1;
+    }
+    const uint32_t nmat = gate_up ? 2u : 1u;
+    for (int i = 0; i < nseg; ++i) {
+        if (segs[i].N <= 0 || !segs[i].W || !segs[i].out || !aligned16(segs[i].W)) return 1;
+        if (gate_up && (!segs[i].W2 || !aligned16(segs[i].W2))) return 1;
+    }
+    if (norm && norm->w && (!aligned16(norm->w) || (norm->xn_out && !aligned16(norm->xn_out)))) return 1;
+
+    // Threads per row (cw warps) and pieces per thread: the fewest warps per row whose register slice fits,
+    // with at least one row per row lane in a stage.
+    int cw = 0, cpt = 0;
+    for (int w = 1; w <= CWARPS; w *= 2) {
+        int need = (a.pieces + w * 32 - 1) / (w * 32);
+        int p2 = 1;
+        while (p2 < need) p2 *= 2;
+        if (p2 > cpt_max) continue;
+        if ((uint64_t)(CWARPS / w) * a.row_bytes * nmat > STAGE_MAX) continue;
+        cw = w;
+        cpt = p2;
+        break;
+    }
+    if (!cw) return 1;
+    const int rl = CWARPS / cw;
+
+    // Rows per stage: a multiple of the row lanes within the stage budget; among the candidates the one that
+    // leaves the persistent CTAs the most evenly loaded (ties: the larger stage).
+    const int grid_max = ctx->sm_count > 0 ? ctx->sm_count : 1;
+    int best_R = 0;
+    double best_eff = -1.0;
+    for (int R = rl; R <= MAX_ROWS; R += rl) {
+        if ((uint64_t)R * a.row_bytes * nmat > STAGE_MAX) break;
+        long long groups = 0;
+        for (int i = 0; i < nseg; ++i) groups += (segs[i].N + R - 1) / R;
+        const long long grid = groups < grid_max ? groups : grid_max;
+        const long long per = (groups + grid - 1) / grid;
+        const double eff = (double)groups / (double)(per * grid);
+        if (eff >= best_eff - 1e-9) {
+            best_eff = eff > best_eff ? eff : best_eff;
+            best_R = R;
+        }
+    }
+    if (!best_R) return 1;
+    a.R = best_R;
+    a.cw = cw;
+    a.stage_bytes = ((uint32_t)a.R * a.row_bytes * nmat + 127u) & ~127u;
+    a.nstages = (int)(RING_MAX / a.stage_bytes);
+    if (a.nstages > MAX_STAGES) a.nstages = MAX_STAGES;
+    if (a.nstages < 2) return 1;
+    int g = 0;
+    for (int i = 0; i < nseg; ++i) {
+        a.seg[i].W = (const uint8_t*)segs[i].W;
+        a.seg[i].W2 = (const uint8_t*)segs[i].W2;
+        a.seg[i].out = segs[i].out;
+        a.seg[i].bias = segs[i].bias;
+        a.seg[i].residual = segs[i].residual;
+        a.seg[i].N = segs[i].N;
+        a.seg[i].group0 = g;
+        g += (segs[i].N + a.R - 1) / a.R;
+    }
+    a.nseg = nseg;
+    a.total_groups = g;
+    a.K = K;
+    a.x = x;
+    a.status = ctx->d_status;
+    if (norm && norm->w) {
+        a.norm_w = norm->w;
+        a.norm_f32 = norm->w_is_f32;
+        a.eps = norm->eps;
+        a.xn_out = norm->xn_out;
+    }
+    const int grid = g < grid_max ? g : grid_max;
+    if (fmt == M40_GEMV_F16)
+        return gate_up ? launch_cpt<M40_GEMV_F16, 1>(ctx, s, a, grid, cpt) : launch_cpt<M40_GEMV_F16, 0>(ctx, s, a, grid, cpt);
+    return gate_up ? launch_cpt<M40_GEMV_Q80, 1>(ctx, s, a, grid, cpt) : launch_cpt<M40_GEMV_Q80, 0>(ctx, s, a, grid, cpt);
+}

@@ -1,4 +1,4 @@
-// PTX wrappers for the sm_100a tensor-core path: mbarrier, TMA (no multicast), TMEM, tcgen05.
+// PTX wrappers for the sm_100a tensor-core path: mbarrier, TMA (plain per-CTA loads), TMEM, tcgen05.
 #pragma once
 #include <cuda.h>
 #include <stdint.h>

@@ -52,17 +52,10 @@ int DecodeLayer::enqueue(M40llmKVCache* kv, const LayerWeights& w, const KvCompr
             if (rc != 0) return fail(rc, "attention_block_select_exact_fp16_k_q4_v_old_direct");
         }
     }
-    rc = m40llm_gemm_f32xf16_gguf_f32_async(ctx_, d_att_, w.wo, d_x1_, (int)rows, (int)H, (int)QD, 1u);
-    if (rc != 0) return fail(rc, "out_proj");
-    rc = m40llm_residual_add_f32_async(ctx_, d_x, d_x1_, d_x1_, (size_t)rows * H);
-    if (rc != 0) return fail(rc, "residual_add");
-    rc = m40llm_rms_norm_f32_weighted_async(ctx_, d_x1_, w.ffn_norm, d_x1n_, rows, H, cfg_.rms_eps, 1u);
-    if (rc != 0) return fail(rc, "ffn_norm");
-    rc = w.ffn_q80 ? m40llm_ffn_swiglu_q80_f32_async(ctx_, d_x1n_, w.wg, w.wu, w.wd, d_x1_, d_hid_, d_out, rows, H,
-                                                     cfg_.ffn, 1u)
-                   : m40llm_ffn_swiglu_f16_f32_async(ctx_, d_x1n_, w.wg, w.wu, w.wd, d_x1_, d_hid_, d_out, rows, H,
-                                                     cfg_.ffn, 1u);
-    if (rc != 0) return fail(rc, "ffn_swiglu");
+    // steps 9-13 in one call: out-projection + residual, FFN norm, SwiGLU FFN + residual
+    rc = m40llm_attn_out_ffn_async(ctx_, d_att_, w.wo, d_x, w.ffn_norm, 1u, cfg_.rms_eps, w.wg, w.wu, w.wd,
+                                   w.ffn_q80 ? 1u : 0u, d_x1_, d_hid_, d_out, rows, H, QD, cfg_.ffn);
+    if (rc != 0) return fail(rc, "attn_out_ffn");
     return 0;
 }
 

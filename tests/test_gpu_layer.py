@@ -24,8 +24,9 @@ def make_weights(O, rng, H, qh, kvh, hd, F, q80, bias):
     return w
 
 
-def device_layer(nat, kv, w, x_rows, seq_ids, positions, cfg, q80):
-    """The layer as the fused entry points issue it: prologue, batched attention, Wo+residual, FFN+residual."""
+def device_layer(nat, kv, w, x_rows, seq_ids, positions, cfg, q80, fused_tail=False):
+    """The layer as the fused entry points issue it: prologue, batched attention, then either the reference's op
+    sequence (Wo, residual, norm, FFN + residual) or the single composite call for steps 9-13."""
     L, ctx = nat.lib, nat.ctx
     rows = x_rows.shape[0]
     H, qd, F = cfg.hidden, cfg.q_heads * cfg.head_dim, cfg.ffn
@@ -40,6 +41,13 @@ def device_layer(nat, kv, w, x_rows, seq_ids, positions, cfg, q80):
                                                 cfg.q_heads, cfg.rope_base, cfg.rope_scale, cfg.rope_layout, dq.ptr)
     assert rc == 0, rc
     assert L.m40llm_attention_last_token_f32_gqa_batched_async(ctx, kv, dids.ptr, dlens.ptr, rows, dq.ptr, cfg.q_heads, datt.ptr) == 0
+    if fused_tail:
+        rc = L.m40llm_attn_out_ffn_async(ctx, datt.ptr, d["wo"].ptr, dx.ptr, d["ffn_norm"].ptr, 1, cfg.eps, d["wg"].ptr,
+                                         d["wu"].ptr, d["wd"].ptr, 1 if q80 else 0, dx1.ptr, dhid.ptr, dout.ptr, rows,
+                                         H, qd, F)
+        assert rc == 0, rc
+        nat.sync(1)
+        return (dout.download(np.float32, (rows, H)), dq.download(np.float32, (rows, qd)), datt.download(np.float32, (rows, qd)))
     # y = att.Wo ; x1 = x + y   (decode stream throughout: no cross-stream waits needed)
     assert L.m40llm_gemm_f32xf16_gguf_f32_async(ctx, datt.ptr, d["wo"].ptr, dx1.ptr, rows, H, qd, 1) == 0
     assert L.m40llm_residual_add_f32_async(ctx, dx.ptr, dx1.ptr, dx1.ptr, rows * H) == 0
@@ -57,7 +65,8 @@ def device_layer(nat, kv, w, x_rows, seq_ids, positions, cfg, q80):
     (2048, 16, 2, 128, 1024, False, 1, True, 1e6, 200),  # Qwen heads: NeoX RoPE + QKV bias
     (4096, 32, 8, 128, 14336, True, 0, False, 5e5, 600), # Llama-3-8B-shaped layer, Q8_0 FFN
 ])
-def test_decode_layer_single_row(nat, O, H, qh, kvh, hd, F, q80, layout, bias, base, ctx_len):
+@pytest.mark.parametrize("fused_tail", [False, True])
+def test_decode_layer_single_row(nat, O, H, qh, kvh, hd, F, q80, layout, bias, base, ctx_len, fused_tail):
     rng = np.random.default_rng(H + F)
     cfg = O.LayerCfg(H, qh, kvh, hd, F, 1 if q80 else 0, layout, 1e-5, base, 1.0)
     w = make_weights(O, rng, H, qh, kvh, hd, F, q80, bias)
@@ -72,7 +81,7 @@ def test_decode_layer_single_row(nat, O, H, qh, kvh, hd, F, q80, layout, bias, b
     # two consecutive tokens (tests/forward_parity_toy.rs runs one and two tokens)
     for step in range(2):
         pos = ctx_len + step
-        out, q_rot, att = device_layer(nat, kv, w, x[None, :], [0], [pos], cfg, q80)
+        out, q_rot, att = device_layer(nat, kv, w, x[None, :], [0], [pos], cfg, q80, fused_tail)
         eout, eq, eatt = O.decode_layer(cfg, x, w, K, V, pos)
         assert_close(q_rot[0], eq, what=f"q after rope, step {step}")
         assert_close(att[0], eatt, what=f"attention, step {step}")
@@ -82,7 +91,8 @@ def test_decode_layer_single_row(nat, O, H, qh, kvh, hd, F, q80, layout, bias, b
     nat.free_all()
 
 
-def test_decode_layer_batched_rows_and_compressed_append(nat, O):
+@pytest.mark.parametrize("fused_tail", [False, True])
+def test_decode_layer_batched_rows_and_compressed_append(nat, O, fused_tail):
     """Batched decode rows (src/infer/forward.rs:1729-2140): every row equals the single-row layer on its own
     sequence; the fused prologue also feeds a compressed cache (ring + eviction)."""
     rng = np.random.default_rng(77)
@@ -100,7 +110,7 @@ def test_decode_layer_batched_rows_and_compressed_append(nat, O):
         if n > 1:
             nat.kv_fill(kv, b, Ks[b][:n - 1], Vs[b][:n - 1])
     x = rng.standard_normal((B, H)).astype(np.float32)
-    out, q_rot, att = device_layer(nat, kv, w, x, list(range(B)), [n - 1 for n in lens], cfg, True)
+    out, q_rot, att = device_layer(nat, kv, w, x, list(range(B)), [n - 1 for n in lens], cfg, True, fused_tail)
     for b, n in enumerate(lens):
         eout, eq, eatt = O.decode_layer(cfg, x[b], w, Ks[b], Vs[b], n - 1)
         assert_close(att[b], eatt, what=f"row {b} attention")
