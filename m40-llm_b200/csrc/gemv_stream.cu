@@ -4,16 +4,18 @@
 // keeping HBM busy. The kernel is persistent (one CTA per SM) and warp-specialised:
 //
 //   * a producer thread streams groups of whole weight rows into a shared-memory ring with 1-D bulk async copies
-//     (cp.async.bulk ... mbarrier::complete_tx), 16-40 KB per stage and up to 200 KB in flight per SM,
+//     (cp.async.bulk ... mbarrier::complete_tx), 8-36 KB per stage and up to ~200 KB in flight per SM,
 //     independent of how fast the consumers issue instructions;
-//   * eight consumer warps read the rows from shared memory. A thread owns fixed column pieces of every row, so
-//     its slice of the activation vector stays in registers for the whole launch:
+//   * sixteen consumer warps form groups of `cw` warps; a group owns every G-th stage, so the groups run
+//     decoupled from one another (no CTA-wide barrier in the steady state). A thread owns fixed column pieces of
+//     every row, so its slice of the activation vector stays in registers for the whole launch:
 //       - f16 weights: 16-byte pieces, f32 activations, f32 FMAs;
 //       - Q8_0 weights: 68-byte pieces (two raw 34-byte GGUF blocks: 4-byte aligned although single blocks are
 //         not), int8 dot products with dp4a against the activations held as three signed 8-bit digits per value
 //         and one scale per 32-block (x = s/128 * (128 a + b + c/128), error <= 2^-22 of the block maximum, i.e.
-//         f32 rounding level), then one f32 multiply-add per block with d * s;
-//   * row sums meet by warp shuffle, then across the warps that share a row through shared memory in a fixed
+//         f32 rounding level), then one f32 multiply-add per block with d * s. The digits are made once per CTA
+//         (cooperatively, into shared memory) with add-magic rounding, so no conversion-unit instruction is used;
+//   * row sums meet by warp shuffle, then across the warps of the group through shared memory in a fixed
 //     order (no atomics: results are deterministic).
 // Up to three matrices that share x go in one launch (Wq | Wk | Wv), gate and up are streamed side by side with
 // the SwiGLU epilogue, bias/residual are folded into the store, and the RMSNorm of x can be applied on the fly.
@@ -22,19 +24,21 @@
 // (all warps still pass the same barriers) and drains its own copies before it returns.
 #include "gemv_stream.cuh"
 
+#include <stdlib.h>
+
 #include "tc_ptx.cuh"
 
 namespace {
 using namespace tc;
 
-constexpr int CWARPS = 8;                 // consumer warps
+constexpr int CWARPS = 16;                // consumer warps
 constexpr int CONSUMERS = CWARPS * 32;
 constexpr int THREADS = CONSUMERS + 32;   // + the producer warp
 constexpr int MAX_SEGS = 3;
-constexpr int MAX_STAGES = 8;
+constexpr int MAX_STAGES = 12;
 constexpr int MAX_ROWS = 16;              // rows of one matrix per stage
-constexpr uint32_t STAGE_MAX = 40u * 1024u;
-constexpr uint32_t RING_MAX = 200u * 1024u;
+constexpr uint32_t STAGE_MAX = 36u * 1024u;
+constexpr uint32_t SMEM_MAX = 200u * 1024u;  // ring + activation digits
 
 struct SegDev {
     const uint8_t* W;
@@ -55,7 +59,7 @@ struct GemvArgs {
     float eps;
     int norm_f32;
     int nseg, K, pieces, cw, R, nstages, total_groups;
-    uint32_t row_bytes, stage_bytes;
+    uint32_t row_bytes, stage_bytes, xq_off;
 };
 
 __device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
@@ -63,6 +67,10 @@ __device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t b
                  ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
 }
 __device__ __forceinline__ void consumer_barrier() { asm volatile("bar.sync 1, %0;" ::"n"(CONSUMERS) : "memory"); }
+// Barrier of one consumer group (ids 2..9; id 1 is the all-consumer barrier, id 0 __syncthreads).
+__device__ __forceinline__ void group_barrier(int grp, int threads) {
+    asm volatile("bar.sync %0, %1;" ::"r"(grp + 2), "r"(threads) : "memory");
+}
 
 __device__ __forceinline__ void locate_group(const GemvArgs& a, int g, int* seg, int* row0, int* rows) {
     int s = 0;
@@ -94,32 +102,30 @@ struct Q80X {
     float s[2];
 };
 
-__device__ __forceinline__ void q80_quantise_x(const float* v, Q80X& q) {
+// One 32-value block -> 3 x 8 digit words + scale, with add-magic rounding (1.5 * 2^23: the rounded integer sits in
+// the low mantissa bits as two's complement, ties to even like rintf).
+__device__ __forceinline__ void q80_quantise_block(const float* v, uint32_t* da, uint32_t* db, uint32_t* dc, float* s) {
+    const float MAGIC = 12582912.0f;
+    float mx = 0.0f;
 #pragma unroll
-    for (int b = 0; b < 2; ++b) {
-        float mx = 0.0f;
+    for (int i = 0; i < 32; ++i) mx = fmaxf(mx, fabsf(v[i]));
+    const float inv = mx > 0.0f ? 127.0f / mx : 0.0f;
+    *s = mx * (1.0f / (127.0f * 128.0f));
 #pragma unroll
-        for (int i = 0; i < 32; ++i) mx = fmaxf(mx, fabsf(v[b * 32 + i]));
-        const float inv = mx > 0.0f ? 127.0f / mx : 0.0f;
-        q.s[b] = mx * (1.0f / (127.0f * 128.0f));
+    for (int w = 0; w < 8; ++w) {
+        uint32_t pa = 0, pb = 0, pc = 0;
 #pragma unroll
-        for (int w = 0; w < 8; ++w) {
-            uint32_t pa = 0, pb = 0, pc = 0;
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const float t = v[b * 32 + w * 4 + e] * inv;
-                const float fa = rintf(t);
-                const float r1 = (t - fa) * 128.0f;
-                const float fb = rintf(r1);
-                const float fc = rintf((r1 - fb) * 128.0f);
-                pa |= ((uint32_t)(int)fa & 0xffu) << (8 * e);
-                pb |= ((uint32_t)(int)fb & 0xffu) << (8 * e);
-                pc |= ((uint32_t)(int)fc & 0xffu) << (8 * e);
-            }
-            q.d[0][b * 8 + w] = (int)pa;
-            q.d[1][b * 8 + w] = (int)pb;
-            q.d[2][b * 8 + w] = (int)pc;
+        for (int e = 0; e < 4; ++e) {
+            const float t = v[w * 4 + e] * inv;
+            const float ma = t + MAGIC;
+            const float r1 = (t - (ma - MAGIC)) * 128.0f;
+            const float mb = r1 + MAGIC;
+            const float mc = (r1 - (mb - MAGIC)) * 128.0f + MAGIC;
+            pa |= (__float_as_uint(ma) & 0xffu) << (8 * e);
+            pb |= (__float_as_uint(mb) & 0xffu) << (8 * e);
+            pc |= (__float_as_uint(mc) & 0xffu) << (8 * e);
         }
+        da[w] = pa, db[w] = pb, dc[w] = pc;
     }
 }
 
@@ -168,7 +174,7 @@ template <int FMT, int GATE_UP, int CPT>
 __global__ void __launch_bounds__(THREADS, 1) gemv_stream_kernel(const __grid_constant__ GemvArgs a) {
     extern __shared__ __align__(128) uint8_t ring[];
     __shared__ uint64_t full[MAX_STAGES], empty[MAX_STAGES];
-    __shared__ float red[2][2][MAX_ROWS][CWARPS];
+    __shared__ float red[2][2][MAX_ROWS][CWARPS];  // [parity][matrix][row][consumer warp]
     __shared__ float ssq[CWARPS];
     __shared__ volatile uint32_t abort_flag;
 
@@ -176,7 +182,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_stream_kernel(const __grid_co
     if (tid == 0) {
         for (int s = 0; s < a.nstages; ++s) {
             mbar_init(&full[s], 1);
-            mbar_init(&empty[s], CWARPS);
+            mbar_init(&empty[s], 1);
         }
         abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -217,8 +223,8 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_stream_kernel(const __grid_co
     }
 
     // ---------------------------------------------------------------- consumers
-    const int cw = a.cw, lanes_of_rows = CWARPS / cw;
-    const int rl = warp / cw, cwi = warp % cw;
+    const int cw = a.cw, G = CWARPS / cw;
+    const int grp = warp / cw, cwi = warp % cw;
     const int c = cwi * 32 + lane, cols = cw * 32;
 
     float scale = 1.0f;
@@ -237,46 +243,90 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_stream_kernel(const __grid_co
         scale = rsqrtf(tot / (float)a.K + a.eps);
     }
 
-    constexpr int XV = FMT == M40_GEMV_Q80 ? 64 : 8;  // activation values per piece
     float xr[FMT == M40_GEMV_Q80 ? 1 : CPT][8];
-    Q80X xq[FMT == M40_GEMV_Q80 ? CPT : 1];
+    Q80X xq;
+    if (FMT == M40_GEMV_Q80) {
+        // digits of the whole row, once per CTA: thread t takes 32-blocks t, t + 512, ...
+        uint32_t* dig = reinterpret_cast<uint32_t*>(ring + a.xq_off);   // [3][K/4] words
+        float* xs = reinterpret_cast<float*>(dig + 3 * (a.K / 4));      // [K/32]
+        for (int blk = tid; blk < a.K / 32; blk += CONSUMERS) {
+            float v[32];
+            const int k0 = blk * 32;
 #pragma unroll
-    for (int j = 0; j < CPT; ++j) {
-        const int p = c + j * cols;
-        float v[XV];
-#pragma unroll
-        for (int i = 0; i < XV; ++i) v[i] = 0.0f;
-        if (p < a.pieces) {
-            const int k0 = p * XV;
-#pragma unroll
-            for (int i = 0; i < XV; i += 4) {
+            for (int i = 0; i < 32; i += 4) {
                 const float4 t = *reinterpret_cast<const float4*>(a.x + k0 + i);
                 v[i] = t.x, v[i + 1] = t.y, v[i + 2] = t.z, v[i + 3] = t.w;
             }
             if (a.norm_w) {
 #pragma unroll
-                for (int i = 0; i < XV; ++i) {
+                for (int i = 0; i < 32; ++i) {
                     const float w = a.norm_f32 ? reinterpret_cast<const float*>(a.norm_w)[k0 + i]
                                                : __half2float(reinterpret_cast<const __half*>(a.norm_w)[k0 + i]);
                     v[i] = v[i] * scale * w;
                 }
-                if (a.xn_out && blockIdx.x == 0 && rl == 0) {
+                if (a.xn_out && blockIdx.x == 0) {
 #pragma unroll
-                    for (int i = 0; i < XV; i += 4)
+                    for (int i = 0; i < 32; i += 4)
                         *reinterpret_cast<float4*>(a.xn_out + k0 + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
                 }
             }
-        }
-        if (FMT == M40_GEMV_Q80) {
-            q80_quantise_x(v, xq[j]);
-        } else {
+            uint32_t da[8], db[8], dc[8];
+            float s;
+            q80_quantise_block(v, da, db, dc, &s);
 #pragma unroll
-            for (int i = 0; i < 8; ++i) xr[j][i] = v[i];
+            for (int w = 0; w < 8; ++w) {
+                dig[blk * 8 + w] = da[w];
+                dig[a.K / 4 + blk * 8 + w] = db[w];
+                dig[2 * (a.K / 4) + blk * 8 + w] = dc[w];
+            }
+            xs[blk] = s;
+        }
+        consumer_barrier();
+#pragma unroll
+        for (int i = 0; i < 16; ++i) xq.d[0][i] = xq.d[1][i] = xq.d[2][i] = 0;
+        xq.s[0] = xq.s[1] = 0.0f;
+        if (c < a.pieces) {
+#pragma unroll
+            for (int pl = 0; pl < 3; ++pl)
+#pragma unroll
+                for (int i = 0; i < 16; i += 4) {
+                    const uint4 t = *reinterpret_cast<const uint4*>(dig + pl * (a.K / 4) + c * 16 + i);
+                    xq.d[pl][i] = (int)t.x, xq.d[pl][i + 1] = (int)t.y, xq.d[pl][i + 2] = (int)t.z, xq.d[pl][i + 3] = (int)t.w;
+                }
+            xq.s[0] = xs[2 * c];
+            xq.s[1] = xs[2 * c + 1];
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < CPT; ++j) {
+            const int p = c + j * cols;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) xr[j][i] = 0.0f;
+            if (p < a.pieces) {
+                const int k0 = p * 8;
+                const float4 t0 = *reinterpret_cast<const float4*>(a.x + k0);
+                const float4 t1 = *reinterpret_cast<const float4*>(a.x + k0 + 4);
+                xr[j][0] = t0.x, xr[j][1] = t0.y, xr[j][2] = t0.z, xr[j][3] = t0.w;
+                xr[j][4] = t1.x, xr[j][5] = t1.y, xr[j][6] = t1.z, xr[j][7] = t1.w;
+                if (a.norm_w) {
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const float w = a.norm_f32 ? reinterpret_cast<const float*>(a.norm_w)[k0 + i]
+                                                   : __half2float(reinterpret_cast<const __half*>(a.norm_w)[k0 + i]);
+                        xr[j][i] = xr[j][i] * scale * w;
+                    }
+                    if (a.xn_out && blockIdx.x == 0 && grp == 0) {
+                        *reinterpret_cast<float4*>(a.xn_out + k0) = make_float4(xr[j][0], xr[j][1], xr[j][2], xr[j][3]);
+                        *reinterpret_cast<float4*>(a.xn_out + k0 + 4) = make_float4(xr[j][4], xr[j][5], xr[j][6], xr[j][7]);
+                    }
+                }
+            }
         }
     }
 
     constexpr uint32_t PIECE_BYTES = FMT == M40_GEMV_Q80 ? 68u : 16u;
-    for (int i = 0; i < my_groups; ++i) {
+    int it = 0;  // this group's stage counter (parity of the reduction buffer)
+    for (int i = grp; i < my_groups; i += G, ++it) {
         const int s = i % a.nstages;
         bool ok = abort_flag == 0;
         if (ok && !mbar_wait(&full[s], (uint32_t)((i / a.nstages) & 1))) {
@@ -289,64 +339,78 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_stream_kernel(const __grid_co
         const SegDev& sg = a.seg[sidx];
         const uint8_t* st = ring + (size_t)s * a.stage_bytes;
         float add_final = 0.0f;
-        if (cw > 1 && ok && tid < rows) add_final = load_addend(sg, row0 + tid);
+        if (cw > 1 && ok && c < rows) add_final = load_addend(sg, row0 + c);
         if (ok) {
-            for (int r = rl; r < rows; r += lanes_of_rows) {
+            for (int r = 0; r < rows; r += 2) {  // two rows per pass: independent chains for the shuffles
+                const bool two = r + 1 < rows;
                 const uint8_t* rowp = st + (size_t)r * a.row_bytes;
-                float acc = 0.0f, acc2 = 0.0f, add = 0.0f;
-                if (cw == 1 && lane == 0) add = load_addend(sg, row0 + r);
+                float acc[2] = {0.0f, 0.0f}, acc2[2] = {0.0f, 0.0f}, add[2] = {0.0f, 0.0f};
+                if (cw == 1 && lane == 0) {
+                    add[0] = load_addend(sg, row0 + r);
+                    if (two) add[1] = load_addend(sg, row0 + r + 1);
+                }
 #pragma unroll
                 for (int j = 0; j < CPT; ++j) {
                     const int p = c + j * cols;
                     if (p < a.pieces) {
-                        if (FMT == M40_GEMV_Q80) {
-                            acc += q80_pair_dot(reinterpret_cast<const uint32_t*>(rowp + (size_t)p * PIECE_BYTES), xq[j]);
-                            if (GATE_UP)
-                                acc2 += q80_pair_dot(
-                                    reinterpret_cast<const uint32_t*>(rowp + mat2_off + (size_t)p * PIECE_BYTES), xq[j]);
-                        } else {
-                            acc += dot8(*reinterpret_cast<const uint4*>(rowp + (size_t)p * PIECE_BYTES), xr[j]);
-                            if (GATE_UP)
-                                acc2 += dot8(*reinterpret_cast<const uint4*>(rowp + mat2_off + (size_t)p * PIECE_BYTES), xr[j]);
+#pragma unroll
+                        for (int rr = 0; rr < 2; ++rr) {
+                            if (rr == 1 && !two) break;
+                            const uint8_t* pp = rowp + (size_t)rr * a.row_bytes + (size_t)p * PIECE_BYTES;
+                            if (FMT == M40_GEMV_Q80) {
+                                acc[rr] += q80_pair_dot(reinterpret_cast<const uint32_t*>(pp), xq);
+                                if (GATE_UP) acc2[rr] += q80_pair_dot(reinterpret_cast<const uint32_t*>(pp + mat2_off), xq);
+                            } else {
+                                acc[rr] += dot8(*reinterpret_cast<const uint4*>(pp), xr[j]);
+                                if (GATE_UP) acc2[rr] += dot8(*reinterpret_cast<const uint4*>(pp + mat2_off), xr[j]);
+                            }
                         }
                     }
                 }
-                acc = warp_sum(acc);
-                if (GATE_UP) acc2 = warp_sum(acc2);
+#pragma unroll
+                for (int rr = 0; rr < 2; ++rr) {
+                    acc[rr] = warp_sum(acc[rr]);
+                    if (GATE_UP) acc2[rr] = warp_sum(acc2[rr]);
+                }
                 if (lane == 0) {
-                    if (cw == 1) {
-                        store_row<GATE_UP>(sg, row0 + r, acc, acc2, add);
-                    } else {
-                        red[i & 1][0][r][cwi] = acc;
-                        if (GATE_UP) red[i & 1][1][r][cwi] = acc2;
+#pragma unroll
+                    for (int rr = 0; rr < 2; ++rr) {
+                        if (rr == 1 && !two) break;
+                        if (cw == 1) {
+                            store_row<GATE_UP>(sg, row0 + r + rr, acc[rr], acc2[rr], add[rr]);
+                        } else {
+                            red[it & 1][0][r + rr][warp] = acc[rr];
+                            if (GATE_UP) red[it & 1][1][r + rr][warp] = acc2[rr];
+                        }
                     }
                 }
             }
         }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&empty[s]);  // this warp has finished reading the stage
         if (cw > 1) {
-            consumer_barrier();
-            if (ok && tid < rows) {
+            group_barrier(grp, cols);  // every warp of the group has read the stage and written its partials
+            if (c == 0) mbar_arrive(&empty[s]);
+            if (ok && c < rows) {
                 float v = 0.0f, v2 = 0.0f;
                 for (int k = 0; k < cw; ++k) {
-                    v += red[i & 1][0][tid][k];
-                    if (GATE_UP) v2 += red[i & 1][1][tid][k];
+                    v += red[it & 1][0][c][grp * cw + k];
+                    if (GATE_UP) v2 += red[it & 1][1][c][grp * cw + k];
                 }
-                store_row<GATE_UP>(sg, row0 + tid, v, v2, add_final);
+                store_row<GATE_UP>(sg, row0 + c, v, v2, add_final);
             }
+        } else {
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty[s]);
         }
     }
 }
 
 template <int FMT, int GATE_UP, int CPT>
-int launch(M40llmCudaContext* ctx, cudaStream_t s, const GemvArgs& a, int grid) {
+int launch(M40llmCudaContext* ctx, cudaStream_t s, const GemvArgs& a, int grid, size_t smem) {
     static bool attr_set[64] = {};
-    const size_t smem = (size_t)a.nstages * a.stage_bytes;
     const int dev = ctx->device_id;
     if (dev < 0 || dev >= 64 || !attr_set[dev]) {
         if (cudaFuncSetAttribute(gemv_stream_kernel<FMT, GATE_UP, CPT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 (int)RING_MAX) != cudaSuccess)
+                                 (int)SMEM_MAX) != cudaSuccess)
             return -2;
         if (dev >= 0 && dev < 64) attr_set[dev] = true;
     }
@@ -355,14 +419,12 @@ int launch(M40llmCudaContext* ctx, cudaStream_t s, const GemvArgs& a, int grid) 
     return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 
-template <int FMT, int GATE_UP>
-int launch_cpt(M40llmCudaContext* ctx, cudaStream_t s, const GemvArgs& a, int grid, int cpt) {
-    if (cpt == 1) return launch<FMT, GATE_UP, 1>(ctx, s, a, grid);
-    if (cpt == 2) return launch<FMT, GATE_UP, 2>(ctx, s, a, grid);
-    if (FMT == M40_GEMV_F16) {
-        if (cpt == 4) return launch<M40_GEMV_F16, GATE_UP, 4>(ctx, s, a, grid);
-        if (cpt == 8) return launch<M40_GEMV_F16, GATE_UP, 8>(ctx, s, a, grid);
-    }
+template <int GATE_UP>
+int launch_fmt(M40llmCudaContext* ctx, cudaStream_t s, const GemvArgs& a, int grid, size_t smem, int fmt, int cpt) {
+    if (fmt == M40_GEMV_Q80) return launch<M40_GEMV_Q80, GATE_UP, 1>(ctx, s, a, grid, smem);
+    if (cpt == 1) return launch<M40_GEMV_F16, GATE_UP, 1>(ctx, s, a, grid, smem);
+    if (cpt == 2) return launch<M40_GEMV_F16, GATE_UP, 2>(ctx, s, a, grid, smem);
+    if (cpt == 4) return launch<M40_GEMV_F16, GATE_UP, 4>(ctx, s, a, grid, smem);
     return 1;
 }
 
@@ -375,16 +437,19 @@ int m40_gemv_stream(M40llmCudaContext* ctx, cudaStream_t s, const float* x, int 
     if (nseg < 1 || nseg > MAX_SEGS || K <= 0 || !aligned16(x)) return 1;
     GemvArgs a = {};
     int cpt_max;
+    uint32_t xq_bytes = 0;
     if (fmt == M40_GEMV_F16) {
         if (K % 8 != 0) return 1;
         a.row_bytes = (uint32_t)K * 2u;
         a.pieces = K / 8;
-        cpt_max = 8;
+        cpt_max = 4;
     } else if (fmt == M40_GEMV_Q80) {
         if (K % 256 != 0) return 1;  // whole block pairs and 16-byte row pitch
         a.row_bytes = (uint32_t)(K / 32) * 34u;
         a.pieces = K / 64;
-        cpt_max = 2;
+        cpt_max = 1;
+        xq_bytes = (uint32_t)(3 * K + (K / 32) * 4);
+        xq_bytes = (xq_bytes + 127u) & ~127u;
     } else {
         return 1;
     }
@@ -394,47 +459,62 @@ int m40_gemv_stream(M40llmCudaContext* ctx, cudaStream_t s, const float* x, int 
         if (gate_up && (!segs[i].W2 || !aligned16(segs[i].W2))) return 1;
     }
     if (norm && norm->w && (!aligned16(norm->w) || (norm->xn_out && !aligned16(norm->xn_out)))) return 1;
+    if ((uint64_t)a.row_bytes * nmat > STAGE_MAX || xq_bytes + 2u * a.row_bytes * nmat > SMEM_MAX) return 1;
 
-    // Threads per row (cw warps) and pieces per thread: the fewest warps per row whose register slice fits,
-    // with at least one row per row lane in a stage.
+    // Warps per group: the fewest whose per-thread register slice of x fits.
     int cw = 0, cpt = 0;
     for (int w = 1; w <= CWARPS; w *= 2) {
-        int need = (a.pieces + w * 32 - 1) / (w * 32);
+        const int need = (a.pieces + w * 32 - 1) / (w * 32);
         int p2 = 1;
         while (p2 < need) p2 *= 2;
         if (p2 > cpt_max) continue;
-        if ((uint64_t)(CWARPS / w) * a.row_bytes * nmat > STAGE_MAX) continue;
         cw = w;
         cpt = p2;
         break;
     }
     if (!cw) return 1;
-    const int rl = CWARPS / cw;
+    const int G = CWARPS / cw;
+    const uint32_t ring_max = SMEM_MAX - xq_bytes;
 
-    // Rows per stage: a multiple of the row lanes within the stage budget; among the candidates the one that
-    // leaves the persistent CTAs the most evenly loaded (ties: the larger stage).
+    // Rows per stage: within the stage budget, a ring deep enough that every group can hold a stage while two
+    // more are in flight (when the row size allows), and among those the choice that loads the persistent CTAs
+    // most evenly (ties: the larger stage).
     const int grid_max = ctx->sm_count > 0 ? ctx->sm_count : 1;
     int best_R = 0;
-    double best_eff = -1.0;
-    for (int R = rl; R <= MAX_ROWS; R += rl) {
-        if ((uint64_t)R * a.row_bytes * nmat > STAGE_MAX) break;
-        long long groups = 0;
-        for (int i = 0; i < nseg; ++i) groups += (segs[i].N + R - 1) / R;
-        const long long grid = groups < grid_max ? groups : grid_max;
-        const long long per = (groups + grid - 1) / grid;
-        const double eff = (double)groups / (double)(per * grid);
-        if (eff >= best_eff - 1e-9) {
-            best_eff = eff > best_eff ? eff : best_eff;
-            best_R = R;
+    {
+        double eff_of[MAX_ROWS + 1];
+        int deep_of[MAX_ROWS + 1];
+        int n_cand = 0, any_deep = 0;
+        double best_eff = -1.0;
+        for (int R = 1; R <= MAX_ROWS; ++R) {
+            const uint64_t sb = ((uint64_t)R * a.row_bytes * nmat + 127u) & ~(uint64_t)127u;
+            if (sb > STAGE_MAX) break;
+            long long nst = (long long)(ring_max / sb);
+            if (nst > MAX_STAGES) nst = MAX_STAGES;
+            if (nst < 2) break;
+            long long groups = 0;
+            for (int i = 0; i < nseg; ++i) groups += (segs[i].N + R - 1) / R;
+            const long long grid = groups < grid_max ? groups : grid_max;
+            const long long per = (groups + grid - 1) / grid;
+            eff_of[R] = (double)groups / (double)(per * grid);
+            deep_of[R] = nst >= G + 2 ? 1 : 0;
+            any_deep |= deep_of[R];
+            n_cand = R;
         }
+        for (int R = 1; R <= n_cand; ++R)
+            if (deep_of[R] == any_deep && eff_of[R] > best_eff) best_eff = eff_of[R];
+        // the largest stage within 3 % of the best balance: fewer barrier round trips per byte
+        for (int R = 1; R <= n_cand; ++R)
+            if (deep_of[R] == any_deep && eff_of[R] >= best_eff - 0.03) best_R = R;
     }
     if (!best_R) return 1;
     a.R = best_R;
     a.cw = cw;
     a.stage_bytes = ((uint32_t)a.R * a.row_bytes * nmat + 127u) & ~127u;
-    a.nstages = (int)(RING_MAX / a.stage_bytes);
+    a.nstages = (int)(ring_max / a.stage_bytes);
     if (a.nstages > MAX_STAGES) a.nstages = MAX_STAGES;
     if (a.nstages < 2) return 1;
+    a.xq_off = (uint32_t)a.nstages * a.stage_bytes;
     int g = 0;
     for (int i = 0; i < nseg; ++i) {
         a.seg[i].W = (const uint8_t*)segs[i].W;
@@ -458,7 +538,6 @@ int m40_gemv_stream(M40llmCudaContext* ctx, cudaStream_t s, const float* x, int 
         a.xn_out = norm->xn_out;
     }
     const int grid = g < grid_max ? g : grid_max;
-    if (fmt == M40_GEMV_F16)
-        return gate_up ? launch_cpt<M40_GEMV_F16, 1>(ctx, s, a, grid, cpt) : launch_cpt<M40_GEMV_F16, 0>(ctx, s, a, grid, cpt);
-    return gate_up ? launch_cpt<M40_GEMV_Q80, 1>(ctx, s, a, grid, cpt) : launch_cpt<M40_GEMV_Q80, 0>(ctx, s, a, grid, cpt);
+    const size_t smem = (size_t)a.xq_off + xq_bytes;
+    return gate_up ? launch_fmt<1>(ctx, s, a, grid, smem, fmt, cpt) : launch_fmt<0>(ctx, s, a, grid, smem, fmt, cpt);
 }
