@@ -156,6 +156,8 @@ __global__ void __launch_bounds__(256) attn_merge_wide_kernel(const float* __res
     __shared__ float sw[256];
     __shared__ float sred[8];
     __shared__ float4 sacc[8][32];
+    pdl_wait();
+    pdl_trigger();
     const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
     const uint32_t h = blockIdx.x, row = blockIdx.y;
     const size_t base = ((size_t)row * q_heads + h) * splits;
@@ -342,7 +344,8 @@ int m40_attention_merge_rows(M40llmCudaContext* ctx, const float* m, const float
                              uint32_t q_heads, uint32_t hd, float* out, uint32_t rows) {
     dim3 grid(q_heads, rows);
     if (merge_wide_ok(o, out, hd, splits, 0))
-        attn_merge_wide_kernel<<<grid, 256, 0, ctx->decode_stream>>>(m, l, o, out, q_heads, hd, splits, 0, 0, 0u);
+        m40_launch_dependent(attn_merge_wide_kernel, grid, dim3(256), 0, ctx->decode_stream, m, l, o, out, q_heads, hd,
+                             splits, (size_t)0, (size_t)0, 0u);
     else
         attn_merge_kernel<<<grid, 128, 0, ctx->decode_stream>>>(m, l, o, out, q_heads, hd, splits, 0, 0, 0u);
     M40_COUNT_LAUNCH(ctx);

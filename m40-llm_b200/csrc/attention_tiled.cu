@@ -79,6 +79,8 @@ __global__ void __launch_bounds__(128, 2) attn_decode_tiled_kernel(DenseAttnArgs
     __half* sK = reinterpret_cast<__half*>(smem_raw);
     __half* sV = reinterpret_cast<__half*>(smem_raw + Cfg::STAGES * Cfg::TILE_BYTES);
 
+    pdl_wait();     // q and the newest cache row come from the previous kernel
+    pdl_trigger();
     const uint32_t split = blockIdx.x, kvh = blockIdx.y, row = blockIdx.z;
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
     const uint32_t g = lane >> 2, t4 = lane & 3u;
@@ -292,9 +294,9 @@ int launch(M40llmCudaContext* ctx, const DenseAttnArgs& a, uint32_t rows) {
         configured |= bit;
     }
     dim3 grid(a.splits, a.kv_heads, rows);
-    kern<<<grid, 128, TiledCfg<HD>::SMEM, ctx->decode_stream>>>(a);
+    const cudaError_t e = m40_launch_dependent(kern, grid, dim3(128), (size_t)TiledCfg<HD>::SMEM, ctx->decode_stream, a);
     M40_COUNT_LAUNCH(ctx);
-    return cudaGetLastError() == cudaSuccess ? 0 : -4;
+    return e == cudaSuccess && cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 
 }  // namespace

@@ -114,6 +114,33 @@ void* m40_ensure_scratch(M40llmCudaContext* ctx, uint32_t kind, size_t bytes, ui
 
 #define M40_COUNT_LAUNCH(ctx) ((ctx)->launches++)
 
+// ----------------------------------------------------------------------------
+// Programmatic dependent launch. A kernel launched through m40_launch_dependent may start while its predecessor
+// on the stream is still running; it must execute pdl_wait() before it reads anything the predecessor wrote and
+// before its own first global write. Kernels call pdl_trigger() early so that their successor's CTAs are placed
+// the moment resources free up. Both are no-ops for plain launches. M40LLM_PDL=0 turns the launch attribute off.
+// ----------------------------------------------------------------------------
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+bool m40_pdl_enabled();
+
+template <typename... KArgs, typename... Args>
+static inline cudaError_t m40_launch_dependent(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                               cudaStream_t s, Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = m40_pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

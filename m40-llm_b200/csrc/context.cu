@@ -387,3 +387,12 @@ int m40llm_persistent_decode_poll(M40llmCudaContext* ctx, uint32_t* out_status, 
 }
 
 }  // extern "C"
+
+bool m40_pdl_enabled() {
+    static int v = -1;
+    if (v < 0) {
+        const char* e = getenv("M40LLM_PDL");
+        v = (e && e[0] == '0') ? 0 : 1;
+    }
+    return v != 0;
+}

@@ -22,6 +22,8 @@ __global__ void __launch_bounds__(64) rope_q_append_kv_rows_kernel(float* __rest
                                                                    uint32_t q_heads, float freq_base, float freq_scale,
                                                                    uint32_t layout, uint32_t* status) {
     __shared__ float red[32];
+    pdl_wait();
+    pdl_trigger();
     const uint32_t row = blockIdx.y, hsel = blockIdx.x;
     const uint32_t hd = kv.head_dim, half = hd / 2u;
     const uint32_t seq = seq_ids[row], pos = positions[row];
@@ -115,10 +117,11 @@ extern "C" int m40llm_qkv_rmsnorm_rope_append_async(M40llmCudaContext* ctx, M40l
         if (rc != 0) return rc;
     }
     dim3 grid(q_heads + kv->num_heads, rows);
-    rope_q_append_kv_rows_kernel<<<grid, 64, 0, s>>>((float*)d_q_out_f32, kbuf, vbuf, *kv, d_seq_ids, d_positions,
-                                                     q_heads, freq_base, freq_scale, rope_layout, ctx->d_status);
+    const cudaError_t e = m40_launch_dependent(rope_q_append_kv_rows_kernel, grid, dim3(64), 0, s, (float*)d_q_out_f32,
+                                               (const float*)kbuf, (const float*)vbuf, *kv, d_seq_ids, d_positions,
+                                               q_heads, freq_base, freq_scale, rope_layout, ctx->d_status);
     M40_COUNT_LAUNCH(ctx);
-    return cudaGetLastError() == cudaSuccess ? 0 : -6;
+    return e == cudaSuccess && cudaGetLastError() == cudaSuccess ? 0 : -6;
 }
 
 // Steps 9-13 of the layer (src/infer/forward.rs:470-667): x1 = x + att.Wo; xn = rmsnorm(x1) * w;

@@ -188,6 +188,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_stream_kernel(const __grid_co
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
+    pdl_trigger();  // the successor may be placed as soon as this CTA's resources free up
     const int my_groups = ((int)blockIdx.x < a.total_groups)
                               ? (a.total_groups - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
     const uint32_t mat2_off = (uint32_t)a.R * a.row_bytes;
@@ -223,6 +224,8 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_stream_kernel(const __grid_co
     }
 
     // ---------------------------------------------------------------- consumers
+    // The weights streamed by the producer above never depend on the previous kernel; the activations do.
+    pdl_wait();
     const int cw = a.cw, G = CWARPS / cw;
     const int grp = warp / cw, cwi = warp % cw;
     const int c = cwi * 32 + lane, cols = cw * 32;
@@ -414,9 +417,9 @@ int launch(M40llmCudaContext* ctx, cudaStream_t s, const GemvArgs& a, int grid, 
             return -2;
         if (dev >= 0 && dev < 64) attr_set[dev] = true;
     }
-    gemv_stream_kernel<FMT, GATE_UP, CPT><<<grid, THREADS, smem, s>>>(a);
+    const cudaError_t e = m40_launch_dependent(gemv_stream_kernel<FMT, GATE_UP, CPT>, dim3(grid), dim3(THREADS), smem, s, a);
     M40_COUNT_LAUNCH(ctx);
-    return cudaGetLastError() == cudaSuccess ? 0 : -2;
+    return e == cudaSuccess && cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 
 template <int GATE_UP>
