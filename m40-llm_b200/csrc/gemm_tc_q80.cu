@@ -3,20 +3,24 @@
 // Q8_0 stores 32 weights as {f16 d; int8 q[32]} (34 bytes, cuda/kernels.cu:856-867 of the reference):
 // w = d * q with a different d for every (row, 32-k block).
 //
-//   raw bytes   TMA (plain 2D box of 128 rows x 272 bytes = 8 blocks per row) straight from the GGUF layout;
-//   dequant     16 worker warps (4 threads per weight row) turn the bytes into TWO f16 tiles in the
-//               128-byte-swizzled K-major layout the MMA reads: hi = rn(d*q) and lo = d*q - hi (exact by FMA),
-//               so hi + lo carries the product to ~2^-22 -- the value the reference computes in f32;
-//   MMA         D[128 x M_pad] += hi.Xh + hi.Xl + lo.Xh with activations split the same way, f32 in TMEM,
-//               one accumulator per tile segment (two TMEM buffers alternate between segments);
+//   raw bytes   TMA (plain 2D box of 128 rows x 272 bytes = 8 blocks per row) straight from the GGUF layout, four
+//               stages deep;
+//   dequant     16 worker warps. Worker group g (4 warps = 128 threads = 128 weight rows) owns the g-th 64-k
+//               sub-block of every raw stage; a thread turns the two blocks of its row into TWO f16 operands,
+//               hi = rn(d*q) and lo = d*q - hi (exact by FMA), so hi + lo carries the product to ~2^-22 -- the value
+//               the reference computes in f32 -- and stores them with tcgen05.st straight into TENSOR MEMORY
+//               (lane = weight row, one column = two f16 along k). No shared-memory round trip for the converted
+//               operand, and the operand ring is seven sub-blocks deep;
+//   MMA         D[128 x M_pad] += hi.Xh + hi.Xl + lo.Xh with the A operand read from tensor memory and the
+//               activations (split the same way) from shared memory, f32 accumulators in TMEM, one accumulator per
+//               tile segment (two alternate between segments);
 //   epilogue    the worker threads read their row of D back (tcgen05.ld) at the end of a segment.
 //
-// Work is split stream-K style: the (tile, 256-k unit) space is cut into one contiguous span per CTA
-// (one CTA per SM; shared memory holds two raw stages, three dequantised tile pairs and the activation ring), so every SM streams the same number of
-// weight bytes. A span that crosses tile boundaries writes one partial per tile; the epilogue kernel adds
-// the partials of each tile and applies residual or SiLU(gate)*up.
+// Work is split stream-K style: the (tile, 256-k unit) space is cut into one contiguous span per CTA (one CTA per
+// SM), so every SM streams the same number of weight bytes. A span that crosses tile boundaries writes one partial
+// per tile; the epilogue kernel adds the partials of each tile and applies residual or SiLU(gate)*up.
 //
-// Every wait is bounded; a wait that runs out sets bit 2 of the context's device status word and the CTA
+// Every wait is bounded; a wait that runs out sets bit 4 of the context's device status word and the CTA
 // drains, frees its TMEM and returns.
 #include <cuda.h>
 
@@ -31,9 +35,11 @@ using namespace tc;
 constexpr uint32_t UNIT_K = 256;                       // k per raw stage (8 Q8_0 blocks)
 constexpr uint32_t RAW_ROW_BYTES = UNIT_K / 32 * 34;   // 272
 constexpr uint32_t RAW_BYTES = BLOCK_N * RAW_ROW_BYTES; // 34816
-constexpr uint32_t A_BYTES = BLOCK_N * BLOCK_K * 2;    // 16384: one converted 64-k sub-block
-constexpr uint32_t RS = 2, AS = 3, TB = 2;             // ring depths: raw stages, (hi, lo) A tile pairs, TMEM accumulators
-__host__ __device__ constexpr uint32_t b_slots(int m_pad) { return m_pad <= 32 ? 4u : 2u; }  // activation sub-block slots
+constexpr uint32_t RS = 4, TB = 2;                     // ring depths: raw stages, TMEM accumulators
+constexpr uint32_t A_COLS = BLOCK_K;                   // TMEM columns of one converted sub-block: 32 hi + 32 lo
+constexpr uint32_t TMEM_COLS = 512;
+__host__ __device__ constexpr uint32_t a_stages(int m_pad) { return (TMEM_COLS - TB * (uint32_t)m_pad) / A_COLS; }  // 7, 7, 6
+__host__ __device__ constexpr uint32_t b_slots(int m_pad) { return m_pad <= 32 ? 8u : 4u; }  // activation sub-block slots
 
 struct Q80Args {
     float* partial;  // [ctas][seg_max][M][128]
@@ -51,7 +57,6 @@ __device__ __forceinline__ void span_of(const Q80Args& a, uint32_t cta, uint32_t
 
 struct Q80Smem {
     unsigned char* s_raw;
-    unsigned char* s_a;
     uint64_t *raw_full, *raw_empty, *a_full, *a_empty, *t_full, *t_empty;
     volatile uint32_t* abort_flag;
 };
@@ -60,17 +65,20 @@ constexpr uint32_t WORKER_WARPS = 16;                    // 4 threads per weight
 constexpr uint32_t WORKER_THREADS = WORKER_WARPS * 32;   // 512
 constexpr uint32_t CTA_THREADS = 96 + WORKER_THREADS;    // + weight producer, MMA issuer, activation producer warps
 
-// One worker thread owns (weight row r, quarter C4): it dequantises weights [16*C4, 16*C4+16) of every 64-k
-// sub-block into the hi and lo f16 tiles, and at the end of a tile segment reads columns
+// One worker thread owns weight row r of the tile and, in every raw stage, the C4-th 64-k sub-block (two Q8_0
+// blocks, bytes [68*C4, 68*C4+68) of the row: 4-byte aligned). At the end of a tile segment it reads columns
 // [C4*M_PAD/4, +M_PAD/4) of its row of the accumulator.
 template <int M_PAD, int C4>
 __device__ __forceinline__ void q80_worker(const Q80Args& a, const Q80Smem& sm, uint32_t tmem_base, uint32_t u0,
                                            uint32_t u1, uint32_t lane_group, uint32_t lane) {
     constexpr int COLS = M_PAD / 4;
+    constexpr uint32_t AST = a_stages(M_PAD);
+    constexpr uint32_t A_COL0 = TB * M_PAD;
     const uint32_t r = lane_group * 32 + lane;  // weight row of the tile == TMEM lane
+    const uint32_t tmem_lane = tmem_base + ((lane_group * 32u) << 16);
     bool ok = true;
-    uint32_t ucount = 0;
-    // every wait of a worker warp is made warp-uniform so the warp-collective tcgen05.ld stays converged
+    uint32_t icount = 0;  // raw stages consumed by this CTA so far
+    // every wait of a worker warp is made warp-uniform so the warp-collective tcgen05 instructions stay converged
     auto wwait = [&](uint64_t* bar, uint32_t parity) {
         const bool r0 = mbar_wait(bar, parity);
         return (bool)__all_sync(0xffffffffu, r0);
@@ -80,62 +88,54 @@ __device__ __forceinline__ void q80_worker(const Q80Args& a, const Q80Smem& sm, 
         const uint32_t kb_begin = pos % a.units_per_tile;
         uint32_t kb_end = kb_begin + (u1 - pos);
         if (kb_end > a.units_per_tile) kb_end = a.units_per_tile;
-        for (uint32_t kb = kb_begin; kb < kb_end && ok; ++kb) {
-            const uint32_t i = ucount / 4, rs = i % RS;
-            if (!wwait(&sm.raw_full[rs], (i / RS) & 1u)) { ok = false; break; }
-            const unsigned char* row = sm.s_raw + rs * RAW_BYTES + r * RAW_ROW_BYTES;
+        for (uint32_t kb = kb_begin; kb < kb_end && ok; ++kb, ++icount) {
+            const uint32_t rs = icount % RS;
+            const uint32_t u = icount * 4u + C4, as = u % AST;  // this group's sub-block and its operand stage
+            if (!wwait(&sm.raw_full[rs], (icount / RS) & 1u)) { ok = false; break; }
+            // 68 bytes = words [C4, C4+17) of the five 16-byte chunks that cover them; the row pitch is 17 chunks,
+            // so the 16-byte reads of a warp's 32 rows fall on distinct banks
+            const uint4* chunk = reinterpret_cast<const uint4*>(sm.s_raw + rs * RAW_BYTES + r * RAW_ROW_BYTES) + (68 * C4) / 16;
+            uint32_t L[20];
 #pragma unroll
-            for (uint32_t sub = 0; sub < 4; ++sub) {
-                const uint32_t u = ucount, as = u % AS;
-                if (u >= AS && !wwait(&sm.a_empty[as], ((u / AS) - 1) & 1u)) { ok = false; break; }
-                // this thread's 16 weights: bytes [b0, b0+16) of the row (2-byte aligned), scale at the block start
-                const uint32_t blk_off = (2 * sub + (C4 >> 1)) * 34;
-                const __half d = *reinterpret_cast<const __half*>(row + blk_off);
-                const uint32_t b0 = blk_off + 2 + (C4 & 1) * 16;
-                const uint32_t bs = b0 & ~3u;             // 4-byte aligned start of the word window
-                const bool upper_first = (b0 & 2u) != 0u;  // first pair is the upper half of word 0
-                const uint32_t chunk = bs >> 4, wo = (bs & 15u) >> 2;
-                uint32_t w[8];
-                {
-                    const uint4 t0 = *reinterpret_cast<const uint4*>(row + chunk * 16);
-                    w[0] = t0.x; w[1] = t0.y; w[2] = t0.z; w[3] = t0.w;
-                    if (wo + (upper_first ? 5u : 4u) > 4u) {
-                        const uint4 t1 = *reinterpret_cast<const uint4*>(row + chunk * 16 + 16);
-                        w[4] = t1.x; w[5] = t1.y; w[6] = t1.z; w[7] = t1.w;
-                    } else {
-                        w[4] = w[5] = w[6] = w[7] = 0u;
+            for (int i = 0; i < 5; ++i) {
+                const uint4 t = chunk[i];
+                L[4 * i] = t.x, L[4 * i + 1] = t.y, L[4 * i + 2] = t.z, L[4 * i + 3] = t.w;
+            }
+            if (u >= AST && !wwait(&sm.a_empty[as], ((u / AST) - 1) & 1u)) { ok = false; break; }
+            tc_fence_after();
+            const __half2 bias = __float2half2_rn(1152.0f);
+            const uint32_t col = tmem_lane + A_COL0 + as * A_COLS;
+#pragma unroll
+            for (int blk = 0; blk < 2; ++blk) {
+                // block 0: scale in the low half of word 0, weights from byte 2; block 1: scale in the high half
+                // of word 8, weights word aligned from word 9
+                const uint32_t dbits = blk == 0 ? (L[C4] & 0xffffu) : (L[C4 + 8] >> 16);
+                const __half2 d2 = __half2half2(__ushort_as_half((unsigned short)dbits));
+                uint32_t hi[16], lo[16];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    uint32_t word = blk == 0 ? __funnelshift_r(L[C4 + j], L[C4 + j + 1], 16) : L[C4 + 9 + j];
+                    word ^= 0x80808080u;
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        const uint32_t y = __byte_perm(word, 0x64646464u, h ? 0x7362 : 0x5140);  // (1024+u0, 1024+u1)
+                        const __half2 q2 = __hsub2(*reinterpret_cast<const __half2*>(&y), bias);  // exact ints
+                        const __half2 h2 = __hmul2(q2, d2);                                       // rn(d*q)
+                        const __half2 l2 = __hfma2(q2, d2, __hneg2(h2));                          // d*q - hi, exact
+                        hi[2 * j + h] = *reinterpret_cast<const uint32_t*>(&h2);
+                        lo[2 * j + h] = *reinterpret_cast<const uint32_t*>(&l2);
                     }
                 }
-                const __half2 bias = __float2half2_rn(1152.0f);
-                const __half2 d2 = __half2half2(d);
-                uint32_t hi[8], lo[8];
-#pragma unroll
-                for (uint32_t p = 0; p < 8; ++p) {
-                    // pair p sits at byte offset 2p from b0: word (p + upper_first) / 2, alternating halves
-                    const uint32_t q = p + (upper_first ? 1u : 0u);
-                    const uint32_t word = w[wo + (q >> 1)] ^ 0x80808080u;
-                    const uint32_t h = __byte_perm(word, 0x64646464u, (q & 1u) ? 0x7362 : 0x5140);  // (1024+u0, 1024+u1)
-                    const __half2 q2 = __hsub2(*reinterpret_cast<const __half2*>(&h), bias);          // exact ints
-                    const __half2 h2 = __hmul2(q2, d2);                                               // rn(d*q)
-                    const __half2 l2 = __hfma2(q2, d2, __hneg2(h2));                                  // d*q - hi, exact
-                    hi[p] = *reinterpret_cast<const uint32_t*>(&h2);
-                    lo[p] = *reinterpret_cast<const uint32_t*>(&l2);
-                }
-                unsigned char* dst = sm.s_a + as * 2 * A_BYTES + (r >> 3) * 1024 + (r & 7u) * 128;
-                const uint32_t c0 = ((2 * C4) ^ (r & 7u)) * 16, c1 = ((2 * C4 + 1) ^ (r & 7u)) * 16;
-                *reinterpret_cast<uint4*>(dst + c0) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
-                *reinterpret_cast<uint4*>(dst + c1) = make_uint4(hi[4], hi[5], hi[6], hi[7]);
-                *reinterpret_cast<uint4*>(dst + A_BYTES + c0) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
-                *reinterpret_cast<uint4*>(dst + A_BYTES + c1) = make_uint4(lo[4], lo[5], lo[6], lo[7]);
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                // one arrival per warp: hundreds of per-thread arrivals on one barrier word serialise in shared memory
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&sm.a_full[as]);
-                ++ucount;
+                tmem_st_x16(col + blk * 16, hi);
+                tmem_st_x16(col + 32 + blk * 16, lo);
             }
-            if (!ok) break;
+            tmem_st_wait();
+            tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&sm.raw_empty[rs]);
+            if (lane == 0) {
+                mbar_arrive(&sm.a_full[as]);
+                mbar_arrive(&sm.raw_empty[rs]);  // the raw bytes of this stage are in registers / converted
+            }
         }
         if (!ok) break;
         // ---- end of the tile segment: read this row's accumulator columns and store the partial
@@ -172,17 +172,18 @@ __global__ void __launch_bounds__(CTA_THREADS, 1) gemm_tc_q80_kernel(const __gri
                                                                      Q80Args a) {
     constexpr uint32_t B_BYTES = M_PAD * BLOCK_K * 2;  // one of hi / lo for a 64-k sub-block
     constexpr uint32_t BS = b_slots(M_PAD);
+    constexpr uint32_t AST = a_stages(M_PAD);
+    constexpr uint32_t A_COL0 = TB * M_PAD;
     extern __shared__ unsigned char smem_unaligned[];
     unsigned char* smem = smem_unaligned + ((1024u - (smem_u32(smem_unaligned) & 1023u)) & 1023u);
     unsigned char* s_raw = smem;                             // RS x RAW_BYTES
-    unsigned char* s_a = s_raw + RS * RAW_BYTES;             // AS x (hi, lo) x A_BYTES (1024-aligned: RAW_BYTES = 34 KB)
-    unsigned char* s_b = s_a + AS * 2 * A_BYTES;             // BS x (hi, lo)
+    unsigned char* s_b = s_raw + RS * RAW_BYTES;             // BS x (hi, lo); 1024-aligned: RAW_BYTES = 34 KB
     uint64_t* bars = reinterpret_cast<uint64_t*>(s_b + BS * 2 * B_BYTES);
     uint64_t* raw_full = bars;
     uint64_t* raw_empty = raw_full + RS;
     uint64_t* a_full = raw_empty + RS;
-    uint64_t* a_empty = a_full + AS;
-    uint64_t* b_full = a_empty + AS;
+    uint64_t* a_empty = a_full + AST;
+    uint64_t* b_full = a_empty + AST;
     uint64_t* b_empty = b_full + BS;
     uint64_t* t_full = b_empty + BS;
     uint64_t* t_empty = t_full + TB;
@@ -190,7 +191,6 @@ __global__ void __launch_bounds__(CTA_THREADS, 1) gemm_tc_q80_kernel(const __gri
     volatile uint32_t* abort_flag = tmem_slot + 1;
 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
-    constexpr uint32_t TMEM_COLS = TB * M_PAD < 32 ? 32 : TB * M_PAD;  // 32 / 64 / 128: powers of two
 
     uint32_t u0, u1;
     span_of(a, blockIdx.x, &u0, &u1);
@@ -198,7 +198,7 @@ __global__ void __launch_bounds__(CTA_THREADS, 1) gemm_tc_q80_kernel(const __gri
 
     if (threadIdx.x == 0) {
         for (uint32_t i = 0; i < RS; ++i) { mbar_init(&raw_full[i], 1); mbar_init(&raw_empty[i], WORKER_WARPS); }
-        for (uint32_t i = 0; i < AS; ++i) { mbar_init(&a_full[i], WORKER_WARPS); mbar_init(&a_empty[i], 1); }
+        for (uint32_t i = 0; i < AST; ++i) { mbar_init(&a_full[i], 4); mbar_init(&a_empty[i], 1); }  // 4 warps per worker group
         for (uint32_t i = 0; i < BS; ++i) { mbar_init(&b_full[i], 1); mbar_init(&b_empty[i], 1); }
         for (uint32_t i = 0; i < TB; ++i) { mbar_init(&t_full[i], 1); mbar_init(&t_empty[i], WORKER_WARPS); }
         *abort_flag = 0;
@@ -263,19 +263,19 @@ __global__ void __launch_bounds__(CTA_THREADS, 1) gemm_tc_q80_kernel(const __gri
                 const uint32_t d_tmem = tmem_base + tb * M_PAD;
                 const uint32_t n_sub = (kb_end - kb_begin) * 4;
                 for (uint32_t j = 0; j < n_sub && ok; ++j, ++u) {
-                    const uint32_t as = u % AS, bs = u % BS;
-                    if (!mbar_wait(&a_full[as], (u / AS) & 1u) || !mbar_wait(&b_full[bs], (u / BS) & 1u)) { ok = false; break; }
+                    const uint32_t as = u % AST, bs = u % BS;
+                    if (!mbar_wait(&a_full[as], (u / AST) & 1u) || !mbar_wait(&b_full[bs], (u / BS) & 1u)) { ok = false; break; }
                     tc_fence_after();
-                    const uint32_t sa = smem_u32(s_a + as * 2 * A_BYTES);
+                    const uint32_t ta = tmem_base + A_COL0 + as * A_COLS;  // hi columns [0,32), lo columns [32,64)
                     const uint32_t sb = smem_u32(s_b + bs * 2 * B_BYTES);
 #pragma unroll
                     for (uint32_t kk = 0; kk < BLOCK_K / UMMA_K; ++kk) {
                         const uint32_t off = kk * UMMA_K * 2;
-                        const uint64_t a_hi = make_desc_sw128(sa + off), a_lo = make_desc_sw128(sa + A_BYTES + off);
                         const uint64_t b_hi = make_desc_sw128(sb + off), b_lo = make_desc_sw128(sb + B_BYTES + off);
-                        umma_f16(d_tmem, a_hi, b_hi, idesc, (j | kk) != 0u);
-                        umma_f16(d_tmem, a_hi, b_lo, idesc, 1u);
-                        umma_f16(d_tmem, a_lo, b_hi, idesc, 1u);
+                        const uint32_t a_hi = ta + kk * (UMMA_K / 2), a_lo = a_hi + 32;
+                        umma_f16_ts(d_tmem, a_hi, b_hi, idesc, (j | kk) != 0u);
+                        umma_f16_ts(d_tmem, a_hi, b_lo, idesc, 1u);
+                        umma_f16_ts(d_tmem, a_lo, b_hi, idesc, 1u);
                     }
                     umma_commit(&a_empty[as]);
                     umma_commit(&b_empty[bs]);
@@ -288,7 +288,7 @@ __global__ void __launch_bounds__(CTA_THREADS, 1) gemm_tc_q80_kernel(const __gri
         }
     } else {
         // ---------------- workers: warps 3..18; TMEM lane group = warp % 4, row quarter = (warp - 3) / 4
-        Q80Smem sm = {s_raw, s_a, raw_full, raw_empty, a_full, a_empty, t_full, t_empty, abort_flag};
+        Q80Smem sm = {s_raw, raw_full, raw_empty, a_full, a_empty, t_full, t_empty, abort_flag};
         const uint32_t lane_group = warp & 3u;
         switch ((warp - 3u) >> 2) {
             case 0: q80_worker<M_PAD, 0>(a, sm, tmem_base, u0, u1, lane_group, lane); break;
@@ -417,7 +417,7 @@ __global__ void split_activations_q80_kernel(const float* __restrict__ x, __half
 template <int M_PAD>
 int launch_q80(M40llmCudaContext* ctx, cudaStream_t s, const CUtensorMap* mW, const CUtensorMap& mXh,
                const CUtensorMap& mXl, const Q80Args& a) {
-    constexpr size_t smem = RS * RAW_BYTES + AS * 2 * A_BYTES + b_slots(M_PAD) * 2 * (M_PAD * BLOCK_K * 2) + 32 * 8 + 16 + 1024;
+    constexpr size_t smem = RS * RAW_BYTES + b_slots(M_PAD) * 2 * (M_PAD * BLOCK_K * 2) + 64 * 8 + 16 + 1024;
     auto kern = gemm_tc_q80_kernel<M_PAD>;
     static unsigned long long configured = 0ull;
     const unsigned long long bit = 1ull << (ctx->device_id & 63);
