@@ -38,7 +38,8 @@ constexpr uint32_t RAW_BYTES = BLOCK_N * RAW_ROW_BYTES; // 34816
 constexpr uint32_t RS = 4, TB = 2;                     // ring depths: raw stages, TMEM accumulators
 constexpr uint32_t A_COLS = BLOCK_K;                   // TMEM columns of one converted sub-block: 32 hi + 32 lo
 constexpr uint32_t TMEM_COLS = 512;
-__host__ __device__ constexpr uint32_t a_stages(int m_pad) { return (TMEM_COLS - TB * (uint32_t)m_pad) / A_COLS; }  // 7, 7, 6
+__host__ __device__ constexpr uint32_t acc_cols(int m_pad) { return 2u * (uint32_t)m_pad; }  // [hi.Xh + lo.Xh | hi.Xl]
+__host__ __device__ constexpr uint32_t a_stages(int m_pad) { return (TMEM_COLS - TB * acc_cols(m_pad)) / A_COLS; }  // 7, 6, 4
 __host__ __device__ constexpr uint32_t b_slots(int m_pad) { return m_pad <= 32 ? 8u : 4u; }  // activation sub-block slots
 
 struct Q80Args {
@@ -73,7 +74,7 @@ __device__ __forceinline__ void q80_worker(const Q80Args& a, const Q80Smem& sm, 
                                            uint32_t u1, uint32_t lane_group, uint32_t lane) {
     constexpr int COLS = M_PAD / 4;
     constexpr uint32_t AST = a_stages(M_PAD);
-    constexpr uint32_t A_COL0 = TB * M_PAD;
+    constexpr uint32_t A_COL0 = TB * acc_cols(M_PAD);
     const uint32_t r = lane_group * 32 + lane;  // weight row of the tile == TMEM lane
     const uint32_t tmem_lane = tmem_base + ((lane_group * 32u) << 16);
     bool ok = true;
@@ -142,11 +143,11 @@ __device__ __forceinline__ void q80_worker(const Q80Args& a, const Q80Smem& sm, 
         const uint32_t tb = seg % TB;
         if (!wwait(&sm.t_full[tb], (seg / TB) & 1u)) { ok = false; break; }
         tc_fence_after();
-        uint32_t x[COLS];
-        const uint32_t taddr = tmem_base + ((lane_group * 32u) << 16) + tb * M_PAD + C4 * COLS;
-        if (COLS == 4) tmem_ld_x4(taddr, x);
-        else if (COLS == 8) tmem_ld_x8(taddr, x);
-        else tmem_ld_x16(taddr, x);
+        uint32_t x[COLS], y[COLS];
+        const uint32_t taddr = tmem_base + ((lane_group * 32u) << 16) + tb * acc_cols(M_PAD) + C4 * COLS;
+        if (COLS == 4) { tmem_ld_x4(taddr, x); tmem_ld_x4(taddr + M_PAD, y); }
+        else if (COLS == 8) { tmem_ld_x8(taddr, x); tmem_ld_x8(taddr + M_PAD, y); }
+        else { tmem_ld_x16(taddr, x); tmem_ld_x16(taddr + M_PAD, y); }
         tmem_ld_wait();
         tc_fence_before();
         __syncwarp();
@@ -155,7 +156,7 @@ __device__ __forceinline__ void q80_worker(const Q80Args& a, const Q80Smem& sm, 
 #pragma unroll
         for (int j = 0; j < COLS; ++j) {
             const uint32_t m = C4 * COLS + j;
-            if (m < a.M) dstp[(size_t)m * BLOCK_N] = __uint_as_float(x[j]);
+            if (m < a.M) dstp[(size_t)m * BLOCK_N] = __uint_as_float(x[j]) + __uint_as_float(y[j]);
         }
         pos += kb_end - kb_begin;
         ++seg;
@@ -173,7 +174,7 @@ __global__ void __launch_bounds__(CTA_THREADS, 1) gemm_tc_q80_kernel(const __gri
     constexpr uint32_t B_BYTES = M_PAD * BLOCK_K * 2;  // one of hi / lo for a 64-k sub-block
     constexpr uint32_t BS = b_slots(M_PAD);
     constexpr uint32_t AST = a_stages(M_PAD);
-    constexpr uint32_t A_COL0 = TB * M_PAD;
+    constexpr uint32_t A_COL0 = TB * acc_cols(M_PAD);
     extern __shared__ unsigned char smem_unaligned[];
     unsigned char* smem = smem_unaligned + ((1024u - (smem_u32(smem_unaligned) & 1023u)) & 1023u);
     unsigned char* s_raw = smem;                             // RS x RAW_BYTES
@@ -250,7 +251,9 @@ __global__ void __launch_bounds__(CTA_THREADS, 1) gemm_tc_q80_kernel(const __gri
     } else if (warp == 1) {
         // ---------------- MMA issuer: one accumulator per tile segment, TMEM buffer = segment % TB
         if (lane == 0) {
-            const uint32_t idesc = make_idesc(M_PAD);
+            // one MMA takes hi against [Xh | Xl] (the two activation tiles are contiguous rows of one operand), a
+            // second adds lo.Xh into the first half: the weight operand passes the tensor core twice, not three times
+            const uint32_t idesc2 = make_idesc(2 * M_PAD), idesc1 = make_idesc(M_PAD);
             bool ok = true;
             uint32_t pos = u0, seg = 0, u = 0;
             while (pos < u1 && ok) {
@@ -260,22 +263,22 @@ __global__ void __launch_bounds__(CTA_THREADS, 1) gemm_tc_q80_kernel(const __gri
                 const uint32_t tb = seg % TB;
                 if (seg >= TB && !mbar_wait(&t_empty[tb], ((seg / TB) - 1) & 1u)) { ok = false; break; }
                 tc_fence_after();
-                const uint32_t d_tmem = tmem_base + tb * M_PAD;
+                const uint32_t d_tmem = tmem_base + tb * acc_cols(M_PAD);
                 const uint32_t n_sub = (kb_end - kb_begin) * 4;
                 for (uint32_t j = 0; j < n_sub && ok; ++j, ++u) {
                     const uint32_t as = u % AST, bs = u % BS;
-                    if (!mbar_wait(&a_full[as], (u / AST) & 1u) || !mbar_wait(&b_full[bs], (u / BS) & 1u)) { ok = false; break; }
+                    if (!mbar_wait(&a_full[as], (u / AST) & 1u)) { ok = false; break; }
+                    if (!mbar_wait(&b_full[bs], (u / BS) & 1u)) { ok = false; break; }
                     tc_fence_after();
                     const uint32_t ta = tmem_base + A_COL0 + as * A_COLS;  // hi columns [0,32), lo columns [32,64)
                     const uint32_t sb = smem_u32(s_b + bs * 2 * B_BYTES);
 #pragma unroll
                     for (uint32_t kk = 0; kk < BLOCK_K / UMMA_K; ++kk) {
                         const uint32_t off = kk * UMMA_K * 2;
-                        const uint64_t b_hi = make_desc_sw128(sb + off), b_lo = make_desc_sw128(sb + B_BYTES + off);
+                        const uint64_t b_x = make_desc_sw128(sb + off);  // rows [0, M_PAD) = Xh, [M_PAD, 2 M_PAD) = Xl
                         const uint32_t a_hi = ta + kk * (UMMA_K / 2), a_lo = a_hi + 32;
-                        umma_f16_ts(d_tmem, a_hi, b_hi, idesc, (j | kk) != 0u);
-                        umma_f16_ts(d_tmem, a_hi, b_lo, idesc, 1u);
-                        umma_f16_ts(d_tmem, a_lo, b_hi, idesc, 1u);
+                        umma_f16_ts(d_tmem, a_hi, b_x, idesc2, (j | kk) != 0u);
+                        umma_f16_ts(d_tmem, a_lo, b_x, idesc1, 1u);
                     }
                     umma_commit(&a_empty[as]);
                     umma_commit(&b_empty[bs]);
