@@ -62,8 +62,13 @@ __global__ void __launch_bounds__(192, 1) gemm_tc_f16_kernel(const __grid_consta
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * a.stages + 1);
     volatile uint32_t* abort_flag = tmem_slot + 1;
 
+    // hi and lo activation tiles are contiguous rows of one operand: up to M_pad = 128 a single MMA of width
+    // 2 * M_pad takes the weight tile against both (the weight operand passes the tensor core once); the two
+    // halves of the accumulator are added in the epilogue.
+    const bool stacked = a.use_lo && a.M_pad <= 128u;
+    const uint32_t acc_cols = stacked ? 2u * a.M_pad : a.M_pad;
     uint32_t tmem_cols = 32;
-    while (tmem_cols < a.M_pad) tmem_cols <<= 1;
+    while (tmem_cols < acc_cols) tmem_cols <<= 1;
 
     uint32_t problem = 0;
     while (problem + 1 < a.problems && tile >= a.tile_begin[problem + 1]) ++problem;
@@ -107,7 +112,7 @@ __global__ void __launch_bounds__(192, 1) gemm_tc_f16_kernel(const __grid_consta
     } else if (warp == 1) {
         // ---------------- MMA issuer
         if (lane == 0) {
-            const uint32_t idesc = make_idesc(a.M_pad);
+            const uint32_t idesc = make_idesc(acc_cols);
             bool ok = true;
             for (uint32_t i = 0; i < n_kb && ok; ++i) {
                 const uint32_t s = i % a.stages, round = i / a.stages;
@@ -119,7 +124,7 @@ __global__ void __launch_bounds__(192, 1) gemm_tc_f16_kernel(const __grid_consta
                 for (uint32_t k = 0; k < BLOCK_K / UMMA_K; ++k) {
                     const uint64_t da = make_desc_sw128(sa + k * UMMA_K * 2);
                     umma_f16(tmem_base, da, make_desc_sw128(sb + k * UMMA_K * 2), idesc, (i | k) != 0u);
-                    if (a.use_lo) umma_f16(tmem_base, da, make_desc_sw128(sb + b_bytes + k * UMMA_K * 2), idesc, 1u);
+                    if (a.use_lo && !stacked) umma_f16(tmem_base, da, make_desc_sw128(sb + b_bytes + k * UMMA_K * 2), idesc, 1u);
                 }
                 umma_commit(&empty[s]);  // frees the stage once these MMAs have read it
             }
@@ -138,8 +143,15 @@ __global__ void __launch_bounds__(192, 1) gemm_tc_f16_kernel(const __grid_consta
         float* dst = a.partial + (size_t)ksplit * a.M * a.n_total + n_glob;
         for (uint32_t c = 0; c < a.M_pad; c += 8) {
             float v[8];
-            if (ok) tmem_ld8(tmem_base + ((lane_group * 32u) << 16) + c, v);
-            else {
+            if (ok) {
+                tmem_ld8(tmem_base + ((lane_group * 32u) << 16) + c, v);
+                if (stacked) {
+                    float w[8];
+                    tmem_ld8(tmem_base + ((lane_group * 32u) << 16) + a.M_pad + c, w);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) v[j] += w[j];
+                }
+            } else {
 #pragma unroll
                 for (int j = 0; j < 8; ++j) v[j] = 0.0f;
             }
