@@ -95,16 +95,17 @@ extern "C" int m40llm_qkv_rmsnorm_rope_append_async(M40llmCudaContext* ctx, M40l
     const void* wp[3] = {d_wq_f16, d_wk_f16, d_wv_f16};
     if (rc == 0) {
         // projections done above
-    } else if ((rc = m40_rms_norm_rows(ctx, d_x_f32, d_norm_w, xn, rows, hidden, eps, norm_w_dtype)) != 0) {
-        return rc;
-    } else if ((int)rows >= m40_tc_min_rows() && m40_gemm_tc_supported((int)rows, (int)hidden, 3, wp)) {
-        // one tensor-core launch over Wq | Wk | Wv (they share the normalised activations)
+    } else if ((int)rows >= m40_tc_min_rows() && m40_gemm_tc_supported((int)rows, (int)hidden, 3, wp) && hidden % 4 == 0) {
+        // one tensor-core launch over Wq | Wk | Wv; the norm rides on the f16 split of the activations
         const __half* w[3] = {(const __half*)d_wq_f16, (const __half*)d_wk_f16, (const __half*)d_wv_f16};
         const int n[3] = {(int)QD, (int)KD, (int)KD};
         float* o[3] = {(float*)d_q_out_f32, kbuf, vbuf};
         const float* b[3] = {(const float*)d_bq_f32, (const float*)d_bk_f32, (const float*)d_bv_f32};
-        rc = m40_gemm_tc_f16(ctx, s, 1u, xn, (int)rows, (int)hidden, 3, w, n, o, b, nullptr, 0);
+        const M40GemvNorm norm = {d_norm_w, norm_w_dtype == 1u ? 1 : 0, eps, nullptr};
+        rc = m40_gemm_tc_f16(ctx, s, 1u, (const float*)d_x_f32, (int)rows, (int)hidden, 3, w, n, o, b, nullptr, 0, &norm);
         if (rc != 0) return rc;
+    } else if ((rc = m40_rms_norm_rows(ctx, d_x_f32, d_norm_w, xn, rows, hidden, eps, norm_w_dtype)) != 0) {
+        return rc;
     } else {
         rc = m40_gemm_f32xf16_gguf(ctx, s, xn, (const __half*)d_wq_f16, (float*)d_q_out_f32, (int)rows, (int)QD,
                                    (int)hidden, (const float*)d_bq_f32, nullptr);
@@ -163,12 +164,15 @@ extern "C" int m40llm_attn_out_ffn_async(M40llmCudaContext* ctx, const void* d_a
                                                    (const float*)d_x1_f32);
         }
     }
+    const M40GemvNorm norm = {d_ffn_norm_w, norm_w_dtype == 1u ? 1 : 0, eps, nullptr};
+    rc = m40_ffn_swiglu(ctx, 1u, d_x1_f32, d_wg, d_wu, d_wd, d_x1_f32, d_hid_f32, d_out_f32, rows, hidden, ffn,
+                        ffn_q80 ? 1 : 0, &norm);
+    if (rc != 1) return rc;
+    // the shape went to a path that cannot fold the norm: normalise explicitly
     float* xn = (float*)m40_ensure_scratch(ctx, 1, (size_t)rows * hidden * sizeof(float), 1);
     if (!xn) return -5;
     rc = m40_rms_norm_rows(ctx, d_x1_f32, d_ffn_norm_w, xn, rows, hidden, eps, norm_w_dtype);
     if (rc != 0) return rc;
-    return ffn_q80 ? m40llm_ffn_swiglu_q80_f32_async(ctx, xn, d_wg, d_wu, d_wd, d_x1_f32, d_hid_f32, d_out_f32, rows,
-                                                     hidden, ffn, 1u)
-                   : m40llm_ffn_swiglu_f16_f32_async(ctx, xn, d_wg, d_wu, d_wd, d_x1_f32, d_hid_f32, d_out_f32, rows,
-                                                     hidden, ffn, 1u);
+    return m40_ffn_swiglu(ctx, 1u, xn, d_wg, d_wu, d_wd, d_x1_f32, d_hid_f32, d_out_f32, rows, hidden, ffn,
+                          ffn_q80 ? 1 : 0, nullptr);
 }

@@ -415,9 +415,10 @@ int m40_gemm_f32xq80_gguf(M40llmCudaContext* ctx, cudaStream_t s, const float* A
 // Q8_0 projections for batched rows on the tensor cores, 64 rows per pass. Returns 1 when not applicable.
 static int q80_tc_rows(M40llmCudaContext* ctx, cudaStream_t s, uint32_t stream_kind, const float* A, int M, int K,
                        int problems, const uint8_t* const* W, const int* N, float* const* out, const float* residual,
-                       int mode) {
+                       int mode, const M40GemvNorm* norm = nullptr) {
     const void* wp[3] = {W[0], problems > 1 ? W[1] : W[0], problems > 2 ? W[2] : W[0]};
     if (M < m40_tc_min_rows() || !m40_gemm_tc_q80_supported(M < 64 ? M : 64, K, problems, wp)) return 1;
+    if (norm && norm->w && M % 64 == 1) return 1;  // a single trailing row would need the un-normalised path
     for (int m0 = 0; m0 < M; m0 += 64) {
         const int rows = M - m0 < 64 ? M - m0 : 64;
         if (rows < 2) {  // a single trailing row: CUDA-core kernel
@@ -439,7 +440,7 @@ static int q80_tc_rows(M40llmCudaContext* ctx, cudaStream_t s, uint32_t stream_k
             o[p] = out[p] ? out[p] + (size_t)m0 * N[p] : nullptr;
             r[p] = residual ? residual + (size_t)m0 * N[p] : nullptr;
         }
-        const int rc = m40_gemm_tc_q80(ctx, s, stream_kind, A + (size_t)m0 * K, rows, K, problems, W, N, o, r, mode);
+        const int rc = m40_gemm_tc_q80(ctx, s, stream_kind, A + (size_t)m0 * K, rows, K, problems, W, N, o, r, mode, norm);
         if (rc != 0) return rc;
     }
     return 0;
@@ -544,6 +545,56 @@ int gemm_rowmajor_b(M40llmCudaContext* ctx, const AT* A, const __half* B, float*
 }
 
 }  // namespace
+
+// The SwiGLU FFN (gate|up with the SiLU*up epilogue, then down + residual) over Q8_0 or f16 GGUF weights.
+// `norm` (optional) is applied to x on the fly by the batched tensor-core path; returns 1 when a norm was asked for
+// but the shape went to a path that cannot fold it (the caller then normalises explicitly and calls again).
+int m40_ffn_swiglu(M40llmCudaContext* ctx, uint32_t stream_kind, const void* d_x, const void* d_wg, const void* d_wu,
+                   const void* d_wd, const void* d_residual, void* d_hid, void* d_out, uint32_t rows, uint32_t hidden,
+                   uint32_t ffn, int q80, const M40GemvNorm* norm) {
+    cudaStream_t s = m40_stream(ctx, stream_kind);
+    const bool want_norm = norm && norm->w;
+    int rc;
+    if (q80) {
+        {
+            const uint8_t* w[2] = {(const uint8_t*)d_wg, (const uint8_t*)d_wu};
+            const int n[2] = {(int)ffn, (int)ffn};
+            float* o[2] = {(float*)d_hid, nullptr};
+            rc = q80_tc_rows(ctx, s, stream_kind, (const float*)d_x, (int)rows, (int)hidden, 2, w, n, o, nullptr, 1, norm);
+        }
+        if (rc == 1) {
+            if (want_norm) return 1;
+            rc = m40_gate_up_swiglu_q80(ctx, s, (const float*)d_x, (const uint8_t*)d_wg, (const uint8_t*)d_wu,
+                                        (float*)d_hid, (int)rows, (int)ffn, (int)hidden);
+        }
+        if (rc != 0) return rc;
+        {
+            const uint8_t* w[1] = {(const uint8_t*)d_wd};
+            const int n[1] = {(int)hidden};
+            float* o[1] = {(float*)d_out};
+            rc = q80_tc_rows(ctx, s, stream_kind, (const float*)d_hid, (int)rows, (int)ffn, 1, w, n, o,
+                             (const float*)d_residual, 0);
+        }
+        if (rc != 1) return rc;
+        return m40_gemm_f32xq80_gguf(ctx, s, (const float*)d_hid, (const uint8_t*)d_wd, (float*)d_out, (int)rows,
+                                     (int)hidden, (int)ffn, (const float*)d_residual);
+    }
+    const void* wp[2] = {d_wg, d_wu};
+    if ((int)rows >= m40_tc_min_rows() && m40_gemm_tc_supported((int)rows, (int)hidden, 2, wp)) {
+        const __half* w[2] = {(const __half*)d_wg, (const __half*)d_wu};
+        const int n[2] = {(int)ffn, (int)ffn};
+        float* o[2] = {(float*)d_hid, nullptr};
+        rc = m40_gemm_tc_f16(ctx, s, stream_kind, (const float*)d_x, (int)rows, (int)hidden, 2, w, n, o, nullptr, nullptr,
+                             1, norm);
+    } else {
+        if (want_norm) return 1;
+        rc = m40_gate_up_swiglu_f16(ctx, s, (const float*)d_x, (const __half*)d_wg, (const __half*)d_wu, (float*)d_hid,
+                                    (int)rows, (int)ffn, (int)hidden);
+    }
+    if (rc != 0) return rc;
+    return m40_gemm_dispatch_f16(ctx, s, stream_kind, (const float*)d_hid, (const __half*)d_wd, (float*)d_out, (int)rows,
+                                 (int)hidden, (int)ffn, nullptr, (const float*)d_residual);
+}
 
 extern "C" {
 
@@ -657,29 +708,9 @@ int m40llm_ffn_swiglu_q80_f32_async(M40llmCudaContext* ctx, const void* d_x_f32,
     if (!ctx || !d_x_f32 || !d_wg_q80 || !d_wu_q80 || !d_wd_q80 || !d_hid_f32 || !d_out_f32) return -1;
     if (rows == 0 || hidden == 0 || ffn == 0 || hidden % 128 != 0 || ffn % 128 != 0) return -2;
     if (m40_ensure_device(ctx) != 0) return -1;
-    cudaStream_t s = m40_stream(ctx, stream_kind);
-    if (!s) return -4;
-    int rc;
-    {
-        const uint8_t* w[2] = {(const uint8_t*)d_wg_q80, (const uint8_t*)d_wu_q80};
-        const int n[2] = {(int)ffn, (int)ffn};
-        float* o[2] = {(float*)d_hid_f32, nullptr};
-        rc = q80_tc_rows(ctx, s, stream_kind, (const float*)d_x_f32, (int)rows, (int)hidden, 2, w, n, o, nullptr, 1);
-    }
-    if (rc == 1)
-        rc = m40_gate_up_swiglu_q80(ctx, s, (const float*)d_x_f32, (const uint8_t*)d_wg_q80, (const uint8_t*)d_wu_q80,
-                                    (float*)d_hid_f32, (int)rows, (int)ffn, (int)hidden);
-    if (rc != 0) return rc;
-    {
-        const uint8_t* w[1] = {(const uint8_t*)d_wd_q80};
-        const int n[1] = {(int)hidden};
-        float* o[1] = {(float*)d_out_f32};
-        rc = q80_tc_rows(ctx, s, stream_kind, (const float*)d_hid_f32, (int)rows, (int)ffn, 1, w, n, o,
-                         (const float*)d_residual_f32, 0);
-    }
-    if (rc != 1) return rc;
-    return m40_gemm_f32xq80_gguf(ctx, s, (const float*)d_hid_f32, (const uint8_t*)d_wd_q80, (float*)d_out_f32,
-                                 (int)rows, (int)hidden, (int)ffn, (const float*)d_residual_f32);
+    if (!m40_stream(ctx, stream_kind)) return -4;
+    return m40_ffn_swiglu(ctx, stream_kind, d_x_f32, d_wg_q80, d_wu_q80, d_wd_q80, d_residual_f32, d_hid_f32, d_out_f32,
+                          rows, hidden, ffn, 1, nullptr);
 }
 
 int m40llm_ffn_swiglu_f16_f32_async(M40llmCudaContext* ctx, const void* d_x_f32, const void* d_wg_f16,
@@ -689,24 +720,9 @@ int m40llm_ffn_swiglu_f16_f32_async(M40llmCudaContext* ctx, const void* d_x_f32,
     if (!ctx || !d_x_f32 || !d_wg_f16 || !d_wu_f16 || !d_wd_f16 || !d_hid_f32 || !d_out_f32) return -1;
     if (rows == 0 || hidden == 0 || ffn == 0 || hidden % 8 != 0 || ffn % 8 != 0) return -2;
     if (m40_ensure_device(ctx) != 0) return -1;
-    cudaStream_t s = m40_stream(ctx, stream_kind);
-    if (!s) return -4;
-    int rc;
-    const void* wp[2] = {d_wg_f16, d_wu_f16};
-    if ((int)rows >= m40_tc_min_rows() && m40_gemm_tc_supported((int)rows, (int)hidden, 2, wp)) {
-        const __half* w[2] = {(const __half*)d_wg_f16, (const __half*)d_wu_f16};
-        const int n[2] = {(int)ffn, (int)ffn};
-        float* o[2] = {(float*)d_hid_f32, nullptr};
-        rc = m40_gemm_tc_f16(ctx, s, stream_kind, (const float*)d_x_f32, (int)rows, (int)hidden, 2, w, n, o, nullptr,
-                             nullptr, 1);
-    } else {
-        rc = m40_gate_up_swiglu_f16(ctx, s, (const float*)d_x_f32, (const __half*)d_wg_f16, (const __half*)d_wu_f16,
-                                    (float*)d_hid_f32, (int)rows, (int)ffn, (int)hidden);
-    }
-    if (rc != 0) return rc;
-    return m40_gemm_dispatch_f16(ctx, s, stream_kind, (const float*)d_hid_f32, (const __half*)d_wd_f16,
-                                 (float*)d_out_f32, (int)rows, (int)hidden, (int)ffn, nullptr,
-                                 (const float*)d_residual_f32);
+    if (!m40_stream(ctx, stream_kind)) return -4;
+    return m40_ffn_swiglu(ctx, stream_kind, d_x_f32, d_wg_f16, d_wu_f16, d_wd_f16, d_residual_f32, d_hid_f32, d_out_f32,
+                          rows, hidden, ffn, 0, nullptr);
 }
 
 }  // extern "C"

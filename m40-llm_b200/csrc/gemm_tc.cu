@@ -181,7 +181,44 @@ __global__ void split_activations_kernel(const float* __restrict__ x, __half* __
     }
 }
 
-// Adds the K splits and applies the epilogue. One thread per (m, n) of one problem.
+// One CTA per activation row: optional RMSNorm (x * rsqrt(mean(x^2) + eps) * w), then the f16 hi/lo split.
+__global__ void __launch_bounds__(256) norm_split_rows_kernel(const float* __restrict__ x, const void* __restrict__ w,
+                                                              int w_f32, float eps, __half* __restrict__ hi,
+                                                              __half* __restrict__ lo, uint32_t K) {
+    __shared__ float red[8];
+    const float* xr = x + (size_t)blockIdx.x * K;
+    __half* hr = hi + (size_t)blockIdx.x * K;
+    __half* lr = lo + (size_t)blockIdx.x * K;
+    float ss = 0.0f;
+    for (uint32_t k = threadIdx.x * 4u; k < K; k += 1024u) {
+        const float4 v = *reinterpret_cast<const float4*>(xr + k);
+        ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+    }
+    ss = warp_sum(ss);
+    if ((threadIdx.x & 31u) == 0u) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    float tot = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) tot += red[i];
+    const float scale = rsqrtf(tot / (float)K + eps);
+    for (uint32_t k = threadIdx.x * 4u; k < K; k += 1024u) {
+        const float4 v = *reinterpret_cast<const float4*>(xr + k);
+        float t[4] = {v.x, v.y, v.z, v.w};
+        __half h[4], l[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float wv = w_f32 ? reinterpret_cast<const float*>(w)[k + i]
+                                   : __half2float(reinterpret_cast<const __half*>(w)[k + i]);
+            const float y = t[i] * scale * wv;
+            h[i] = __float2half_rn(y);
+            l[i] = __float2half_rn(y - __half2float(h[i]));
+        }
+        *reinterpret_cast<uint2*>(hr + k) = *reinterpret_cast<const uint2*>(h);
+        *reinterpret_cast<uint2*>(lr + k) = *reinterpret_cast<const uint2*>(l);
+    }
+}
+
+// Adds the K splits and applies the epilogue. Thread (n, lane of 2) walks 8 activation rows of one problem.
 // mode 0: C = sum (+ bias[n]) (+ residual[m][n]);  mode 1: problems 0/1 are gate/up, C = silu(gate) * up.
 struct EpiArgs {
     const float* partial;
@@ -193,25 +230,27 @@ struct EpiArgs {
     uint32_t problems, M, n_total, k_splits, mode;
 };
 
-__global__ void gemm_tc_epilogue_kernel(EpiArgs e) {
+__global__ void __launch_bounds__(256) gemm_tc_epilogue_kernel(EpiArgs e) {
     const uint32_t p = blockIdx.z;
-    const uint32_t n = blockIdx.x * blockDim.x + threadIdx.x;
-    const uint32_t m = blockIdx.y;
+    const uint32_t n = blockIdx.x * 128u + (threadIdx.x & 127u);
     if (n >= e.N[p]) return;
     const size_t split_stride = (size_t)e.M * e.n_total;
-    const size_t idx = (size_t)m * e.n_total + (size_t)e.tile_begin[p] * BLOCK_N + n;
-    float acc = 0.0f;
-    for (uint32_t s = 0; s < e.k_splits; ++s) acc += e.partial[s * split_stride + idx];
-    if (e.mode == 1) {
-        const size_t idx_u = (size_t)m * e.n_total + (size_t)e.tile_begin[1] * BLOCK_N + n;
-        float up = 0.0f;
-        for (uint32_t s = 0; s < e.k_splits; ++s) up += e.partial[s * split_stride + idx_u];
-        e.out[0][(size_t)m * e.N[0] + n] = (acc / (1.0f + expf(-acc))) * up;
-        return;
+    const uint32_t m_end = min(e.M, (blockIdx.y + 1u) * 8u);
+    for (uint32_t m = blockIdx.y * 8u + (threadIdx.x >> 7); m < m_end; m += 2u) {
+        const size_t idx = (size_t)m * e.n_total + (size_t)e.tile_begin[p] * BLOCK_N + n;
+        float acc = 0.0f;
+        for (uint32_t s = 0; s < e.k_splits; ++s) acc += e.partial[s * split_stride + idx];
+        if (e.mode == 1) {
+            const size_t idx_u = (size_t)m * e.n_total + (size_t)e.tile_begin[1] * BLOCK_N + n;
+            float up = 0.0f;
+            for (uint32_t s = 0; s < e.k_splits; ++s) up += e.partial[s * split_stride + idx_u];
+            e.out[0][(size_t)m * e.N[0] + n] = (acc / (1.0f + expf(-acc))) * up;
+            continue;
+        }
+        if (e.bias[p]) acc += e.bias[p][n];
+        if (e.residual[p]) acc += e.residual[p][(size_t)m * e.N[p] + n];
+        e.out[p][(size_t)m * e.N[p] + n] = acc;
     }
-    if (e.bias[p]) acc += e.bias[p][n];
-    if (e.residual[p]) acc += e.residual[p][(size_t)m * e.N[p] + n];
-    e.out[p][(size_t)m * e.N[p] + n] = acc;
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -247,6 +286,21 @@ bool make_map_f16(CUtensorMap* map, const void* base, uint64_t rows, uint64_t co
 
 }  // namespace
 
+int m40_split_activations(M40llmCudaContext* ctx, cudaStream_t s, const float* X, __half* hi, __half* lo, int M, int K,
+                          const M40GemvNorm* norm) {
+    if (norm && norm->w) {
+        if (K % 4 != 0 || (((uintptr_t)X) & 15u) != 0u) return -2;
+        norm_split_rows_kernel<<<(unsigned)M, 256, 0, s>>>(X, norm->w, norm->w_is_f32, norm->eps, hi, lo, (uint32_t)K);
+    } else {
+        const size_t n = (size_t)M * K;
+        size_t blocks = (n + 255) / 256;
+        if (blocks > (size_t)ctx->sm_count * 8) blocks = (size_t)ctx->sm_count * 8;
+        split_activations_kernel<<<(unsigned)blocks, 256, 0, s>>>(X, hi, lo, n);
+    }
+    M40_COUNT_LAUNCH(ctx);
+    return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
 bool m40_gemm_tc_supported(int M, int K, int problems, const void* const* W) {
     if (M < 2 || M > 256 || K % 8 != 0 || K < BLOCK_K || problems < 1 || problems > 3) return false;
     for (int p = 0; p < problems; ++p)
@@ -256,7 +310,7 @@ bool m40_gemm_tc_supported(int M, int K, int problems, const void* const* W) {
 
 int m40_gemm_tc_f16(M40llmCudaContext* ctx, cudaStream_t s, uint32_t stream_kind, const float* X, int M, int K,
                     int problems, const __half* const* W, const int* N, float* const* out, const float* const* bias,
-                    const float* const* residual, int mode) {
+                    const float* const* residual, int mode, const M40GemvNorm* norm) {
     const uint32_t M_pad = (uint32_t)((M + 15) / 16 * 16);
     TcArgs a = {};
     a.M = (uint32_t)M;
@@ -310,12 +364,7 @@ int m40_gemm_tc_f16(M40llmCudaContext* ctx, cudaStream_t s, uint32_t stream_kind
     if (!make_map_f16(&mXh, xh, (uint64_t)M, (uint64_t)K, M_pad)) return -2;
     if (!make_map_f16(&mXl, a.use_lo ? xl : xh, (uint64_t)M, (uint64_t)K, M_pad)) return -2;
 
-    {
-        size_t blocks = (act_elems + 255) / 256;
-        if (blocks > (size_t)ctx->sm_count * 8) blocks = (size_t)ctx->sm_count * 8;
-        split_activations_kernel<<<(unsigned)blocks, 256, 0, s>>>(X, xh, xl, act_elems);
-        M40_COUNT_LAUNCH(ctx);
-    }
+    if (m40_split_activations(ctx, s, X, xh, xl, M, K, norm) != 0) return -2;
     static unsigned long long configured = 0ull;
     const unsigned long long bit = 1ull << (ctx->device_id & 63);
     if (!(configured & bit)) {
@@ -344,7 +393,7 @@ int m40_gemm_tc_f16(M40llmCudaContext* ctx, cudaStream_t s, uint32_t stream_kind
     e.n_total = a.n_total;
     e.k_splits = ks;
     e.mode = (uint32_t)mode;
-    dim3 egrid((maxN + 255) / 256, (unsigned)M, mode == 1 ? 1u : (unsigned)problems);
+    dim3 egrid((maxN + 127) / 128, (unsigned)(M + 7) / 8, mode == 1 ? 1u : (unsigned)problems);
     gemm_tc_epilogue_kernel<<<egrid, 256, 0, s>>>(e);
     M40_COUNT_LAUNCH(ctx);
     return cudaGetLastError() == cudaSuccess ? 0 : -2;

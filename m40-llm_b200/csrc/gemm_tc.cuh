@@ -1,6 +1,7 @@
 // Tensor-core (tcgen05) weight-streaming GEMM for batched decode rows; see gemm_tc.cu.
 #pragma once
 #include "common.cuh"
+#include "gemv_stream.cuh"  // M40GemvNorm
 
 // True when the tcgen05 path can take this problem set (2 <= M <= 256, K % 8 == 0, 16-byte aligned weights).
 bool m40_gemm_tc_supported(int M, int K, int problems, const void* const* W);
@@ -10,11 +11,15 @@ bool m40_gemm_tc_supported(int M, int K, int problems, const void* const* W);
 // mode 1: two problems (gate, up) of equal N: out[0][m][n] = silu(X.Wg^T) * (X.Wu^T).
 int m40_gemm_tc_f16(M40llmCudaContext* ctx, cudaStream_t s, uint32_t stream_kind, const float* X, int M, int K,
                     int problems, const __half* const* W, const int* N, float* const* out, const float* const* bias,
-                    const float* const* residual, int mode);
+                    const float* const* residual, int mode, const M40GemvNorm* norm = nullptr);
+// `norm` (optional): RMSNorm applied to X while it is split into f16 hi/lo (saves the separate norm pass).
 
 // Same over Q8_0 GGUF rows (K % 256 == 0, 2 <= M <= 64 per call). mode 0: out[p] = X.W[p]^T (+ residual[p]);
 // mode 1: out[0] = silu(X.Wg^T) * (X.Wu^T).
 bool m40_gemm_tc_q80_supported(int M, int K, int problems, const void* const* W);
 int m40_gemm_tc_q80(M40llmCudaContext* ctx, cudaStream_t s, uint32_t stream_kind, const float* X, int M, int K,
                     int problems, const uint8_t* const* W, const int* N, float* const* out,
-                    const float* const* residual, int mode);
+                    const float* const* residual, int mode, const M40GemvNorm* norm = nullptr);
+// The f32 -> f16 hi/lo split (with optional RMSNorm per row) shared by both tensor-core paths.
+int m40_split_activations(M40llmCudaContext* ctx, cudaStream_t s, const float* X, __half* hi, __half* lo, int M, int K,
+                          const M40GemvNorm* norm);

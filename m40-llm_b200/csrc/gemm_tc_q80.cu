@@ -336,32 +336,36 @@ __device__ __forceinline__ void q80_tile_ctas(const Q80EpiArgs& e, uint32_t tile
     *count = n;
 }
 
-// grid (tiles of the widest problem, M, problems or 1), block 128 = one tile row per thread.
-__global__ void __launch_bounds__(128) gemm_tc_q80_epilogue_kernel(Q80EpiArgs e) {
+// grid (tiles of the widest problem, ceil(M / 8), problems or 1), block 256: thread = (tile row, lane of 2) walking
+// 8 activation rows.
+__global__ void __launch_bounds__(256) gemm_tc_q80_epilogue_kernel(Q80EpiArgs e) {
     __shared__ uint32_t first[2], count[2], seg0[2];
-    const uint32_t p = blockIdx.z, m = blockIdx.y, t = blockIdx.x;
-    const uint32_t n = t * BLOCK_N + threadIdx.x;
+    const uint32_t p = blockIdx.z, t = blockIdx.x, tr = threadIdx.x & 127u;
+    const uint32_t n = t * BLOCK_N + tr;
     if (t * BLOCK_N >= e.N[p]) return;
     if (threadIdx.x == 0) q80_tile_ctas(e, e.tile_begin[p] + t, &first[0], &count[0], &seg0[0]);
     if (threadIdx.x == 32 && e.mode == 1) q80_tile_ctas(e, e.tile_begin[1] + t, &first[1], &count[1], &seg0[1]);
     __syncthreads();
     if (n >= e.N[p]) return;
-    auto tile_sum = [&](int w) {
-        float acc = 0.0f;
-        for (uint32_t i = 0; i < count[w]; ++i) {
-            const size_t slot = (size_t)(first[w] + i) * e.seg_max + (i == 0 ? seg0[w] : 0u);
-            acc += e.partial[(slot * e.M + m) * BLOCK_N + threadIdx.x];
+    const uint32_t m_end = min(e.M, (blockIdx.y + 1u) * 8u);
+    for (uint32_t m = blockIdx.y * 8u + (threadIdx.x >> 7); m < m_end; m += 2u) {
+        auto tile_sum = [&](int w) {
+            float acc = 0.0f;
+            for (uint32_t i = 0; i < count[w]; ++i) {
+                const size_t slot = (size_t)(first[w] + i) * e.seg_max + (i == 0 ? seg0[w] : 0u);
+                acc += e.partial[(slot * e.M + m) * BLOCK_N + tr];
+            }
+            return acc;
+        };
+        float acc = tile_sum(0);
+        if (e.mode == 1) {
+            const float up = tile_sum(1);
+            e.out[0][(size_t)m * e.N[0] + n] = (acc / (1.0f + expf(-acc))) * up;
+            continue;
         }
-        return acc;
-    };
-    float acc = tile_sum(0);
-    if (e.mode == 1) {
-        const float up = tile_sum(1);
-        e.out[0][(size_t)m * e.N[0] + n] = (acc / (1.0f + expf(-acc))) * up;
-        return;
+        if (e.residual[p]) acc += e.residual[p][(size_t)m * e.N[p] + n];
+        e.out[p][(size_t)m * e.N[p] + n] = acc;
     }
-    if (e.residual[p]) acc += e.residual[p][(size_t)m * e.N[p] + n];
-    e.out[p][(size_t)m * e.N[p] + n] = acc;
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -406,17 +410,6 @@ bool make_map_act(CUtensorMap* map, const void* base, uint64_t rows, uint64_t co
                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-__global__ void split_activations_q80_kernel(const float* __restrict__ x, __half* __restrict__ hi,
-                                             __half* __restrict__ lo, size_t n) {
-    const size_t stride = (size_t)gridDim.x * blockDim.x;
-    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
-        const float v = x[i];
-        const __half h = __float2half_rn(v);
-        hi[i] = h;
-        lo[i] = __float2half_rn(v - __half2float(h));
-    }
-}
-
 template <int M_PAD>
 int launch_q80(M40llmCudaContext* ctx, cudaStream_t s, const CUtensorMap* mW, const CUtensorMap& mXh,
                const CUtensorMap& mXl, const Q80Args& a) {
@@ -444,7 +437,7 @@ bool m40_gemm_tc_q80_supported(int M, int K, int problems, const void* const* W)
 
 int m40_gemm_tc_q80(M40llmCudaContext* ctx, cudaStream_t s, uint32_t stream_kind, const float* X, int M, int K,
                     int problems, const uint8_t* const* W, const int* N, float* const* out,
-                    const float* const* residual, int mode) {
+                    const float* const* residual, int mode, const M40GemvNorm* norm) {
     const uint32_t M_pad = M <= 16 ? 16u : (M <= 32 ? 32u : 64u);
     Q80Args a = {};
     a.M = (uint32_t)M;
@@ -481,12 +474,7 @@ int m40_gemm_tc_q80(M40llmCudaContext* ctx, cudaStream_t s, uint32_t stream_kind
     }
     if (!make_map_act(&mXh, xh, (uint64_t)M, (uint64_t)K, M_pad)) return -2;
     if (!make_map_act(&mXl, xl, (uint64_t)M, (uint64_t)K, M_pad)) return -2;
-    {
-        size_t blocks = (act_elems + 255) / 256;
-        if (blocks > (size_t)ctx->sm_count * 8) blocks = (size_t)ctx->sm_count * 8;
-        split_activations_q80_kernel<<<(unsigned)blocks, 256, 0, s>>>(X, xh, xl, act_elems);
-        M40_COUNT_LAUNCH(ctx);
-    }
+    if (m40_split_activations(ctx, s, X, xh, xl, M, K, norm) != 0) return -2;
     int rc;
     if (M_pad == 16) rc = launch_q80<16>(ctx, s, mW, mXh, mXl, a);
     else if (M_pad == 32) rc = launch_q80<32>(ctx, s, mW, mXh, mXl, a);
@@ -510,8 +498,8 @@ int m40_gemm_tc_q80(M40llmCudaContext* ctx, cudaStream_t s, uint32_t stream_kind
     e.seg_max = a.seg_max;
     e.mode = (uint32_t)mode;
     e.problems = (uint32_t)problems;
-    dim3 egrid((maxN + BLOCK_N - 1) / BLOCK_N, (unsigned)M, mode == 1 ? 1u : (unsigned)problems);
-    gemm_tc_q80_epilogue_kernel<<<egrid, 128, 0, s>>>(e);
+    dim3 egrid((maxN + BLOCK_N - 1) / BLOCK_N, (unsigned)(M + 7) / 8, mode == 1 ? 1u : (unsigned)problems);
+    gemm_tc_q80_epilogue_kernel<<<egrid, 256, 0, s>>>(e);
     M40_COUNT_LAUNCH(ctx);
     return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
