@@ -287,6 +287,8 @@ def run_reference_arm(args, rank, world):
         return
     from oracle import oracle as O
     lens, sets, x = make_inputs(O, 0)
+    # torchrun exports OMP_NUM_THREADS=1; the reference arm is meant to use every host thread it can get
+    O.set_num_threads(len(os.sched_getaffinity(0)))
     cores = O.num_threads()
     cpu = CpuLayer(O, sets, x, lens)
     times = []
@@ -477,9 +479,42 @@ def main():
                            "algorithmic_bytes": b1, "achieved_gbs": b1 / (ms1 * 1e-3) / 1e9,
                            "frac_of_hbm_peak": b1 / (ms1 * 1e-3) / 1e9 / peak, "peak_kind": peak_kind}
 
+    # ---------------- long-context compressed attention (BASELINE configs[3] shape), rank 0: Qwen2.5-3B heads,
+    # context 32768 in the FP16-K / q4-V cache, 512-token ring, 64-token blocks, top 64. Four caches rotate.
+    if rank == 0:
+        cq, ckv, chd, cL, cR, cbs, ctop = 16, 2, 128, 32768, 512, 64, 64
+        crng = np.random.default_rng(7)
+        caches = []
+        for _ in range(4):
+            c = nat.kv_compressed(cL, 1, ckv, chd, cR, cbs, ctop)
+            nat.kv_fill(c, 0, crng.standard_normal((cL, ckv, chd), dtype=np.float32).astype(np.float16),
+                        crng.standard_normal((cL, ckv, chd), dtype=np.float32).astype(np.float16), final_len=cL)
+            caches.append(c)
+        cdq = nat.buf(crng.standard_normal(cq * chd, dtype=np.float32))
+        cdo = nat.buf(cq * chd * 4)
+        f = L.m40llm_attention_last_token_f32_gqa_block_select_exact_fp16_k_q4_v_old_direct_async
+        for i in range(8):
+            assert f(ctx, caches[i % 4], 0, cdq.ptr, cq, cL, cR, cbs, ctop, cdo.ptr) == 0
+        nat.sync(1)
+        ev.start()
+        creps = 200
+        for i in range(creps):
+            assert f(ctx, caches[i % 4], 0, cdq.ptr, cq, cL, cR, cbs, ctop, cdo.ptr) == 0
+        cms = ev.stop_ms() / creps
+        old_len = cL - cR
+        # every old K once per kv head; selected q4 V + scales (<= top blocks per q head); the ring K and V
+        cbytes = old_len * ckv * chd * 2 + cq * ctop * cbs * (chd // 2 + 4) + 2 * cR * ckv * chd * 2
+        extra["compressed32k"] = {"ms_per_call": cms, "algorithmic_bytes": cbytes,
+                                  "achieved_gbs": cbytes / (cms * 1e-3) / 1e9,
+                                  "frac_of_hbm_peak": cbytes / (cms * 1e-3) / 1e9 / peak,
+                                  "config": "16/2/128 heads, context 32768, ring 512, block 64, top 64"}
+        for c in caches:
+            L.m40llm_kvcache_destroy(c)
+
     # ---------------- CPU baseline (rank 0, N = 1): the oracle on a bounded sample of this batch
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        O.set_num_threads(len(os.sched_getaffinity(0)))
         cl = CpuLayer(O, sets, x, lens)
         cl.step(0)
         spent, n = 0.0, 0
