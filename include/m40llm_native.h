@@ -424,6 +424,24 @@ int m40llm_kvcache_debug_read_old_token(M40llmCudaContext* ctx, M40llmKVCache* k
 /* Device error word of the context: bit 0 = a batched-attention row carried an out-of-range
  * sequence id or length and was skipped. Reading clears it. */
 int m40llm_context_take_device_status(M40llmCudaContext* ctx, uint32_t* out_status);
+/* Token embedding gather on the device: out[r][:] = f32(table[token_ids[r]][:]), table f16 [vocab][hidden]
+ * (the reference gathers rows on the host and uploads them, src/infer/embeddings.rs:80-140). An id >= vocab yields a
+ * zero row and raises bit 8 of the device status word. Decode stream. */
+int m40llm_embed_tokens_f16_async(M40llmCudaContext* ctx, const void* d_table_f16, const uint32_t* d_token_ids,
+                                  void* d_out_f32, uint32_t rows, uint32_t hidden, uint32_t vocab);
+/* Logits head (src/infer/logits.rs:57-116): logits[r][v] = rmsnorm(hidden[r], norm_w) . lm_head[v], lm_head f16 GGUF
+ * rows [vocab][hidden]; d_norm_w may be NULL (no output norm), norm_w_dtype 0 f16 / 1 f32. Decode stream; the logits
+ * stay on the device. */
+int m40llm_logits_head_f32_async(M40llmCudaContext* ctx, const void* d_hidden_f32, const void* d_norm_w,
+                                 uint32_t norm_w_dtype, float eps, const void* d_lm_head_f16, void* d_logits_f32,
+                                 uint32_t rows, uint32_t hidden, uint32_t vocab);
+/* Greedy choice per row (Sampler::sample_greedy, src/sampling.rs:95-108): index of the first largest value under
+ * strict '>' starting from -inf, so NaN is never chosen and a row without any value above -inf yields 0. */
+int m40llm_argmax_f32_async(M40llmCudaContext* ctx, const void* d_values_f32, uint32_t rows, uint32_t n,
+                            uint32_t* d_out_index);
+/* positions[r] += 1 and lens[r] += 1 (either pointer may be NULL): lets a captured token step be replayed back to
+ * back (the reference re-uploads these scalars per token, src/decode_session.rs:856-881). */
+int m40llm_advance_positions_async(M40llmCudaContext* ctx, uint32_t* d_positions, uint32_t* d_lens, uint32_t rows);
 /* No counterpart in the reference. Same contract as m40llm_attention_last_token_f32_gqa_async (dense cache, one
  * sequence, decode stream), but it never allocates or frees device or host memory: the per-split partials live in a
  * fixed 4 MiB device array that belongs to the loaded library. For callers that cannot take an allocating call (all

@@ -26,6 +26,10 @@ class Weights(C.Structure):
                                           "wd")] + [("ffn_q80", C.c_uint32)]
 
 
+class ModelHead(C.Structure):
+    _fields_ = [("embeddings", C.c_void_p), ("output_norm", C.c_void_p), ("lm_head", C.c_void_p), ("vocab", C.c_uint32)]
+
+
 class KvCfg(C.Structure):
     _fields_ = [(n, C.c_uint32) for n in ("mode", "recent_window", "block_size", "top_blocks", "representatives",
                                           "representative_policy", "exact_old_backing", "exact_old_attention")]
@@ -50,6 +54,16 @@ def lib() -> C.CDLL:
         L.m40host_layer_graph_replays.restype = C.c_uint64
         L.m40host_layer_graph_replays.argtypes = [C.c_void_p]
         L.m40host_plan_from_requests.argtypes = [C.c_uint32] + [C.c_void_p] * 8
+        L.m40host_model_create.restype = C.c_void_p
+        L.m40host_model_create.argtypes = [C.c_void_p, C.POINTER(LayerCfg), C.c_uint32, C.POINTER(Weights),
+                                           C.POINTER(ModelHead), C.c_void_p, C.c_uint32]
+        L.m40host_model_destroy.argtypes = [C.c_void_p]
+        L.m40host_model_begin.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p]
+        L.m40host_model_generate.argtypes = [C.c_void_p, C.c_uint32, C.c_uint32, C.c_void_p, C.c_void_p]
+        L.m40host_model_graph_replays.restype = C.c_uint64
+        L.m40host_model_graph_replays.argtypes = [C.c_void_p]
+        L.m40host_model_launches_per_step.restype = C.c_uint64
+        L.m40host_model_launches_per_step.argtypes = [C.c_void_p]
         _lib = L
     return _lib
 
@@ -128,3 +142,46 @@ class DecodeLayer:
         if self.handle:
             lib().m40host_layer_destroy(self.handle)
             self.handle = None
+
+
+class DecodeModel:
+    """Greedy decode of a whole layer stack (embedding -> layers -> logits head -> arg-max on the device); mirror of the
+    reference's session loop (src/decode_session.rs:637-954, src/infer/logits.rs:57-116, src/sampling.rs:95-108).
+    `kv` is a dense cache with sequences * layers slots (slot = sequence * layers + layer, src/infer/kv.rs:109)."""
+
+    def __init__(self, ctx, cfg: LayerCfg, layers, head: ModelHead, kv, sequences: int):
+        arr = (Weights * len(layers))(*layers)
+        self._keep = (arr, head, cfg)
+        self.sequences, self.vocab = sequences, int(head.vocab)
+        self.h = lib().m40host_model_create(ctx, C.byref(cfg), len(layers), arr, C.byref(head), kv, sequences)
+        if not self.h:
+            raise RuntimeError(last_error())
+
+    def begin(self, token_ids, positions):
+        t = np.ascontiguousarray(token_ids, dtype=np.uint32)
+        p = np.ascontiguousarray(positions, dtype=np.uint32)
+        assert t.shape == (self.sequences,) and p.shape == (self.sequences,)
+        if lib().m40host_model_begin(self.h, t.ctypes.data_as(C.c_void_p), p.ctypes.data_as(C.c_void_p)) != 0:
+            raise RuntimeError(last_error())
+
+    def generate(self, steps: int, use_graph: bool = True, want_ids: bool = True, want_logits: bool = False):
+        """Returns (ids [steps, sequences] or None, logits of the last step [sequences, vocab] or None)."""
+        ids = np.empty((steps, self.sequences), np.uint32) if want_ids else None
+        logits = np.empty((self.sequences, self.vocab), np.float32) if want_logits else None
+        rc = lib().m40host_model_generate(self.h, steps, 1 if use_graph else 0,
+                                          ids.ctypes.data_as(C.c_void_p) if want_ids else None,
+                                          logits.ctypes.data_as(C.c_void_p) if want_logits else None)
+        if rc != 0:
+            raise RuntimeError(last_error())
+        return ids, logits
+
+    def graph_replays(self) -> int:
+        return int(lib().m40host_model_graph_replays(self.h))
+
+    def launches_per_step(self) -> int:
+        return int(lib().m40host_model_launches_per_step(self.h))
+
+    def close(self):
+        if self.h:
+            lib().m40host_model_destroy(self.h)
+            self.h = None

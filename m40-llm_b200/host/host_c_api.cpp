@@ -6,6 +6,7 @@
 
 #include "decode_batch.hpp"
 #include "decode_layer.hpp"
+#include "decode_model.hpp"
 #include "kv_compression.hpp"
 
 using namespace m40host;
@@ -109,5 +110,61 @@ int m40host_layer_forward_host(void* layer, M40llmKVCache* kv, const m40host_wei
 }
 
 uint64_t m40host_layer_graph_replays(void* layer) { return ((DecodeLayer*)layer)->graph_replays(); }
+
+
+// ---- whole-model greedy decode (decode_model.hpp)
+struct m40host_model_head {
+    const void *embeddings, *output_norm, *lm_head;
+    uint32_t vocab;
+};
+
+void* m40host_model_create(M40llmCudaContext* ctx, const m40host_layer_cfg* c, uint32_t n_layers,
+                           const m40host_weights* layers, const m40host_model_head* head, M40llmKVCache* kv,
+                           uint32_t sequences) {
+    if (!ctx || !c || !layers || !head || !kv || n_layers == 0) {
+        g_err = "m40host_model_create: null argument";
+        return nullptr;
+    }
+    ModelConfig m;
+    m.hidden = c->hidden, m.q_heads = c->q_heads, m.kv_heads = c->kv_heads, m.head_dim = c->head_dim, m.ffn = c->ffn;
+    m.rope_layout = c->rope_layout, m.rms_eps = c->rms_eps, m.rope_base = c->rope_base, m.rope_scale = c->rope_scale;
+    std::vector<LayerWeights> lw(n_layers);
+    for (uint32_t i = 0; i < n_layers; ++i) {
+        const m40host_weights& w = layers[i];
+        lw[i].attn_norm = w.attn_norm, lw[i].ffn_norm = w.ffn_norm;
+        lw[i].wq = w.wq, lw[i].wk = w.wk, lw[i].wv = w.wv, lw[i].wo = w.wo;
+        lw[i].bq = w.bq, lw[i].bk = w.bk, lw[i].bv = w.bv;
+        lw[i].wg = w.wg, lw[i].wu = w.wu, lw[i].wd = w.wd;
+        lw[i].ffn_q80 = w.ffn_q80 != 0;
+    }
+    ModelHead h;
+    h.embeddings = head->embeddings, h.output_norm = head->output_norm, h.lm_head = head->lm_head, h.vocab = head->vocab;
+    DecodeModel* dm = new DecodeModel(ctx, m, lw, h, kv, sequences);
+    if (!dm->ok()) {
+        g_err = "m40host_model_create: device allocation failed or bad arguments";
+        delete dm;
+        return nullptr;
+    }
+    return dm;
+}
+
+void m40host_model_destroy(void* model) { delete (DecodeModel*)model; }
+
+int m40host_model_begin(void* model, const uint32_t* token_ids, const uint32_t* positions) {
+    DecodeModel* dm = (DecodeModel*)model;
+    const int rc = dm->begin(token_ids, positions);
+    if (rc != 0) g_err = "model begin failed at " + dm->failed_step() + " rc=" + std::to_string(rc);
+    return rc;
+}
+
+int m40host_model_generate(void* model, uint32_t steps, uint32_t use_graph, uint32_t* out_ids, float* out_logits) {
+    DecodeModel* dm = (DecodeModel*)model;
+    const int rc = dm->generate(steps, use_graph != 0, out_ids, out_logits);
+    if (rc != 0) g_err = "model generate failed at " + dm->failed_step() + " rc=" + std::to_string(rc);
+    return rc;
+}
+
+uint64_t m40host_model_graph_replays(void* model) { return ((DecodeModel*)model)->graph_replays(); }
+uint64_t m40host_model_launches_per_step(void* model) { return ((DecodeModel*)model)->launches_per_step(); }
 
 }  // extern "C"

@@ -1,0 +1,107 @@
+"""Whole-model greedy decode through the host driver (embedding -> layers -> logits head -> arg-max on the device)
+against the oracle's composition of the same steps (src/decode_session.rs:637-954, src/infer/logits.rs:57-116,
+src/sampling.rs:95-108). TinyLlama-shaped layers (BASELINE configs[1]) with a short stack so the oracle stays fast."""
+import numpy as np
+import pytest
+
+from helpers import assert_close
+from test_gpu_layer import make_weights, _host_weights
+
+pytestmark = pytest.mark.gpu
+
+
+def oracle_step(O, cfg, layers, emb, out_norm, lm, Ks, Vs, token, pos):
+    x = O.f16_to_f32(emb[token])
+    for l, w in enumerate(layers):
+        x, _, _ = O.decode_layer(cfg, x, w, Ks[l], Vs[l], pos)   # appends K/V of `pos` into Ks[l], Vs[l]
+    logits = O.gemm_f32xf16_gguf(O.rms_norm(x[None, :], out_norm, cfg.eps), lm)[0]
+    return logits
+
+
+@pytest.mark.parametrize("H,qh,kvh,hd,F,q80,n_layers,vocab,ctx_len", [
+    (256, 8, 2, 32, 512, False, 2, 1000, 9),
+    (2048, 32, 4, 64, 5632, False, 3, 32000, 70),    # TinyLlama shapes, 3 of its 22 layers
+    (1024, 16, 4, 64, 2048, True, 2, 5000, 33),      # Q8_0 FFN
+])
+def test_greedy_decode_matches_oracle(nat, O, pkg, H, qh, kvh, hd, F, q80, n_layers, vocab, ctx_len):
+    rng = np.random.default_rng(H + vocab)
+    steps, seqs = 4, 2
+    cfg = O.LayerCfg(H, qh, kvh, hd, F, 1 if q80 else 0, 0, 1e-5, 1e4, 1.0)
+    layers = [make_weights(O, rng, H, qh, kvh, hd, F, q80, False) for _ in range(n_layers)]
+    emb = (rng.standard_normal((vocab, H)) * 0.5).astype(np.float16)
+    lm = (rng.standard_normal((vocab, H)) * 0.02).astype(np.float16)
+    out_norm = (1 + 0.05 * rng.standard_normal(H)).astype(np.float32)
+    max_seq = ctx_len + 2 * steps + 2
+    kv = nat.kv_dense(max_seq, seqs * n_layers, kvh, hd)
+    lens = [ctx_len, ctx_len // 2]
+    Ks = [[np.zeros((max_seq, kvh, hd), np.float16) for _ in range(n_layers)] for _ in range(seqs)]
+    Vs = [[np.zeros((max_seq, kvh, hd), np.float16) for _ in range(n_layers)] for _ in range(seqs)]
+    for s in range(seqs):
+        for l in range(n_layers):
+            Ks[s][l][:lens[s]] = rng.standard_normal((lens[s], kvh, hd)).astype(np.float16)
+            Vs[s][l][:lens[s]] = rng.standard_normal((lens[s], kvh, hd)).astype(np.float16)
+            nat.kv_fill(kv, s * n_layers + l, Ks[s][l][:lens[s]], Vs[s][l][:lens[s]])
+    host = pkg.host
+    hw = [_host_weights(pkg, nat, w, q80) for w in layers]
+    head = host.ModelHead(nat.buf(emb).ptr, nat.buf(out_norm).ptr, nat.buf(lm).ptr, vocab)
+    model = host.DecodeModel(nat.ctx, host.LayerCfg(H, qh, kvh, hd, F, 0, 1e-5, 1e4, 1.0), hw, head, kv, seqs)
+    first = rng.integers(0, vocab, size=seqs).astype(np.uint32)
+    for use_graph in (False, True):
+        if use_graph:  # second pass continues from where the first stopped (positions advanced on the device)
+            start_tok, start_pos = ids[-1], [n + steps for n in lens]
+        else:
+            start_tok, start_pos = first, lens
+        model.begin(start_tok, start_pos)
+        ids, logits = model.generate(steps, use_graph=use_graph, want_logits=True)
+        for s in range(seqs):
+            tok, pos = int(start_tok[s]), int(start_pos[s])
+            for t in range(steps):
+                elog = oracle_step(O, cfg, layers, emb, out_norm, lm, Ks[s], Vs[s], tok, pos)
+                order = np.argsort(-elog, kind="stable")
+                gap = elog[order[0]] - elog[order[1]]
+                got = int(ids[t, s])
+                if gap > 4e-3:   # a clear winner must be reproduced; a near tie may go either way
+                    assert got == int(order[0]), f"seq {s} step {t} graph={use_graph}: {got} vs {int(order[0])} (gap {gap})"
+                else:
+                    assert elog[got] >= elog[order[0]] - 4e-3
+                if t == steps - 1:
+                    assert_close(logits[s], elog, what=f"logits seq {s} graph={use_graph}")
+                tok, pos = got, pos + 1
+    assert model.graph_replays() >= steps - 2
+    model.close()
+    nat.lib.m40llm_kvcache_destroy(kv)
+    nat.free_all()
+
+
+def test_argmax_and_embedding_rules(nat):
+    L = nat.lib
+    x = np.array([[1.0, 5.0, 5.0, np.nan, -np.inf], [np.nan, np.nan, np.nan, np.nan, np.nan],
+                  [-np.inf, -np.inf, -3.0, -3.0, -np.inf]], np.float32)
+    dx, do = nat.buf(x), nat.buf(3 * 4)
+    assert L.m40llm_argmax_f32_async(nat.ctx, dx.ptr, 3, 5, do.ptr) == 0
+    nat.sync(1)
+    assert list(do.download(np.uint32, (3,))) == [1, 0, 2]      # first maximum; no candidate -> 0 (sampling.rs:95-108)
+    big = np.zeros((1, 70001), np.float32)
+    big[0, 65000] = big[0, 69999] = 2.5
+    dx2 = nat.buf(big)
+    assert L.m40llm_argmax_f32_async(nat.ctx, dx2.ptr, 1, 70001, do.ptr) == 0
+    nat.sync(1)
+    assert int(do.download(np.uint32, (1,))[0]) == 65000
+    table = np.arange(6 * 8, dtype=np.float32).reshape(6, 8).astype(np.float16)
+    ids = np.array([5, 0, 9], np.uint32)                        # 9 is outside the table
+    dt, di, de = nat.buf(table), nat.buf(ids), nat.buf(3 * 8 * 4)
+    assert L.m40llm_embed_tokens_f16_async(nat.ctx, dt.ptr, di.ptr, de.ptr, 3, 8, 6) == 0
+    nat.sync(1)
+    got = de.download(np.float32, (3, 8))
+    assert np.array_equal(got[0], table[5].astype(np.float32)) and np.array_equal(got[1], table[0].astype(np.float32))
+    assert not got[2].any()
+    st = np.zeros(1, np.uint32)
+    assert L.m40llm_context_take_device_status(nat.ctx, st.ctypes.data) == 0 and st[0] == 8
+    p = np.array([3, 7], np.uint32)
+    dp, dl = nat.buf(p), nat.buf(p + 1)
+    assert L.m40llm_advance_positions_async(nat.ctx, dp.ptr, dl.ptr, 2) == 0
+    nat.sync(1)
+    assert list(dp.download(np.uint32, (2,))) == [4, 8] and list(dl.download(np.uint32, (2,))) == [5, 9]
+    assert L.m40llm_argmax_f32_async(nat.ctx, None, 1, 5, do.ptr) == -1
+    assert L.m40llm_logits_head_f32_async(nat.ctx, dx.ptr, None, 0, 1e-5, None, do.ptr, 1, 8, 6) == -1
+    nat.free_all()
