@@ -47,6 +47,8 @@ __global__ void __launch_bounds__(128) block_score_kernel(SelArgs a) {
     constexpr int LPT = HD / 8;        // lanes per token row (16-byte pieces)
     constexpr int TPI = 32 / LPT;      // tokens per warp-wide load
     extern __shared__ float sq[];      // q of this kv head's group: [G][HD]
+    pdl_wait();
+    pdl_trigger();
     const uint32_t kvh = blockIdx.y;
     const uint32_t G = a.q_heads / a.kv_heads;
     for (uint32_t i = threadIdx.x; i < G * HD; i += blockDim.x) sq[i] = a.q[(size_t)kvh * G * HD + i];
@@ -61,7 +63,7 @@ __global__ void __launch_bounds__(128) block_score_kernel(SelArgs a) {
     float acc[8];
 #pragma unroll
     for (int j = 0; j < 8; ++j) acc[j] = 0.0f;
-#pragma unroll 4
+#pragma unroll 8
     for (uint32_t t = t0 + sub; t < t1; t += TPI) {
         const uint4 w = *reinterpret_cast<const uint4*>(Kh + (size_t)t * HD + piece * 8);
         const __half2* h = reinterpret_cast<const __half2*>(&w);
@@ -86,6 +88,37 @@ __global__ void __launch_bounds__(128) block_score_kernel(SelArgs a) {
 #pragma unroll
         for (int o = LPT / 2; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
         if (lane == 0) a.scores[(size_t)(kvh * G + g) * a.score_stride + (b - a.block_begin)] = (dot * inv_len) * a.inv_sqrt;
+    }
+}
+
+// ---- 2a. top-k by rank. grid q_heads, 256 threads, for nb <= 4096. A block's place in the descending list is the
+// number of selectable blocks that beat it (greater score, or equal score and lower index), which is exactly the
+// order the iterative arg-max below produces; every thread ranks its own blocks against all of shared memory, so the
+// whole selection is one pass with one barrier. Scores that are NaN or <= -1e30 are never selectable.
+__global__ void __launch_bounds__(256) topk_rank_kernel(SelArgs a) {
+    extern __shared__ float sc[];  // nb scores, unselectable ones replaced by -inf
+    pdl_wait();
+    pdl_trigger();
+    const uint32_t h = blockIdx.x;
+    for (uint32_t i = threadIdx.x; i < a.nb; i += blockDim.x) {
+        const float s = a.scores[(size_t)h * a.score_stride + i];
+        sc[i] = s > -1e30f ? s : -INFINITY;  // false for NaN too
+    }
+    for (uint32_t i = threadIdx.x; i < 64u; i += blockDim.x) {
+        a.sel_blocks[h * 64u + i] = 0xffffffffu;
+        a.sel_scores[h * 64u + i] = -1e30f;
+    }
+    __syncthreads();
+    for (uint32_t i = threadIdx.x; i < a.nb; i += blockDim.x) {
+        const float s = sc[i];
+        if (s == -INFINITY) continue;
+        uint32_t rank = 0;
+        for (uint32_t j = 0; j < i; ++j) rank += sc[j] >= s ? 1u : 0u;         // equal score, lower index: ahead
+        for (uint32_t j = i + 1; j < a.nb; ++j) rank += sc[j] > s ? 1u : 0u;
+        if (rank < a.top_n) {
+            a.sel_blocks[h * 64u + rank] = i;
+            a.sel_scores[h * 64u + rank] = s;
+        }
     }
 }
 
@@ -156,6 +189,8 @@ __global__ void __launch_bounds__(128) selected_attend_kernel(SelArgs a) {
     constexpr int DPL = HD / 32;  // dims per lane (4 for 128, 2 for 64), contiguous
     __shared__ uint32_t sblk[64];
     __shared__ float sm_m[4], sm_l[4], sm_o[4][HD];
+    pdl_wait();
+    pdl_trigger();
     const uint32_t split = blockIdx.x, h = blockIdx.y;
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
     const uint32_t G = a.q_heads / a.kv_heads, kvh = h / G;
@@ -181,68 +216,101 @@ __global__ void __launch_bounds__(128) selected_attend_kernel(SelArgs a) {
         acc[j] = 0.0f;
     }
     float m = -INFINITY, l = 0.0f;
-    for (uint32_t slot = s0 + warp; slot < s1; slot += 4u) {
-        uint32_t t;
-        bool old_tok;
-        if (slot < sel_slots) {
-            const uint32_t b = sblk[slot / a.block_size];
-            if (b == 0xffffffffu) continue;
-            t = b * a.block_size + slot % a.block_size;
-            if (t >= a.old_len) continue;
-            old_tok = true;
-        } else {
-            t = a.old_len + (slot - sel_slots);
-            old_tok = false;
-        }
-        const __half* kp;
-        if (DENSE || old_tok) kp = a.old_k + head_base + (size_t)t * HD;
-        else kp = a.ring_k + ring_base + (size_t)(t % a.ring_size) * HD;
-        float kx[DPL], vx[DPL];
-        if (DPL == 4) {
-            const uint2 w = *reinterpret_cast<const uint2*>(kp + lane * 4);
-            const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&w.x));
-            const float2 f1 = __half22float2(*reinterpret_cast<const __half2*>(&w.y));
-            kx[0] = f0.x; kx[1] = f0.y; kx[DPL - 2] = f1.x; kx[DPL - 1] = f1.y;
-        } else {
-            const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(kp + lane * 2));
-            kx[0] = f0.x; kx[1] = f0.y;
-        }
-        float dot = 0.0f;
+    // A warp takes U consecutive slots per pass and issues every load of the pass (K rows, then V rows / q4 bytes
+    // and scales) before it uses any of them: the pass costs one memory latency instead of U.
+    constexpr int U = 4;
+    for (uint32_t base = s0 + warp * U; base < s1; base += 4u * U) {
+        uint32_t tok[U];
+        bool live[U], old_tok[U];
 #pragma unroll
-        for (int j = 0; j < DPL; ++j) dot = fmaf(qr[j], kx[j], dot);
-        const float s = warp_sum(dot) * a.inv_sqrt;
-        if (!DENSE && old_tok) {
-            const float scale = a.q4_scale[vec_base + t];
-            const uint8_t* vp = a.q4_v + (vec_base + t) * (HD / 2) + lane * (DPL / 2);
-            uint32_t bytes;
-            if (DPL == 4) bytes = *reinterpret_cast<const uint16_t*>(vp);
-            else bytes = *vp;
-#pragma unroll
-            for (int j = 0; j < DPL; ++j) {
-                const uint32_t nib = (bytes >> (4 * j)) & 0xfu;
-                const int sv = nib >= 8u ? (int)nib - 16 : (int)nib;
-                vx[j] = __half2float(__float2half_rn((float)sv * scale));
-            }
-        } else {
-            const __half* vp = DENSE ? a.dense_v + head_base + (size_t)t * HD
-                                     : a.ring_v + ring_base + (size_t)(t % a.ring_size) * HD;
-            if (DPL == 4) {
-                const uint2 w = *reinterpret_cast<const uint2*>(vp + lane * 4);
-                const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&w.x));
-                const float2 f1 = __half22float2(*reinterpret_cast<const __half2*>(&w.y));
-                vx[0] = f0.x; vx[1] = f0.y; vx[DPL - 2] = f1.x; vx[DPL - 1] = f1.y;
+        for (int i = 0; i < U; ++i) {
+            const uint32_t slot = base + i;
+            live[i] = slot < s1;
+            old_tok[i] = false;
+            tok[i] = 0;
+            if (!live[i]) continue;
+            if (slot < sel_slots) {
+                const uint32_t b = sblk[slot / a.block_size];
+                const uint32_t t = b * a.block_size + slot % a.block_size;
+                if (b == 0xffffffffu || t >= a.old_len) live[i] = false;
+                else tok[i] = t, old_tok[i] = true;
             } else {
-                const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(vp + lane * 2));
-                vx[0] = f0.x; vx[1] = f0.y;
+                tok[i] = a.old_len + (slot - sel_slots);
             }
         }
-        const float mn = fmaxf(m, s);
-        const float corr = expf(m - mn);
-        const float p = expf(s - mn);
-        l = l * corr + p;
+        uint2 kw[U], vw[U];
+        float vscale[U];
 #pragma unroll
-        for (int j = 0; j < DPL; ++j) acc[j] = fmaf(p, vx[j], acc[j] * corr);
-        m = mn;
+        for (int i = 0; i < U; ++i) {
+            kw[i] = make_uint2(0u, 0u);
+            if (!live[i]) continue;
+            const __half* kp = (DENSE || old_tok[i]) ? a.old_k + head_base + (size_t)tok[i] * HD
+                                                     : a.ring_k + ring_base + (size_t)(tok[i] % a.ring_size) * HD;
+            if (DPL == 4) kw[i] = *reinterpret_cast<const uint2*>(kp + lane * 4);
+            else kw[i].x = *reinterpret_cast<const uint32_t*>(kp + lane * 2);
+        }
+#pragma unroll
+        for (int i = 0; i < U; ++i) {
+            vw[i] = make_uint2(0u, 0u);
+            vscale[i] = 0.0f;
+            if (!live[i]) continue;
+            if (!DENSE && old_tok[i]) {
+                vscale[i] = a.q4_scale[vec_base + tok[i]];
+                const uint8_t* vp = a.q4_v + (vec_base + tok[i]) * (HD / 2) + lane * (DPL / 2);
+                if (DPL == 4) vw[i].x = *reinterpret_cast<const uint16_t*>(vp);
+                else vw[i].x = *vp;
+            } else {
+                const __half* vp = DENSE ? a.dense_v + head_base + (size_t)tok[i] * HD
+                                         : a.ring_v + ring_base + (size_t)(tok[i] % a.ring_size) * HD;
+                if (DPL == 4) vw[i] = *reinterpret_cast<const uint2*>(vp + lane * 4);
+                else vw[i].x = *reinterpret_cast<const uint32_t*>(vp + lane * 2);
+            }
+        }
+        float sc[U];
+#pragma unroll
+        for (int i = 0; i < U; ++i) {
+            const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&kw[i].x));
+            float dot = fmaf(qr[0], f0.x, 0.0f);
+            dot = fmaf(qr[1], f0.y, dot);
+            if (DPL == 4) {
+                const float2 f1 = __half22float2(*reinterpret_cast<const __half2*>(&kw[i].y));
+                dot = fmaf(qr[DPL - 2], f1.x, dot);
+                dot = fmaf(qr[DPL - 1], f1.y, dot);
+            }
+            sc[i] = dot;
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+            for (int i = 0; i < U; ++i) sc[i] += __shfl_xor_sync(0xffffffffu, sc[i], o);
+#pragma unroll
+        for (int i = 0; i < U; ++i) {
+            if (!live[i]) continue;  // warp-uniform
+            const float s = sc[i] * a.inv_sqrt;
+            float vx[DPL];
+            if (!DENSE && old_tok[i]) {
+#pragma unroll
+                for (int j = 0; j < DPL; ++j) {
+                    const uint32_t nib = (vw[i].x >> (4 * j)) & 0xfu;
+                    const int sv = nib >= 8u ? (int)nib - 16 : (int)nib;
+                    vx[j] = __half2float(__float2half_rn((float)sv * vscale[i]));
+                }
+            } else {
+                const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&vw[i].x));
+                vx[0] = f0.x; vx[1] = f0.y;
+                if (DPL == 4) {
+                    const float2 f1 = __half22float2(*reinterpret_cast<const __half2*>(&vw[i].y));
+                    vx[DPL - 2] = f1.x; vx[DPL - 1] = f1.y;
+                }
+            }
+            const float mn = fmaxf(m, s);
+            const float corr = expf(m - mn);
+            const float pw = expf(s - mn);
+            l = l * corr + pw;
+#pragma unroll
+            for (int j = 0; j < DPL; ++j) acc[j] = fmaf(pw, vx[j], acc[j] * corr);
+            m = mn;
+        }
     }
     if (lane == 0) {
         sm_m[warp] = m;
@@ -318,15 +386,21 @@ int launch_scores(M40llmCudaContext* ctx, const SelArgs& a) {
     const uint32_t G = a.q_heads / a.kv_heads;
     dim3 grid((blocks + 3u) / 4u, a.kv_heads);
     const size_t smem = (size_t)G * a.hd * sizeof(float);
-    if (a.hd == 128) block_score_kernel<128><<<grid, 128, smem, ctx->decode_stream>>>(a);
-    else block_score_kernel<64><<<grid, 128, smem, ctx->decode_stream>>>(a);
+    cudaError_t e;
+    if (a.hd == 128) e = m40_launch_dependent(block_score_kernel<128>, grid, dim3(128), smem, ctx->decode_stream, a);
+    else e = m40_launch_dependent(block_score_kernel<64>, grid, dim3(128), smem, ctx->decode_stream, a);
     M40_COUNT_LAUNCH(ctx);
-    return cudaGetLastError() == cudaSuccess ? 0 : -8;
+    return e == cudaSuccess && cudaGetLastError() == cudaSuccess ? 0 : -8;
 }
 
 int launch_topk(M40llmCudaContext* ctx, const SelArgs& a) {
     const size_t smem = (size_t)(a.nb ? a.nb : 1u) * sizeof(float);
     if (smem > 200u * 1024u) return -7;
+    if (a.nb <= 4096u) {
+        const cudaError_t e = m40_launch_dependent(topk_rank_kernel, dim3(a.q_heads), dim3(256), smem, ctx->decode_stream, a);
+        M40_COUNT_LAUNCH(ctx);
+        return e == cudaSuccess && cudaGetLastError() == cudaSuccess ? 0 : -8;
+    }
     if (smem > 48u * 1024u)
         cudaFuncSetAttribute(topk_blocks_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     topk_blocks_kernel<<<a.q_heads, 128, smem, ctx->decode_stream>>>(a);
@@ -337,15 +411,16 @@ int launch_topk(M40llmCudaContext* ctx, const SelArgs& a) {
 int launch_attend(M40llmCudaContext* ctx, const SelArgs& a, bool dense) {
     dim3 grid(a.splits, a.q_heads);
     cudaStream_t s = ctx->decode_stream;
+    cudaError_t e;
     if (a.hd == 128) {
-        if (dense) selected_attend_kernel<128, true><<<grid, 128, 0, s>>>(a);
-        else selected_attend_kernel<128, false><<<grid, 128, 0, s>>>(a);
+        if (dense) e = m40_launch_dependent(selected_attend_kernel<128, true>, grid, dim3(128), 0, s, a);
+        else e = m40_launch_dependent(selected_attend_kernel<128, false>, grid, dim3(128), 0, s, a);
     } else {
-        if (dense) selected_attend_kernel<64, true><<<grid, 128, 0, s>>>(a);
-        else selected_attend_kernel<64, false><<<grid, 128, 0, s>>>(a);
+        if (dense) e = m40_launch_dependent(selected_attend_kernel<64, true>, grid, dim3(128), 0, s, a);
+        else e = m40_launch_dependent(selected_attend_kernel<64, false>, grid, dim3(128), 0, s, a);
     }
     M40_COUNT_LAUNCH(ctx);
-    return cudaGetLastError() == cudaSuccess ? 0 : -8;
+    return e == cudaSuccess && cudaGetLastError() == cudaSuccess ? 0 : -8;
 }
 
 uint32_t attend_splits(const M40llmCudaContext* ctx, const SelArgs& a) {
