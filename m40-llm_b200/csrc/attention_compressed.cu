@@ -91,11 +91,11 @@ __global__ void __launch_bounds__(128) block_score_kernel(SelArgs a) {
     }
 }
 
-// ---- 2a. top-k by rank. grid q_heads, 256 threads, for nb <= 4096. A block's place in the descending list is the
+// ---- 2a. top-k by rank. grid q_heads, 1024 threads, for nb <= 4096. A block's place in the descending list is the
 // number of selectable blocks that beat it (greater score, or equal score and lower index), which is exactly the
 // order the iterative arg-max below produces; every thread ranks its own blocks against all of shared memory, so the
 // whole selection is one pass with one barrier. Scores that are NaN or <= -1e30 are never selectable.
-__global__ void __launch_bounds__(256) topk_rank_kernel(SelArgs a) {
+__global__ void __launch_bounds__(1024) topk_rank_kernel(SelArgs a) {
     extern __shared__ float sc[];  // nb scores, unselectable ones replaced by -inf
     pdl_wait();
     pdl_trigger();
@@ -109,13 +109,21 @@ __global__ void __launch_bounds__(256) topk_rank_kernel(SelArgs a) {
         a.sel_scores[h * 64u + i] = -1e30f;
     }
     __syncthreads();
-    for (uint32_t i = threadIdx.x; i < a.nb; i += blockDim.x) {
-        const float s = sc[i];
-        if (s == -INFINITY) continue;
+    // four adjacent lanes share one block i and scan a quarter of the others each
+    const uint32_t part = threadIdx.x & 3u, q0 = (a.nb * part) / 4u, q1 = (a.nb * (part + 1u)) / 4u;
+    for (uint32_t i0 = 0; i0 < a.nb; i0 += blockDim.x / 4u) {
+        const uint32_t i = i0 + threadIdx.x / 4u;
+        const float s = i < a.nb ? sc[i] : -INFINITY;
         uint32_t rank = 0;
-        for (uint32_t j = 0; j < i; ++j) rank += sc[j] >= s ? 1u : 0u;         // equal score, lower index: ahead
-        for (uint32_t j = i + 1; j < a.nb; ++j) rank += sc[j] > s ? 1u : 0u;
-        if (rank < a.top_n) {
+        if (s != -INFINITY) {
+            for (uint32_t j = q0; j < q1; ++j) {
+                const float o = sc[j];
+                rank += (o > s || (o == s && j < i)) ? 1u : 0u;  // equal score, lower index: ahead
+            }
+        }
+        rank += __shfl_xor_sync(0xffffffffu, rank, 1);
+        rank += __shfl_xor_sync(0xffffffffu, rank, 2);
+        if (part == 0 && s != -INFINITY && rank < a.top_n) {
             a.sel_blocks[h * 64u + rank] = i;
             a.sel_scores[h * 64u + rank] = s;
         }
@@ -218,24 +226,36 @@ __global__ void __launch_bounds__(128) selected_attend_kernel(SelArgs a) {
     float m = -INFINITY, l = 0.0f;
     // A warp takes U consecutive slots per pass and issues every load of the pass (K rows, then V rows / q4 bytes
     // and scales) before it uses any of them: the pass costs one memory latency instead of U.
-    constexpr int U = 4;
+    constexpr int U = 8;
     for (uint32_t base = s0 + warp * U; base < s1; base += 4u * U) {
         uint32_t tok[U];
         bool live[U], old_tok[U];
+        {
+            // one division pair per pass: the U slots are consecutive, so list position, offset in the block and
+            // ring position are carried
+            uint32_t li = 0, off = 0, rpos = 0, rt = 0;
+            if (base < sel_slots) li = base / a.block_size, off = base % a.block_size;
+            const uint32_t first_recent = base < sel_slots ? sel_slots : base;  // first slot of the pass in the ring part
+            rt = a.old_len + (first_recent - sel_slots);
+            if (!DENSE && a.ring_size) rpos = rt % a.ring_size;
 #pragma unroll
-        for (int i = 0; i < U; ++i) {
-            const uint32_t slot = base + i;
-            live[i] = slot < s1;
-            old_tok[i] = false;
-            tok[i] = 0;
-            if (!live[i]) continue;
-            if (slot < sel_slots) {
-                const uint32_t b = sblk[slot / a.block_size];
-                const uint32_t t = b * a.block_size + slot % a.block_size;
-                if (b == 0xffffffffu || t >= a.old_len) live[i] = false;
-                else tok[i] = t, old_tok[i] = true;
-            } else {
-                tok[i] = a.old_len + (slot - sel_slots);
+            for (int i = 0; i < U; ++i) {
+                const uint32_t slot = base + i;
+                live[i] = slot < s1;
+                old_tok[i] = false;
+                tok[i] = 0;
+                if (slot < sel_slots) {
+                    const uint32_t b = sblk[li < 64u ? li : 63u];
+                    const uint32_t t = b * a.block_size + off;
+                    if (b == 0xffffffffu || t >= a.old_len) live[i] = false;
+                    else tok[i] = t, old_tok[i] = true;
+                    if (++off == a.block_size) off = 0, ++li;
+                } else {
+                    // dense form: the token index; ring form: the ring row of that token
+                    tok[i] = DENSE ? rt : rpos;
+                    ++rt;
+                    if (++rpos == a.ring_size) rpos = 0;
+                }
             }
         }
         uint2 kw[U], vw[U];
@@ -245,7 +265,7 @@ __global__ void __launch_bounds__(128) selected_attend_kernel(SelArgs a) {
             kw[i] = make_uint2(0u, 0u);
             if (!live[i]) continue;
             const __half* kp = (DENSE || old_tok[i]) ? a.old_k + head_base + (size_t)tok[i] * HD
-                                                     : a.ring_k + ring_base + (size_t)(tok[i] % a.ring_size) * HD;
+                                                     : a.ring_k + ring_base + (size_t)tok[i] * HD;
             if (DPL == 4) kw[i] = *reinterpret_cast<const uint2*>(kp + lane * 4);
             else kw[i].x = *reinterpret_cast<const uint32_t*>(kp + lane * 2);
         }
@@ -261,7 +281,7 @@ __global__ void __launch_bounds__(128) selected_attend_kernel(SelArgs a) {
                 else vw[i].x = *vp;
             } else {
                 const __half* vp = DENSE ? a.dense_v + head_base + (size_t)tok[i] * HD
-                                         : a.ring_v + ring_base + (size_t)(tok[i] % a.ring_size) * HD;
+                                         : a.ring_v + ring_base + (size_t)tok[i] * HD;
                 if (DPL == 4) vw[i] = *reinterpret_cast<const uint2*>(vp + lane * 4);
                 else vw[i].x = *reinterpret_cast<const uint32_t*>(vp + lane * 2);
             }
@@ -291,9 +311,10 @@ __global__ void __launch_bounds__(128) selected_attend_kernel(SelArgs a) {
             if (!DENSE && old_tok[i]) {
 #pragma unroll
                 for (int j = 0; j < DPL; ++j) {
+                    // signed nibble as an exact float without a conversion instruction: 2^23 + (nib ^ 8) - (2^23 + 8)
                     const uint32_t nib = (vw[i].x >> (4 * j)) & 0xfu;
-                    const int sv = nib >= 8u ? (int)nib - 16 : (int)nib;
-                    vx[j] = __half2float(__float2half_rn((float)sv * vscale[i]));
+                    const float sv = __uint_as_float(0x4B000000u | (nib ^ 8u)) - 8388616.0f;
+                    vx[j] = __half2float(__float2half_rn(sv * vscale[i]));
                 }
             } else {
                 const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&vw[i].x));
@@ -397,7 +418,7 @@ int launch_topk(M40llmCudaContext* ctx, const SelArgs& a) {
     const size_t smem = (size_t)(a.nb ? a.nb : 1u) * sizeof(float);
     if (smem > 200u * 1024u) return -7;
     if (a.nb <= 4096u) {
-        const cudaError_t e = m40_launch_dependent(topk_rank_kernel, dim3(a.q_heads), dim3(256), smem, ctx->decode_stream, a);
+        const cudaError_t e = m40_launch_dependent(topk_rank_kernel, dim3(a.q_heads), dim3(1024), smem, ctx->decode_stream, a);
         M40_COUNT_LAUNCH(ctx);
         return e == cudaSuccess && cudaGetLastError() == cudaSuccess ? 0 : -8;
     }
@@ -425,11 +446,12 @@ int launch_attend(M40llmCudaContext* ctx, const SelArgs& a, bool dense) {
 
 uint32_t attend_splits(const M40llmCudaContext* ctx, const SelArgs& a) {
     const uint32_t total = 64u * a.block_size + (a.seq_len - a.old_len);
-    uint32_t splits = ((uint32_t)ctx->sm_count * 4u + a.q_heads - 1u) / a.q_heads;
-    const uint32_t max_splits = (total + 127u) / 128u;
+    // ~8 CTAs per SM, never fewer than 64 slots per CTA: the kernel is latency-bound, so parallelism is what counts
+    uint32_t splits = ((uint32_t)ctx->sm_count * 8u + a.q_heads - 1u) / a.q_heads;
+    const uint32_t max_splits = (total + 63u) / 64u;
     if (splits > max_splits) splits = max_splits;
     if (splits < 1u) splits = 1u;
-    if (splits > 64u) splits = 64u;
+    if (splits > 128u) splits = 128u;
     return splits;
 }
 
