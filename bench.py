@@ -280,6 +280,39 @@ def attention_only_case(nat, args):
     nat.lib.m40llm_kvcache_destroy(kv)
 
 
+def ffn_only_case(nat, O, args):
+    """The Q8_0 SwiGLU FFN of the bench layer alone (187 MB of weights per call, three weight sets rotated so that
+    nothing survives in L2): the case the committed profiler summaries of the projection kernels are taken on."""
+    rows = args.ffn_only
+    rng = np.random.default_rng(3)
+    sets = []
+    for _ in range(3):
+        w = {n: nat.buf(O.q80_quantize(rng.standard_normal(s, dtype=np.float32) * np.float32(0.02)))
+             for n, s in dict(wg=(F, H), wu=(F, H), wd=(H, F)).items()}
+        sets.append(w)
+    dx = nat.buf(rng.standard_normal((rows, H), dtype=np.float32))
+    dh, do = nat.buf(rows * F * 4), nat.buf(rows * H * 4)
+    L, ctx = nat.lib, nat.ctx
+
+    def call(i):
+        w = sets[i % 3]
+        rc = L.m40llm_ffn_swiglu_q80_f32_async(ctx, dx.ptr, w["wg"].ptr, w["wu"].ptr, w["wd"].ptr, None, dh.ptr, do.ptr,
+                                               rows, H, F, 1)
+        assert rc == 0, rc
+
+    ev = Events(nat)
+    for i in range(3):
+        call(i)
+    nat.sync(1)
+    ev.start()
+    for i in range(args.steps):
+        call(i)
+    ms = ev.stop_ms() / args.steps
+    by = 3 * F * (H // 32) * 34
+    print(json.dumps({"case": "ffn_only", "rows": rows, "algorithmic_bytes": by, "ms_per_call": ms,
+                      "achieved_gbs": by / ms / 1e6}), flush=True)
+
+
 def run_reference_arm(args, rank, world):
     """`--impl reference`: the reference's CPU path is Rust and cannot be built here (no cargo/rustc, no network),
     so the timed stand-in is the oracle port of that math, on all host threads. Rank 0 only."""
@@ -318,6 +351,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--ffn-only", type=int, default=0, metavar="ROWS",
+                    help="small case for a profiler: the Q8_0 SwiGLU FFN alone for ROWS activation rows")
     ap.add_argument("--attention-only", type=int, default=0, metavar="N",
                     help="small case for a profiler: the batched attention call alone over the first N sequences")
     args = ap.parse_args()
@@ -344,6 +379,9 @@ def main():
 
     if args.attention_only:
         attention_only_case(nat, args)
+        return
+    if args.ffn_only:
+        ffn_only_case(nat, O, args)
         return
     lens, sets, x = make_inputs(O, rank)
     dw = [{n: nat.buf(a) for n, a in w.items()} for w in sets]
