@@ -39,7 +39,7 @@ B, LMIN, LMAX = 32, 512, 8192
 EPS, THETA = 1e-5, 500000.0
 N_WEIGHT_SETS = 2  # rotated between steps so no weight byte survives in L2 from one step to the next
 # Traffic of the dominant kernel from the committed ncu capture (profiles/): DRAM bytes per algorithmic byte.
-NCU_TRAFFIC_RATIO = 1.04
+NCU_TRAFFIC_RATIO = 1.03
 CPU_BASELINE_SECONDS = 12.0  # wall time spent in the oracle for the cpu_baseline leg
 
 
