@@ -177,12 +177,16 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_stream_kernel(const __grid_co
     __shared__ float red[2][2][MAX_ROWS][CWARPS];  // [parity][matrix][row][consumer warp]
     __shared__ float ssq[CWARPS];
     __shared__ volatile uint32_t abort_flag;
+    // use number (ring index / nstages) the producer last armed each slot for: a parity wait can only tell adjacent
+    // uses of a slot apart, and a group may reach a slot that another group used last
+    __shared__ volatile uint32_t slot_use[MAX_STAGES];
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     if (tid == 0) {
         for (int s = 0; s < a.nstages; ++s) {
             mbar_init(&full[s], 1);
             mbar_init(&empty[s], 1);
+            slot_use[s] = 0xffffffffu;
         }
         abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -210,6 +214,8 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_stream_kernel(const __grid_co
             const SegDev& sg = a.seg[sidx];
             const uint32_t bytes = (uint32_t)rows * a.row_bytes;
             uint8_t* dst = ring + (size_t)s * a.stage_bytes;
+            slot_use[s] = (uint32_t)(i / a.nstages);
+            __threadfence_block();
             mbar_expect_tx(&full[s], GATE_UP ? 2u * bytes : bytes);
             bulk_load(dst, sg.W + (size_t)row0 * a.row_bytes, bytes, &full[s]);
             if (GATE_UP) bulk_load(dst + mat2_off, sg.W2 + (size_t)row0 * a.row_bytes, bytes, &full[s]);
@@ -332,7 +338,12 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_stream_kernel(const __grid_co
     for (int i = grp; i < my_groups; i += G, ++it) {
         const int s = i % a.nstages;
         bool ok = abort_flag == 0;
-        if (ok && !mbar_wait(&full[s], (uint32_t)((i / a.nstages) & 1))) {
+        if (ok) {  // the slot must be armed for THIS use before its parity means anything
+            const uint32_t use = (uint32_t)(i / a.nstages);
+            for (uint32_t spin = 0; slot_use[s] != use && spin < WAIT_LIMIT; ++spin) {}
+            ok = slot_use[s] == use;
+        }
+        if (!ok || !mbar_wait(&full[s], (uint32_t)((i / a.nstages) & 1))) {
             abort_flag = 1;
             if (lane == 0) atomicOr(a.status, 4u);
             ok = false;
