@@ -517,6 +517,43 @@ def main():
                            "algorithmic_bytes": b1, "achieved_gbs": b1 / (ms1 * 1e-3) / 1e9,
                            "frac_of_hbm_peak": b1 / (ms1 * 1e-3) / 1e9 / peak, "peak_kind": peak_kind}
 
+    # ---------------- batch sweep (BASELINE configs[4]): the same layer at 1 / 8 / 32 / 128 / 256 sequences with
+    # contexts U[128, 16384], one graph per weight set. Cache contents do not matter for the time (zero-filled at
+    # creation); lengths and positions are what the kernels read.
+    if rank == 0:
+        sweep = []
+        srng = np.random.default_rng(21)
+        for sb in (1, 8, 32, 128, 256):
+            slens = srng.integers(128, 16385, size=sb).astype(np.uint32)
+            skv = nat.kv_dense(16384 + 8, sb, KVH, HD)
+            sl = Layer(nat, skv, dw, sb)
+            sl.dx.upload(srng.standard_normal((sb, H), dtype=np.float32))
+            sl.dids.upload(np.arange(sb, dtype=np.uint32))
+            sl.dpos.upload(slens)
+            sl.dlens.upload(slens + 1)
+            for w in range(N_WEIGHT_SETS):
+                sl.enqueue(w)
+            nat.sync(1)
+            sg = [sl.capture(w) for w in range(N_WEIGHT_SETS)]
+            for i in range(4):
+                assert L.m40llm_cuda_graph_launch(ctx, sg[i % N_WEIGHT_SETS], 1) == 0
+            nat.sync(1)
+            sreps = 100 if sb <= 32 else 30
+            ev.start()
+            for i in range(sreps):
+                assert L.m40llm_cuda_graph_launch(ctx, sg[i % N_WEIGHT_SETS], 1) == 0
+            sms = ev.stop_ms() / sreps
+            sbytes = step_bytes(slens + 1)
+            sweep.append({"batch": sb, "context_sum": int(slens.sum()) + sb, "ms_per_step": sms,
+                          "tokens_per_s": sb / (sms * 1e-3), "algorithmic_bytes": sbytes,
+                          "frac_of_hbm_peak": sbytes / (sms * 1e-3) / 1e9 / peak})
+            for gx in sg:
+                L.m40llm_cuda_graph_destroy(gx)
+            L.m40llm_kvcache_destroy(skv)
+            for bname in ("dx", "dq", "datt", "dx1", "dx1n", "dhid", "dout", "dids", "dpos", "dlens"):
+                getattr(sl, bname).free()
+        extra["batch_sweep"] = sweep
+
     # ---------------- long-context compressed attention (BASELINE configs[3] shape), rank 0: Qwen2.5-3B heads,
     # context 32768 in the FP16-K / q4-V cache, 512-token ring, 64-token blocks, top 64. Four caches rotate.
     if rank == 0:
