@@ -334,7 +334,7 @@ def run_reference_arm(args, rank, world):
     line = {
         "impl": "reference", "metric": "decode_layer_tokens_per_s", "value": val, "unit": "tokens/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": per_tok * 1e3, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "f16 storage / q8_0 / f32 compute", "data": "synthetic",
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": workload_config(lens + 1, world),
         "cpu_baseline": {"value": val, "unit": "tokens/s", "cores": cores, "kind": "port",
                          "sample": cpu.describe() + ", one call per step, OpenMP over rows/heads"},
@@ -663,7 +663,7 @@ def main():
             "metric": "decode_layer_tokens_per_s", "value": world * B / (ms_step * 1e-3), "unit": "tokens/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": "f16 storage / q8_0 / f32 compute", "data": "synthetic",
+            "dtype": "f32", "data": "synthetic",
             "config": workload_config(att_lens, world),
             "step_algorithmic_bytes": sb, "step_achieved_gbs": sb / (ms_step * 1e-3) / 1e9,
             "step_frac_of_hbm_peak": sb / (ms_step * 1e-3) / 1e9 / peak,

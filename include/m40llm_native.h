@@ -424,6 +424,13 @@ int m40llm_kvcache_debug_read_old_token(M40llmCudaContext* ctx, M40llmKVCache* k
 /* Device error word of the context: bit 0 = a batched-attention row carried an out-of-range
  * sequence id or length and was skipped. Reading clears it. */
 int m40llm_context_take_device_status(M40llmCudaContext* ctx, uint32_t* out_status);
+/* Stream-ordered host <-> device copies on one of the context's streams (the reference only has the synchronous
+ * m40llm_memcpy_h2d / _d2h, cuda/kernels.cu). The host buffer must stay valid until the stream has passed the copy;
+ * with pinned memory the call returns at once. */
+int m40llm_memcpy_h2d_async(M40llmCudaContext* ctx, void* dst_device, const void* src_host, size_t bytes,
+                            uint32_t stream_kind);
+int m40llm_memcpy_d2h_async(M40llmCudaContext* ctx, void* dst_host, const void* src_device, size_t bytes,
+                            uint32_t stream_kind);
 /* Token embedding gather on the device: out[r][:] = f32(table[token_ids[r]][:]), table f16 [vocab][hidden]
  * (the reference gathers rows on the host and uploads them, src/infer/embeddings.rs:80-140). An id >= vocab yields a
  * zero row and raises bit 8 of the device status word. Decode stream. */

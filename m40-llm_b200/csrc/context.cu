@@ -170,6 +170,24 @@ int m40llm_memcpy_d2d_async(M40llmCudaContext* ctx, void* dst_device, const void
     return cudaMemcpyAsync(dst_device, src_device, bytes, cudaMemcpyDeviceToDevice, s) == cudaSuccess ? 0 : -2;
 }
 
+int m40llm_memcpy_h2d_async(M40llmCudaContext* ctx, void* dst_device, const void* src_host, size_t bytes,
+                            uint32_t stream_kind) {
+    if (!ctx || !dst_device || !src_host) return -1;
+    if (m40_ensure_device(ctx) != 0) return -3;
+    cudaStream_t s = m40_stream(ctx, stream_kind);
+    if (!s) return -4;
+    return cudaMemcpyAsync(dst_device, src_host, bytes, cudaMemcpyHostToDevice, s) == cudaSuccess ? 0 : -2;
+}
+
+int m40llm_memcpy_d2h_async(M40llmCudaContext* ctx, void* dst_host, const void* src_device, size_t bytes,
+                            uint32_t stream_kind) {
+    if (!ctx || !dst_host || !src_device) return -1;
+    if (m40_ensure_device(ctx) != 0) return -3;
+    cudaStream_t s = m40_stream(ctx, stream_kind);
+    if (!s) return -4;
+    return cudaMemcpyAsync(dst_host, src_device, bytes, cudaMemcpyDeviceToHost, s) == cudaSuccess ? 0 : -2;
+}
+
 int m40llm_validate_device_ptr(const void* ptr) {
     if (!ptr) return -1;
     cudaPointerAttributes attr;

@@ -39,36 +39,40 @@ long DecodeBatchPlan::output_offset_f32(uint64_t request_id, uint32_t q_heads, u
 
 CudaDecodeBatchPlan::~CudaDecodeBatchPlan() {
     if (ctx_) {
+        m40llm_stream_synchronize(ctx_, 1u);
         m40llm_device_free(ctx_, d_ids_);
-        m40llm_device_free(ctx_, d_lens_);
-        m40llm_device_free(ctx_, d_pos_);
     }
 }
 
+// One stream-ordered copy of [ids | lens | positions] onto the decode stream: the kernels that read the plan are
+// enqueued behind it on the same stream, so no host synchronisation is needed here.
 int CudaDecodeBatchPlan::upload(M40llmCudaContext* ctx, const DecodeBatchPlan& plan) {
     const uint32_t n = plan.batch_size();
     if (n > capacity_ || ctx != ctx_) {
         if (ctx_) {
+            m40llm_stream_synchronize(ctx_, 1u);
             m40llm_device_free(ctx_, d_ids_);
-            m40llm_device_free(ctx_, d_lens_);
-            m40llm_device_free(ctx_, d_pos_);
         }
         ctx_ = ctx;
         d_ids_ = d_lens_ = d_pos_ = nullptr;
         capacity_ = 0;
-        int rc;
-        if ((rc = m40llm_device_malloc(ctx, n * 4, (void**)&d_ids_)) != 0) return rc;
-        if ((rc = m40llm_device_malloc(ctx, n * 4, (void**)&d_lens_)) != 0) return rc;
-        if ((rc = m40llm_device_malloc(ctx, n * 4, (void**)&d_pos_)) != 0) return rc;
+        const int rc = m40llm_device_malloc(ctx, (size_t)3 * n * 4, (void**)&d_ids_);
+        if (rc != 0) return rc;
         capacity_ = n;
     }
+    d_lens_ = d_ids_ + capacity_;
+    d_pos_ = d_ids_ + 2 * (size_t)capacity_;
+    // the previous copy out of the staging vector must have left it before it is overwritten
+    int rc = m40llm_stream_synchronize(ctx, 1u);
+    if (rc != 0) return rc;
+    staging_.assign((size_t)3 * capacity_, 0u);
     const std::vector<uint32_t> ids = plan.sequence_ids(), lens = plan.sequence_lens();
-    std::vector<uint32_t> pos(n);
-    for (uint32_t i = 0; i < n; ++i) pos[i] = lens[i] - 1;
-    int rc;
-    if ((rc = m40llm_memcpy_h2d(ctx, d_ids_, ids.data(), n * 4)) != 0) return rc;
-    if ((rc = m40llm_memcpy_h2d(ctx, d_lens_, lens.data(), n * 4)) != 0) return rc;
-    if ((rc = m40llm_memcpy_h2d(ctx, d_pos_, pos.data(), n * 4)) != 0) return rc;
+    for (uint32_t i = 0; i < n; ++i) {
+        staging_[i] = ids[i];
+        staging_[capacity_ + i] = lens[i];
+        staging_[2 * (size_t)capacity_ + i] = lens[i] - 1;
+    }
+    if ((rc = m40llm_memcpy_h2d_async(ctx, d_ids_, staging_.data(), staging_.size() * 4, 1u)) != 0) return rc;
     batch_ = n;
     return 0;
 }

@@ -56,7 +56,8 @@ public:
 
 private:
     M40llmCudaContext* ctx_ = nullptr;
-    uint32_t *d_ids_ = nullptr, *d_lens_ = nullptr, *d_pos_ = nullptr;
+    uint32_t *d_ids_ = nullptr, *d_lens_ = nullptr, *d_pos_ = nullptr;  // three views of one device block
+    std::vector<uint32_t> staging_;  // [ids | lens | positions], alive until the stream has passed the copy
     uint32_t batch_ = 0, capacity_ = 0;
 };
 

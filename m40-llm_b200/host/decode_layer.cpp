@@ -113,10 +113,11 @@ int DecodeLayer::forward_host(M40llmKVCache* kv, const LayerWeights& w, const Kv
     int rc = host_plan_dev_.upload(ctx_, plan);
     if (rc != 0) return fail(rc, "plan_upload");
     const size_t bytes = (size_t)rows * cfg_.hidden * 4;
-    if ((rc = m40llm_memcpy_h2d(ctx_, d_xin_, x_host, bytes)) != 0) return fail(rc, "memcpy_h2d");
+    // everything rides the decode stream: activations in, the layer, the result out, then ONE synchronisation
+    if ((rc = m40llm_memcpy_h2d_async(ctx_, d_xin_, x_host, bytes, 1u)) != 0) return fail(rc, "memcpy_h2d");
     if ((rc = forward_device(kv, w, kvcfg, plan, host_plan_dev_, d_xin_, d_xout_, use_graph)) != 0) return rc;
+    if ((rc = m40llm_memcpy_d2h_async(ctx_, out_host, d_xout_, bytes, 1u)) != 0) return fail(rc, "memcpy_d2h");
     if ((rc = m40llm_stream_synchronize(ctx_, 1u)) != 0) return fail(rc, "stream_synchronize");
-    if ((rc = m40llm_memcpy_d2h(ctx_, out_host, d_xout_, bytes)) != 0) return fail(rc, "memcpy_d2h");
     return 0;
 }
 
