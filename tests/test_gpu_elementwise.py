@@ -137,3 +137,23 @@ def test_streams_events_graphs(nat):
     # out-of-scope entry points answer "unsupported", never a silent success
     assert L.m40llm_start_persistent_decode(ctx) == -100
     nat.free_all()
+
+
+def test_stream_ordered_copies(nat):
+    """The additive async host<->device copies are ordered with the kernels of their stream."""
+    import ctypes as C
+    x = np.arange(4096, dtype=np.float32)
+    y = np.full(4096, 2.0, np.float32)
+    out = np.zeros(4096, np.float32)
+    dx, dy, do = nat.buf(x.nbytes), nat.buf(y.nbytes), nat.buf(out.nbytes)
+    L = nat.lib
+    vp = lambda a: a.ctypes.data_as(C.c_void_p)
+    assert L.m40llm_memcpy_h2d_async(nat.ctx, dx.ptr, vp(x), x.nbytes, 1) == 0
+    assert L.m40llm_memcpy_h2d_async(nat.ctx, dy.ptr, vp(y), y.nbytes, 1) == 0
+    assert L.m40llm_residual_add_f32_async(nat.ctx, dx.ptr, dy.ptr, do.ptr, 4096) == 0
+    assert L.m40llm_memcpy_d2h_async(nat.ctx, vp(out), do.ptr, out.nbytes, 1) == 0
+    nat.sync(1)
+    assert np.array_equal(out, x + 2.0)
+    assert L.m40llm_memcpy_h2d_async(nat.ctx, None, vp(x), 4, 1) == -1
+    assert L.m40llm_memcpy_d2h_async(nat.ctx, vp(out), do.ptr, 4, 7) == -4
+    nat.free_all()
