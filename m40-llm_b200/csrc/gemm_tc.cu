@@ -93,11 +93,25 @@ __global__ void __launch_bounds__(192, 1) gemm_tc_f16_kernel(const __grid_consta
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    pdl_trigger();
 
     if (warp == 0) {
-        // ---------------- TMA producer
+        // ---------------- TMA producer. The weight tiles of the first ring pass do not depend on the previous kernel:
+        // they are requested before the dependency wait, the activation tiles after it.
         if (lane == 0) {
-            for (uint32_t i = 0; i < n_kb; ++i) {
+            const uint32_t pre = n_kb < a.stages ? n_kb : a.stages;
+            for (uint32_t i = 0; i < pre; ++i) {
+                mbar_expect_tx(&full[i], stage_bytes);
+                tma_load_2d(stage_base + i * stage_bytes, tmW, &full[i], (int)((kb0 + i) * BLOCK_K), (int)row0);
+            }
+            pdl_wait();
+            for (uint32_t i = 0; i < pre; ++i) {
+                unsigned char* st = stage_base + i * stage_bytes;
+                const int kx = (int)((kb0 + i) * BLOCK_K);
+                tma_load_2d(st + a_bytes, &tmXh, &full[i], kx, 0);
+                if (a.use_lo) tma_load_2d(st + a_bytes + b_bytes, &tmXl, &full[i], kx, 0);
+            }
+            for (uint32_t i = pre; i < n_kb; ++i) {
                 const uint32_t s = i % a.stages, round = i / a.stages;
                 if (round > 0 && !mbar_wait(&empty[s], (round - 1) & 1u)) { *abort_flag = 1; break; }
                 if (*abort_flag) break;
@@ -133,6 +147,7 @@ __global__ void __launch_bounds__(192, 1) gemm_tc_f16_kernel(const __grid_consta
     } else {
         // ---------------- epilogue: warps 2..5 own TMEM lanes 32*(warp % 4) .. +31
         const uint32_t lane_group = warp & 3u;
+        pdl_wait();  // the partials below reuse scratch that earlier kernels may still read
         bool ok = n_kb > 0;
         if (ok) {
             if (!mbar_wait(accum, 0)) { *abort_flag = 1; ok = false; }
@@ -172,6 +187,8 @@ __global__ void __launch_bounds__(192, 1) gemm_tc_f16_kernel(const __grid_consta
 // f32 activations -> f16 hi (+ lo) copies, [M][K] row-major.
 __global__ void split_activations_kernel(const float* __restrict__ x, __half* __restrict__ hi, __half* __restrict__ lo,
                                          size_t n) {
+    pdl_wait();
+    pdl_trigger();
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
         const float v = x[i];
@@ -186,6 +203,8 @@ __global__ void __launch_bounds__(256) norm_split_rows_kernel(const float* __res
                                                               int w_f32, float eps, __half* __restrict__ hi,
                                                               __half* __restrict__ lo, uint32_t K) {
     __shared__ float red[8];
+    pdl_wait();
+    pdl_trigger();
     const float* xr = x + (size_t)blockIdx.x * K;
     __half* hr = hi + (size_t)blockIdx.x * K;
     __half* lr = lo + (size_t)blockIdx.x * K;
@@ -231,6 +250,8 @@ struct EpiArgs {
 };
 
 __global__ void __launch_bounds__(256) gemm_tc_epilogue_kernel(EpiArgs e) {
+    pdl_wait();
+    pdl_trigger();
     const uint32_t p = blockIdx.z;
     const uint32_t n = blockIdx.x * 128u + (threadIdx.x & 127u);
     if (n >= e.N[p]) return;
@@ -290,12 +311,13 @@ int m40_split_activations(M40llmCudaContext* ctx, cudaStream_t s, const float* X
                           const M40GemvNorm* norm) {
     if (norm && norm->w) {
         if (K % 4 != 0 || (((uintptr_t)X) & 15u) != 0u) return -2;
-        norm_split_rows_kernel<<<(unsigned)M, 256, 0, s>>>(X, norm->w, norm->w_is_f32, norm->eps, hi, lo, (uint32_t)K);
+        m40_launch_dependent(norm_split_rows_kernel, dim3((unsigned)M), dim3(256), 0, s, X, norm->w, norm->w_is_f32, norm->eps,
+                             hi, lo, (uint32_t)K);
     } else {
         const size_t n = (size_t)M * K;
         size_t blocks = (n + 255) / 256;
         if (blocks > (size_t)ctx->sm_count * 8) blocks = (size_t)ctx->sm_count * 8;
-        split_activations_kernel<<<(unsigned)blocks, 256, 0, s>>>(X, hi, lo, n);
+        m40_launch_dependent(split_activations_kernel, dim3((unsigned)blocks), dim3(256), 0, s, X, hi, lo, n);
     }
     M40_COUNT_LAUNCH(ctx);
     return cudaGetLastError() == cudaSuccess ? 0 : -2;
@@ -373,7 +395,7 @@ int m40_gemm_tc_f16(M40llmCudaContext* ctx, cudaStream_t s, uint32_t stream_kind
         configured |= bit;
     }
     dim3 grid(tiles, ks);
-    gemm_tc_f16_kernel<<<grid, 192, smem, s>>>(mW[0], mW[1], mW[2], mXh, mXl, a);
+    m40_launch_dependent(gemm_tc_f16_kernel, grid, dim3(192), smem, s, mW[0], mW[1], mW[2], mXh, mXl, a);
     M40_COUNT_LAUNCH(ctx);
     if (cudaGetLastError() != cudaSuccess) return -2;
 
@@ -394,7 +416,7 @@ int m40_gemm_tc_f16(M40llmCudaContext* ctx, cudaStream_t s, uint32_t stream_kind
     e.k_splits = ks;
     e.mode = (uint32_t)mode;
     dim3 egrid((maxN + 127) / 128, (unsigned)(M + 7) / 8, mode == 1 ? 1u : (unsigned)problems);
-    gemm_tc_epilogue_kernel<<<egrid, 256, 0, s>>>(e);
+    m40_launch_dependent(gemm_tc_epilogue_kernel, egrid, dim3(256), 0, s, e);
     M40_COUNT_LAUNCH(ctx);
     return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }

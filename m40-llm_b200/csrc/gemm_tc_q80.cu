@@ -52,8 +52,9 @@ struct Q80Args {
 };
 
 __device__ __forceinline__ void span_of(const Q80Args& a, uint32_t cta, uint32_t* u0, uint32_t* u1) {
-    *u0 = (uint32_t)(((uint64_t)cta * a.units_total) / a.ctas);
-    *u1 = (uint32_t)(((uint64_t)(cta + 1) * a.units_total) / a.ctas);
+    // units_total * ctas < 2^32 is checked on the host: 32-bit divisions
+    *u0 = (cta * a.units_total) / a.ctas;
+    *u1 = ((cta + 1u) * a.units_total) / a.ctas;
 }
 
 struct Q80Smem {
@@ -209,9 +210,10 @@ __global__ void __launch_bounds__(CTA_THREADS, 1) gemm_tc_q80_kernel(const __gri
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    pdl_trigger();
 
     if (warp == 0) {
-        // ---------------- weight producer: raw Q8_0 stages, running up to RS units ahead of the workers
+        // ---------------- weight producer (weights never depend on the previous kernel: no dependency wait here): raw Q8_0 stages, running up to RS units ahead of the workers
         if (lane == 0) {
             bool ok = true;
             for (uint32_t i = 0; i < n_units && ok; ++i) {
@@ -232,6 +234,7 @@ __global__ void __launch_bounds__(CTA_THREADS, 1) gemm_tc_q80_kernel(const __gri
     } else if (warp == 2) {
         // ---------------- activation producer: hi and lo f16 copies of X for every 64-k sub-block
         if (lane == 0) {
+            pdl_wait();  // X was split by the previous kernel
             bool ok = true;
             for (uint32_t i = 0; i < n_units && ok; ++i) {
                 const uint32_t kb = (u0 + i) % a.units_per_tile;
@@ -290,6 +293,7 @@ __global__ void __launch_bounds__(CTA_THREADS, 1) gemm_tc_q80_kernel(const __gri
     } else {
         // ---------------- workers: warps 3..18; TMEM lane group = warp % 4, row quarter = (warp - 3) / 4
         Q80Smem sm = {s_raw, raw_full, raw_empty, a_full, a_empty, t_full, t_empty, abort_flag};
+        pdl_wait();  // the partials written at segment ends reuse scratch that earlier kernels may still read
         const uint32_t lane_group = warp & 3u;
         switch ((warp - 3u) >> 2) {
             case 0: q80_worker<M_PAD, 0>(a, sm, tmem_base, u0, u1, lane_group, lane); break;
@@ -322,12 +326,12 @@ struct Q80EpiArgs {
 __device__ __forceinline__ void q80_tile_ctas(const Q80EpiArgs& e, uint32_t tile, uint32_t* first, uint32_t* count,
                                               uint32_t* seg_first) {
     const uint32_t t0 = tile * e.units_per_tile, t1 = t0 + e.units_per_tile;
-    uint32_t c = (uint32_t)(((uint64_t)t0 * e.ctas) / e.units_total);
-    while ((uint32_t)(((uint64_t)(c + 1) * e.units_total) / e.ctas) <= t0) ++c;
+    uint32_t c = (t0 * e.ctas) / e.units_total;
+    while (((c + 1u) * e.units_total) / e.ctas <= t0) ++c;
     *first = c;
-    *seg_first = tile - (uint32_t)(((uint64_t)c * e.units_total) / e.ctas) / e.units_per_tile;
+    *seg_first = tile - ((c * e.units_total) / e.ctas) / e.units_per_tile;
     uint32_t n = 0;
-    while (c < e.ctas && (uint32_t)(((uint64_t)c * e.units_total) / e.ctas) < t1) {
+    while (c < e.ctas && (c * e.units_total) / e.ctas < t1) {
         ++c;
         ++n;
     }
@@ -338,6 +342,8 @@ __device__ __forceinline__ void q80_tile_ctas(const Q80EpiArgs& e, uint32_t tile
 // 8 activation rows.
 __global__ void __launch_bounds__(256) gemm_tc_q80_epilogue_kernel(Q80EpiArgs e) {
     __shared__ uint32_t first[2], count[2], seg0[2];
+    pdl_wait();
+    pdl_trigger();
     const uint32_t p = blockIdx.z, t = blockIdx.x, tr = threadIdx.x & 127u;
     const uint32_t n = t * BLOCK_N + tr;
     if (t * BLOCK_N >= e.N[p]) return;
@@ -419,7 +425,7 @@ int launch_q80(M40llmCudaContext* ctx, cudaStream_t s, const CUtensorMap* mW, co
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return -2;
         configured |= bit;
     }
-    kern<<<a.ctas, CTA_THREADS, smem, s>>>(mW[0], mW[1], mW[2], mXh, mXl, a);
+    m40_launch_dependent(kern, dim3(a.ctas), dim3(CTA_THREADS), smem, s, mW[0], mW[1], mW[2], mXh, mXl, a);
     M40_COUNT_LAUNCH(ctx);
     return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
@@ -451,6 +457,7 @@ int m40_gemm_tc_q80(M40llmCudaContext* ctx, cudaStream_t s, uint32_t stream_kind
     a.units_per_tile = (uint32_t)K / UNIT_K;
     a.units_total = tiles * a.units_per_tile;
     a.ctas = (uint32_t)ctx->sm_count < a.units_total ? (uint32_t)ctx->sm_count : a.units_total;
+    if ((uint64_t)(a.units_total + 1) * (a.ctas + 1) >= (1ull << 32)) return -2;  // span arithmetic is 32-bit
     const uint32_t upc = (a.units_total + a.ctas - 1) / a.ctas;
     a.seg_max = upc / a.units_per_tile + 2;
 
@@ -497,7 +504,7 @@ int m40_gemm_tc_q80(M40llmCudaContext* ctx, cudaStream_t s, uint32_t stream_kind
     e.mode = (uint32_t)mode;
     e.problems = (uint32_t)problems;
     dim3 egrid((maxN + BLOCK_N - 1) / BLOCK_N, (unsigned)(M + 7) / 8, mode == 1 ? 1u : (unsigned)problems);
-    gemm_tc_q80_epilogue_kernel<<<egrid, 256, 0, s>>>(e);
+    m40_launch_dependent(gemm_tc_q80_epilogue_kernel, egrid, dim3(256), 0, s, e);
     M40_COUNT_LAUNCH(ctx);
     return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
