@@ -40,7 +40,9 @@ constexpr uint32_t A_COLS = BLOCK_K;                   // TMEM columns of one co
 constexpr uint32_t TMEM_COLS = 512;
 __host__ __device__ constexpr uint32_t acc_cols(int m_pad) { return 2u * (uint32_t)m_pad; }  // [hi.Xh + lo.Xh | hi.Xl]
 __host__ __device__ constexpr uint32_t a_stages(int m_pad) { return (TMEM_COLS - TB * acc_cols(m_pad)) / A_COLS; }  // 7, 6, 4
-__host__ __device__ constexpr uint32_t b_slots(int m_pad) { return a_stages(m_pad); }  // activation tiles ride the operand ring
+// Activation tiles: their bytes are counted on the operand stage's barrier, but they live in a ring of their own that
+// is a few slots deeper, so that a tile is requested when its stage's previous use has been ISSUED, not completed.
+__host__ __device__ constexpr uint32_t b_slots(int m_pad) { return a_stages(m_pad) + (m_pad <= 32 ? 3u : 0u); }
 
 struct Q80Args {
     float* partial;  // [ctas][seg_max][M][128]
@@ -185,7 +187,8 @@ __global__ void __launch_bounds__(CTA_THREADS, 1) gemm_tc_q80_kernel(const __gri
     uint64_t* raw_empty = raw_full + RS;
     uint64_t* a_full = raw_empty + RS;
     uint64_t* a_empty = a_full + AST;
-    uint64_t* t_full = a_empty + AST;
+    uint64_t* b_empty = a_empty + AST;
+    uint64_t* t_full = b_empty + BS;
     uint64_t* t_empty = t_full + TB;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(t_empty + TB);
     volatile uint32_t* abort_flag = tmem_slot + 1;
@@ -201,6 +204,7 @@ __global__ void __launch_bounds__(CTA_THREADS, 1) gemm_tc_q80_kernel(const __gri
         // a stage is full when its 4 worker warps have arrived AND the activation tile's bytes have landed (the
         // activation producer's expect_tx is the fifth arrival); one commit frees it for both
         for (uint32_t i = 0; i < AST; ++i) { mbar_init(&a_full[i], 5); mbar_init(&a_empty[i], 1); }
+        for (uint32_t i = 0; i < BS; ++i) mbar_init(&b_empty[i], 1);
         for (uint32_t i = 0; i < TB; ++i) { mbar_init(&t_full[i], 1); mbar_init(&t_empty[i], WORKER_WARPS); }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -239,13 +243,16 @@ __global__ void __launch_bounds__(CTA_THREADS, 1) gemm_tc_q80_kernel(const __gri
             for (uint32_t i = 0; i < n_units && ok; ++i) {
                 const uint32_t kb = (u0 + i) % a.units_per_tile;
                 for (uint32_t sub = 0; sub < 4; ++sub) {
-                    const uint32_t u = i * 4 + sub, bs = u % AST;
-                    if (u >= AST && !mbar_wait(&a_empty[bs], ((u / AST) - 1) & 1u)) { ok = false; break; }
+                    const uint32_t u = i * 4 + sub, as = u % AST, bs = u % BS;
+                    // the slot must be free (the MMAs of sub-block u - BS have completed) and the stage barrier must
+                    // have finished its previous use (sub-block u - AST was handed to the MMA issuer)
+                    if (u >= BS && !mbar_wait(&b_empty[bs], ((u / BS) - 1) & 1u)) { ok = false; break; }
+                    if (u >= AST && !mbar_wait(&a_full[as], ((u / AST) - 1) & 1u)) { ok = false; break; }
                     if (*abort_flag) { ok = false; break; }
-                    mbar_expect_tx(&a_full[bs], 2 * B_BYTES);
+                    mbar_expect_tx(&a_full[as], 2 * B_BYTES);
                     const int kx = (int)(kb * UNIT_K + sub * BLOCK_K);
-                    tma_load_2d(s_b + bs * 2 * B_BYTES, &tmXh, &a_full[bs], kx, 0);
-                    tma_load_2d(s_b + bs * 2 * B_BYTES + B_BYTES, &tmXl, &a_full[bs], kx, 0);
+                    tma_load_2d(s_b + bs * 2 * B_BYTES, &tmXh, &a_full[as], kx, 0);
+                    tma_load_2d(s_b + bs * 2 * B_BYTES + B_BYTES, &tmXl, &a_full[as], kx, 0);
                 }
             }
             if (!ok) *abort_flag = 1;
@@ -258,7 +265,7 @@ __global__ void __launch_bounds__(CTA_THREADS, 1) gemm_tc_q80_kernel(const __gri
             const uint32_t idesc2 = make_idesc(2 * M_PAD), idesc1 = make_idesc(M_PAD);
             bool ok = true;
             // the loop below is this kernel's critical path: stage index and phase are carried, not recomputed
-            uint32_t pos = u0, seg = 0, as = 0, ph = 0;
+            uint32_t pos = u0, seg = 0, as = 0, ph = 0, bs = 0;
             const uint32_t a_tmem0 = tmem_base + A_COL0, b_smem0 = smem_u32(s_b);
             while (pos < u1 && ok) {
                 const uint32_t kb_begin = pos % a.units_per_tile;
@@ -273,7 +280,7 @@ __global__ void __launch_bounds__(CTA_THREADS, 1) gemm_tc_q80_kernel(const __gri
                     if (!mbar_wait(&a_full[as], ph)) { ok = false; break; }
                     tc_fence_after();
                     const uint32_t ta = a_tmem0 + as * A_COLS;  // hi columns [0,32), lo columns [32,64)
-                    const uint32_t sb = b_smem0 + as * 2 * B_BYTES;
+                    const uint32_t sb = b_smem0 + bs * 2 * B_BYTES;
 #pragma unroll
                     for (uint32_t kk = 0; kk < BLOCK_K / UMMA_K; ++kk) {
                         const uint64_t b_x = make_desc_sw128(sb + kk * UMMA_K * 2);  // rows [0, M_PAD) = Xh, [M_PAD, 2 M_PAD) = Xl
@@ -281,8 +288,10 @@ __global__ void __launch_bounds__(CTA_THREADS, 1) gemm_tc_q80_kernel(const __gri
                         umma_f16_ts(d_tmem, a_hi, b_x, idesc2, (j | kk) != 0u);
                         umma_f16_ts(d_tmem, a_lo, b_x, idesc1, 1u);
                     }
-                    umma_commit(&a_empty[as]);  // frees the operand stage and its activation tile
+                    umma_commit(&a_empty[as]);  // frees the operand stage for the workers
+                    umma_commit(&b_empty[bs]);  // and the activation slot
                     if (++as == AST) as = 0, ph ^= 1u;
+                    if (++bs == BS) bs = 0;
                 }
                 if (ok) umma_commit(&t_full[tb]);
                 pos += kb_end - kb_begin;
