@@ -256,21 +256,43 @@ __global__ void __launch_bounds__(256) gemm_tc_epilogue_kernel(EpiArgs e) {
     const uint32_t n = blockIdx.x * 128u + (threadIdx.x & 127u);
     if (n >= e.N[p]) return;
     const size_t split_stride = (size_t)e.M * e.n_total;
-    const uint32_t m_end = min(e.M, (blockIdx.y + 1u) * 8u);
-    for (uint32_t m = blockIdx.y * 8u + (threadIdx.x >> 7); m < m_end; m += 2u) {
-        const size_t idx = (size_t)m * e.n_total + (size_t)e.tile_begin[p] * BLOCK_N + n;
-        float acc = 0.0f;
-        for (uint32_t s = 0; s < e.k_splits; ++s) acc += e.partial[s * split_stride + idx];
+    // a thread owns 4 activation rows; all partial loads of a chunk of splits are issued before any is used (the
+    // additions keep the split order, so the result does not depend on timing)
+    const uint32_t m0 = blockIdx.y * 8u + (threadIdx.x >> 7);
+    float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f}, up[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    const size_t col = (size_t)e.tile_begin[p] * BLOCK_N + n;
+    const size_t col_u = (size_t)e.tile_begin[1] * BLOCK_N + n;
+    for (uint32_t sbase = 0; sbase < e.k_splits; sbase += 4u) {
+        float v[4][4], w[4][4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const uint32_t m = m0 + 2u * i, sp = sbase + k;
+                const bool live = m < e.M && sp < e.k_splits;
+                v[i][k] = live ? e.partial[sp * split_stride + (size_t)m * e.n_total + col] : 0.0f;
+                w[i][k] = (live && e.mode == 1) ? e.partial[sp * split_stride + (size_t)m * e.n_total + col_u] : 0.0f;
+            }
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                acc[i] += v[i][k];
+                up[i] += w[i][k];
+            }
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const uint32_t m = m0 + 2u * i;
+        if (m >= e.M) continue;
+        float r = acc[i];
         if (e.mode == 1) {
-            const size_t idx_u = (size_t)m * e.n_total + (size_t)e.tile_begin[1] * BLOCK_N + n;
-            float up = 0.0f;
-            for (uint32_t s = 0; s < e.k_splits; ++s) up += e.partial[s * split_stride + idx_u];
-            e.out[0][(size_t)m * e.N[0] + n] = (acc / (1.0f + expf(-acc))) * up;
+            e.out[0][(size_t)m * e.N[0] + n] = (r / (1.0f + expf(-r))) * up[i];
             continue;
         }
-        if (e.bias[p]) acc += e.bias[p][n];
-        if (e.residual[p]) acc += e.residual[p][(size_t)m * e.N[p] + n];
-        e.out[p][(size_t)m * e.N[p] + n] = acc;
+        if (e.bias[p]) r += e.bias[p][n];
+        if (e.residual[p]) r += e.residual[p][(size_t)m * e.N[p] + n];
+        e.out[p][(size_t)m * e.N[p] + n] = r;
     }
 }
 

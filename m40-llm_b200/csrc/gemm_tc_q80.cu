@@ -360,24 +360,41 @@ __global__ void __launch_bounds__(256) gemm_tc_q80_epilogue_kernel(Q80EpiArgs e)
     if (threadIdx.x == 32 && e.mode == 1) q80_tile_ctas(e, e.tile_begin[1] + t, &first[1], &count[1], &seg0[1]);
     __syncthreads();
     if (n >= e.N[p]) return;
-    const uint32_t m_end = min(e.M, (blockIdx.y + 1u) * 8u);
-    for (uint32_t m = blockIdx.y * 8u + (threadIdx.x >> 7); m < m_end; m += 2u) {
-        auto tile_sum = [&](int w) {
-            float acc = 0.0f;
-            for (uint32_t i = 0; i < count[w]; ++i) {
-                const size_t slot = (size_t)(first[w] + i) * e.seg_max + (i == 0 ? seg0[w] : 0u);
-                acc += e.partial[(slot * e.M + m) * BLOCK_N + tr];
-            }
-            return acc;
-        };
-        float acc = tile_sum(0);
+    // a thread owns 4 activation rows; every partial of a tile is loaded before any is added (fixed order)
+    const uint32_t m0 = blockIdx.y * 8u + (threadIdx.x >> 7);
+    float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f}, up[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    const int nw = e.mode == 1 ? 2 : 1;
+    for (int w = 0; w < nw; ++w) {
+        for (uint32_t i0 = 0; i0 < count[w]; i0 += 4u) {
+            float v[4][4];
+#pragma unroll
+            for (int r = 0; r < 4; ++r)
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const uint32_t m = m0 + 2u * r, i = i0 + k;
+                    const size_t slot = (size_t)(first[w] + i) * e.seg_max + (i == 0 ? seg0[w] : 0u);
+                    v[r][k] = (m < e.M && i < count[w]) ? e.partial[(slot * e.M + m) * BLOCK_N + tr] : 0.0f;
+                }
+#pragma unroll
+            for (int r = 0; r < 4; ++r)
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    if (w == 0) acc[r] += v[r][k];
+                    else up[r] += v[r][k];
+                }
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+        const uint32_t m = m0 + 2u * r;
+        if (m >= e.M) continue;
+        float a0 = acc[r];
         if (e.mode == 1) {
-            const float up = tile_sum(1);
-            e.out[0][(size_t)m * e.N[0] + n] = (acc / (1.0f + expf(-acc))) * up;
+            e.out[0][(size_t)m * e.N[0] + n] = (a0 / (1.0f + expf(-a0))) * up[r];
             continue;
         }
-        if (e.residual[p]) acc += e.residual[p][(size_t)m * e.N[p] + n];
-        e.out[p][(size_t)m * e.N[p] + n] = acc;
+        if (e.residual[p]) a0 += e.residual[p][(size_t)m * e.N[p] + n];
+        e.out[p][(size_t)m * e.N[p] + n] = a0;
     }
 }
 
