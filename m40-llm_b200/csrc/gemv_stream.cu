@@ -3,9 +3,11 @@
 // At one activation row every weight byte is read once and nothing is reused, so the only thing that matters is
 // keeping HBM busy. The kernel is persistent (one CTA per SM) and warp-specialised:
 //
-//   * a producer thread streams groups of whole weight rows into a shared-memory ring with 1-D bulk async copies
-//     (cp.async.bulk ... mbarrier::complete_tx), 8-36 KB per stage and up to ~200 KB in flight per SM,
-//     independent of how fast the consumers issue instructions;
+//   * two producer threads (one per producer warp, alternating stages: arming a stage costs one thread more than a
+//     stage's share of the HBM time) stream groups of whole weight rows into a shared-memory ring with 1-D bulk async
+//     copies (cp.async.bulk ... mbarrier::complete_tx), 8-36 KB per stage and up to ~200 KB in flight per SM,
+//     independent of how fast the consumers issue instructions. Every CTA gets the same number of stages: the
+//     group count is made a multiple of the grid by cutting the tail of the last matrix into groups one row smaller;
 //   * sixteen consumer warps form groups of `cw` warps; a group owns every G-th stage, so the groups run
 //     decoupled from one another (no CTA-wide barrier in the steady state). A thread owns fixed column pieces of
 //     every row, so its slice of the activation vector stays in registers for the whole launch:
@@ -15,6 +17,7 @@
 //         and one scale per 32-block (x = s/128 * (128 a + b + c/128), error <= 2^-22 of the block maximum, i.e.
 //         f32 rounding level), then one f32 multiply-add per block with d * s. The digits are made once per CTA
 //         (cooperatively, into shared memory) with add-magic rounding, so no conversion-unit instruction is used;
+//         once every consumer holds its slice in registers that shared memory is handed to the ring's last slots;
 //   * row sums meet by warp shuffle, then across the warps of the group through shared memory in a fixed
 //     order (no atomics: results are deterministic).
 // Up to three matrices that share x go in one launch (Wq | Wk | Wv), gate and up are streamed side by side with
@@ -33,8 +36,9 @@ using namespace tc;
 
 constexpr int CWARPS = 16;                // consumer warps
 constexpr int CONSUMERS = CWARPS * 32;
-constexpr int THREADS = CONSUMERS + 32;   // + the producer warp
-constexpr int MAX_SEGS = 3;
+constexpr int PWARPS = 2;                 // producer warps (one elected thread each)
+constexpr int THREADS = CONSUMERS + 32 * PWARPS;
+constexpr int MAX_SEGS = 4;  // three matrices + the tail part of the last one
 constexpr int MAX_STAGES = 12;
 constexpr int MAX_ROWS = 16;              // rows of one matrix per stage
 constexpr uint32_t STAGE_MAX = 36u * 1024u;
@@ -48,6 +52,7 @@ struct SegDev {
     const float* residual;
     int N;
     int group0;  // id of this matrix's first row group
+    int R;       // rows per group of this matrix (the last group may hold fewer)
 };
 
 struct GemvArgs {
@@ -60,6 +65,7 @@ struct GemvArgs {
     int norm_f32;
     int nseg, K, pieces, cw, R, nstages, total_groups;
     uint32_t row_bytes, stage_bytes, xq_off;
+    int first_late;  // ring slots from this one on share their bytes with the activation digits
 };
 
 __device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
@@ -77,11 +83,11 @@ __device__ __forceinline__ void locate_group(const GemvArgs& a, int g, int* seg,
 #pragma unroll
     for (int i = 1; i < MAX_SEGS; ++i)
         if (i < a.nseg && g >= a.seg[i].group0) s = i;
-    const int r0 = (g - a.seg[s].group0) * a.R;
+    const int r0 = (g - a.seg[s].group0) * a.seg[s].R;
     const int left = a.seg[s].N - r0;
     *seg = s;
     *row0 = r0;
-    *rows = left < a.R ? left : a.R;
+    *rows = left < a.seg[s].R ? left : a.seg[s].R;
 }
 
 __device__ __forceinline__ float dot8(const uint4& w, const float* x) {
@@ -102,31 +108,30 @@ struct Q80X {
     float s[2];
 };
 
-// One 32-value block -> 3 x 8 digit words + scale, with add-magic rounding (1.5 * 2^23: the rounded integer sits in
-// the low mantissa bits as two's complement, ties to even like rintf).
-__device__ __forceinline__ void q80_quantise_block(const float* v, uint32_t* da, uint32_t* db, uint32_t* dc, float* s) {
+// Four values -> one word of each of the three digit planes. v * (127 * 2^14 / block maximum) + 1.5 * 2^23 leaves the
+// rounded 22-bit integer q (ties to even, like rintf) in the low mantissa bits as two's complement; its base-128
+// digits are q = 16384 a + 128 b + c with a = q >> 14 in [-127, 127] (floor) and b, c in [0, 127]: shifts and byte
+// picks, no conversion instruction.
+__device__ __forceinline__ void q80_quantise_unit(const float4& v, float inv14, uint32_t* pa, uint32_t* pb, uint32_t* pc) {
     const float MAGIC = 12582912.0f;
-    float mx = 0.0f;
-#pragma unroll
-    for (int i = 0; i < 32; ++i) mx = fmaxf(mx, fabsf(v[i]));
-    const float inv = mx > 0.0f ? 127.0f / mx : 0.0f;
-    *s = mx * (1.0f / (127.0f * 128.0f));
-#pragma unroll
-    for (int w = 0; w < 8; ++w) {
-        uint32_t pa = 0, pb = 0, pc = 0;
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-            const float t = v[w * 4 + e] * inv;
-            const float ma = t + MAGIC;
-            const float r1 = (t - (ma - MAGIC)) * 128.0f;
-            const float mb = r1 + MAGIC;
-            const float mc = (r1 - (mb - MAGIC)) * 128.0f + MAGIC;
-            pa |= (__float_as_uint(ma) & 0xffu) << (8 * e);
-            pb |= (__float_as_uint(mb) & 0xffu) << (8 * e);
-            pc |= (__float_as_uint(mc) & 0xffu) << (8 * e);
-        }
-        da[w] = pa, db[w] = pb, dc[w] = pc;
-    }
+    const uint32_t m0 = __float_as_uint(fmaf(v.x, inv14, MAGIC)), m1 = __float_as_uint(fmaf(v.y, inv14, MAGIC));
+    const uint32_t m2 = __float_as_uint(fmaf(v.z, inv14, MAGIC)), m3 = __float_as_uint(fmaf(v.w, inv14, MAGIC));
+    // low byte of each of the four words -> one packed word
+    auto pack = [](uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+        return __byte_perm(__byte_perm(a, b, 0x0040), __byte_perm(c, d, 0x0040), 0x5410);
+    };
+    *pc = pack(m0, m1, m2, m3) & 0x7f7f7f7fu;
+    *pb = pack(m0 >> 7, m1 >> 7, m2 >> 7, m3 >> 7) & 0x7f7f7f7fu;
+    *pa = pack(m0 >> 14, m1 >> 14, m2 >> 14, m3 >> 14);
+}
+
+// RMSNorm weights k .. k+3 as f32 (f32 or f16 storage, 16- resp. 8-byte aligned: k is a multiple of 4).
+__device__ __forceinline__ float4 load_norm4(const void* w, int is_f32, int k) {
+    if (is_f32) return *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(w) + k);
+    const uint2 r = *reinterpret_cast<const uint2*>(reinterpret_cast<const __half*>(w) + k);
+    const float2 lo = __half22float2(*reinterpret_cast<const __half2*>(&r.x));
+    const float2 hi = __half22float2(*reinterpret_cast<const __half2*>(&r.y));
+    return make_float4(lo.x, lo.y, hi.x, hi.y);
 }
 
 // x . (two raw Q8_0 blocks at a 4-byte aligned shared-memory address).
@@ -173,7 +178,7 @@ __device__ __forceinline__ void store_row(const SegDev& sg, int n, float v, floa
 template <int FMT, int GATE_UP, int CPT>
 __global__ void __launch_bounds__(THREADS, 1) gemv_stream_kernel(const __grid_constant__ GemvArgs a) {
     extern __shared__ __align__(128) uint8_t ring[];
-    __shared__ uint64_t full[MAX_STAGES], empty[MAX_STAGES];
+    __shared__ uint64_t full[MAX_STAGES], empty[MAX_STAGES], xq_done;
     __shared__ float red[2][2][MAX_ROWS][CWARPS];  // [parity][matrix][row][consumer warp]
     __shared__ float ssq[CWARPS];
     __shared__ volatile uint32_t abort_flag;
@@ -188,6 +193,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_stream_kernel(const __grid_co
             mbar_init(&empty[s], 1);
             slot_use[s] = 0xffffffffu;
         }
+        mbar_init(&xq_done, CWARPS);
         abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -197,13 +203,26 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_stream_kernel(const __grid_co
                               ? (a.total_groups - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
     const uint32_t mat2_off = (uint32_t)a.R * a.row_bytes;
 
-    if (warp == CWARPS) {
-        // ------------------------------------------------------------ producer
+    if (warp >= CWARPS) {
+        // ------------------------------------------------------------ producers
+        // Arming a stage (barrier transaction count + the bulk copies) costs one thread several hundred cycles, more
+        // than a stage's share of the HBM time, so the stages are dealt to PWARPS threads.
         if (lane != 0) return;
-        int issued = 0;
-        for (int i = 0; i < my_groups; ++i) {
-            const int s = i % a.nstages;
-            if (i >= a.nstages && !mbar_wait(&empty[s], (uint32_t)((i / a.nstages) & 1) ^ 1u)) {
+        const int pw = warp - CWARPS;
+        int issued = pw;  // first stage of this thread not yet issued
+        int s = pw;       // ring slot and use number of stage i, carried (no division in this loop)
+        uint32_t use = 0;
+        for (int i = pw; i < my_groups; i += PWARPS) {
+            bool ready = true;
+            if (use > 0) {
+                // the slot's previous use may have been armed by the other producer thread: only once that has
+                // happened does the parity of the release barrier mean the release of THAT use
+                for (uint32_t spin = 0; slot_use[s] != use - 1u && spin < WAIT_LIMIT; ++spin) {}
+                ready = slot_use[s] == use - 1u && mbar_wait(&empty[s], (use & 1u) ^ 1u);
+            } else if (s >= a.first_late) {
+                ready = mbar_wait(&xq_done, 0u);  // the consumers have taken their digits out of these bytes
+            }
+            if (!ready) {
                 abort_flag = 1;
                 atomicOr(a.status, 4u);
                 break;
@@ -214,17 +233,22 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_stream_kernel(const __grid_co
             const SegDev& sg = a.seg[sidx];
             const uint32_t bytes = (uint32_t)rows * a.row_bytes;
             uint8_t* dst = ring + (size_t)s * a.stage_bytes;
-            slot_use[s] = (uint32_t)(i / a.nstages);
-            __threadfence_block();
+            // No fence between the two: once the consumers have released the previous use (waited for above) the
+            // barrier is in this use's phase, so a consumer that sees the new use number early merely waits.
+            slot_use[s] = use;
             mbar_expect_tx(&full[s], GATE_UP ? 2u * bytes : bytes);
             bulk_load(dst, sg.W + (size_t)row0 * a.row_bytes, bytes, &full[s]);
             if (GATE_UP) bulk_load(dst + mat2_off, sg.W2 + (size_t)row0 * a.row_bytes, bytes, &full[s]);
-            issued = i + 1;
+            issued = i + PWARPS;
+            s += PWARPS;
+            if (s >= a.nstages) s -= a.nstages, ++use;
         }
         if (abort_flag) {
-            // the consumers have stopped: wait (bounded) for the copies still in flight before the CTA goes away
-            const int first = issued > a.nstages ? issued - a.nstages : 0;
-            for (int i = first; i < issued; ++i) mbar_wait(&full[i % a.nstages], (uint32_t)((i / a.nstages) & 1));
+            // the consumers have stopped: wait (bounded) for this thread's copies still in flight before the CTA
+            // goes away
+            int first = issued - a.nstages;
+            if (first < pw) first = pw;
+            for (int i = first; i < issued; i += PWARPS) mbar_wait(&full[i % a.nstages], (uint32_t)((i / a.nstages) & 1));
         }
         return;
     }
@@ -236,59 +260,64 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_stream_kernel(const __grid_co
     const int grp = warp / cw, cwi = warp % cw;
     const int c = cwi * 32 + lane, cols = cw * 32;
 
-    float scale = 1.0f;
-    if (a.norm_w) {
-        float ss = 0.0f;
-        for (int k = tid * 4; k < a.K; k += CONSUMERS * 4) {
-            const float4 v = *reinterpret_cast<const float4*>(a.x + k);
-            ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
-        }
-        ss = warp_sum(ss);
-        if (lane == 0) ssq[warp] = ss;
-        consumer_barrier();
-        float tot = 0.0f;
-#pragma unroll
-        for (int i = 0; i < CWARPS; ++i) tot += ssq[i];
-        scale = rsqrtf(tot / (float)a.K + a.eps);
-    }
-
     float xr[FMT == M40_GEMV_Q80 ? 1 : CPT][8];
     Q80X xq;
+    float scale = 1.0f;
     if (FMT == M40_GEMV_Q80) {
-        // digits of the whole row, once per CTA: thread t takes 32-blocks t, t + 512, ...
-        uint32_t* dig = reinterpret_cast<uint32_t*>(ring + a.xq_off);   // [3][K/4] words
-        float* xs = reinterpret_cast<float*>(dig + 3 * (a.K / 4));      // [K/32]
-        for (int blk = tid; blk < a.K / 32; blk += CONSUMERS) {
-            float v[32];
-            const int k0 = blk * 32;
+        // Digits of the whole row, once per CTA. A thread takes 4-value units tid, tid + 512, ...: coalesced 16-byte
+        // loads, one word per digit plane per unit, and the eight units of a 32-block sit in eight adjacent lanes.
+        // Shared layout: [plane][word quad i4][piece][4 words], rows padded by 8 words, so that both these stores
+        // and the 16-byte reads of a thread's own piece below are free of bank conflicts.
+        uint32_t* dig = reinterpret_cast<uint32_t*>(ring + a.xq_off);
+        const int prow = a.pieces * 4 + 8;
+        float* xs = reinterpret_cast<float*>(dig + 12 * prow);  // [K/32]
+        const int units = a.K / 4;
+        constexpr int UR = 8;  // units per thread and round; with a norm the host admits one round only
+        for (int u0 = 0; u0 < units; u0 += CONSUMERS * UR) {
+            float4 xv[UR], wv[UR];
 #pragma unroll
-            for (int i = 0; i < 32; i += 4) {
-                const float4 t = *reinterpret_cast<const float4*>(a.x + k0 + i);
-                v[i] = t.x, v[i + 1] = t.y, v[i + 2] = t.z, v[i + 3] = t.w;
+            for (int p = 0; p < UR; ++p) {
+                const int u = u0 + p * CONSUMERS + tid;
+                xv[p] = u < units ? *reinterpret_cast<const float4*>(a.x + 4 * u) : make_float4(0.f, 0.f, 0.f, 0.f);
+                if (a.norm_w) wv[p] = u < units ? load_norm4(a.norm_w, a.norm_f32, 4 * u) : make_float4(0.f, 0.f, 0.f, 0.f);
             }
             if (a.norm_w) {
+                float ss = 0.0f;
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    const float w = a.norm_f32 ? reinterpret_cast<const float*>(a.norm_w)[k0 + i]
-                                               : __half2float(reinterpret_cast<const __half*>(a.norm_w)[k0 + i]);
-                    v[i] = v[i] * scale * w;
+                for (int p = 0; p < UR; ++p)
+                    ss += xv[p].x * xv[p].x + xv[p].y * xv[p].y + xv[p].z * xv[p].z + xv[p].w * xv[p].w;
+                ss = warp_sum(ss);
+                if (lane == 0) ssq[warp] = ss;
+                consumer_barrier();
+                float tot = 0.0f;
+#pragma unroll
+                for (int i = 0; i < CWARPS; ++i) tot += ssq[i];
+                scale = rsqrtf(tot / (float)a.K + a.eps);
+            }
+#pragma unroll
+            for (int p = 0; p < UR; ++p) {
+                const int u = u0 + p * CONSUMERS + tid;
+                if (u0 + p * CONSUMERS + warp * 32 >= units) break;  // whole warps: units is a multiple of 64
+                float4 v = xv[p];
+                if (a.norm_w) {
+                    v.x = v.x * scale * wv[p].x, v.y = v.y * scale * wv[p].y;
+                    v.z = v.z * scale * wv[p].z, v.w = v.w * scale * wv[p].w;
+                    if (a.xn_out && blockIdx.x == 0 && u < units) *reinterpret_cast<float4*>(a.xn_out + 4 * u) = v;
                 }
-                if (a.xn_out && blockIdx.x == 0) {
-#pragma unroll
-                    for (int i = 0; i < 32; i += 4)
-                        *reinterpret_cast<float4*>(a.xn_out + k0 + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+                float mx = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
+                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+                const float inv14 = mx > 0.0f ? (127.0f * 16384.0f) / mx : 0.0f;
+                uint32_t da, db, dc;
+                q80_quantise_unit(v, inv14, &da, &db, &dc);
+                if (u < units) {
+                    const int pc = u >> 4, j = u & 15;
+                    uint32_t* dst = dig + (j >> 2) * prow + pc * 4 + (j & 3);
+                    dst[0] = da, dst[4 * prow] = db, dst[8 * prow] = dc;
+                    if ((u & 7) == 0) xs[u >> 3] = mx * (1.0f / (127.0f * 128.0f));
                 }
             }
-            uint32_t da[8], db[8], dc[8];
-            float s;
-            q80_quantise_block(v, da, db, dc, &s);
-#pragma unroll
-            for (int w = 0; w < 8; ++w) {
-                dig[blk * 8 + w] = da[w];
-                dig[a.K / 4 + blk * 8 + w] = db[w];
-                dig[2 * (a.K / 4) + blk * 8 + w] = dc[w];
-            }
-            xs[blk] = s;
         }
         consumer_barrier();
 #pragma unroll
@@ -299,18 +328,31 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_stream_kernel(const __grid_co
             for (int pl = 0; pl < 3; ++pl)
 #pragma unroll
                 for (int i = 0; i < 16; i += 4) {
-                    const uint4 t = *reinterpret_cast<const uint4*>(dig + pl * (a.K / 4) + c * 16 + i);
+                    const uint4 t = *reinterpret_cast<const uint4*>(dig + (pl * 4 + (i >> 2)) * prow + c * 4);
                     xq.d[pl][i] = (int)t.x, xq.d[pl][i + 1] = (int)t.y, xq.d[pl][i + 2] = (int)t.z, xq.d[pl][i + 3] = (int)t.w;
                 }
-            xq.s[0] = xs[2 * c];
-            xq.s[1] = xs[2 * c + 1];
+            const float2 sc2 = *reinterpret_cast<const float2*>(xs + 2 * c);
+            xq.s[0] = sc2.x, xq.s[1] = sc2.y;
         }
+        // The digit area is dead from here on: the last ring slots lie over it. Order this thread's reads before the
+        // bulk copies (async proxy) that will overwrite them, then tell the producers.
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&xq_done);
     } else {
+        float4 sv[2] = {make_float4(0.f, 0.f, 0.f, 0.f), make_float4(0.f, 0.f, 0.f, 0.f)};
+        float4 wr[CPT][2];
+        if (a.norm_w) {  // the loads of the sum-of-squares pass and of this thread's own pieces go out together
+            const int k = tid * 4;
+            if (k < a.K) sv[0] = *reinterpret_cast<const float4*>(a.x + k);
+            if (k + CONSUMERS * 4 < a.K) sv[1] = *reinterpret_cast<const float4*>(a.x + k + CONSUMERS * 4);
+        }
 #pragma unroll
         for (int j = 0; j < CPT; ++j) {
             const int p = c + j * cols;
 #pragma unroll
             for (int i = 0; i < 8; ++i) xr[j][i] = 0.0f;
+            wr[j][0] = wr[j][1] = make_float4(0.f, 0.f, 0.f, 0.f);
             if (p < a.pieces) {
                 const int k0 = p * 8;
                 const float4 t0 = *reinterpret_cast<const float4*>(a.x + k0);
@@ -318,16 +360,36 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_stream_kernel(const __grid_co
                 xr[j][0] = t0.x, xr[j][1] = t0.y, xr[j][2] = t0.z, xr[j][3] = t0.w;
                 xr[j][4] = t1.x, xr[j][5] = t1.y, xr[j][6] = t1.z, xr[j][7] = t1.w;
                 if (a.norm_w) {
+                    wr[j][0] = load_norm4(a.norm_w, a.norm_f32, k0);
+                    wr[j][1] = load_norm4(a.norm_w, a.norm_f32, k0 + 4);
+                }
+            }
+        }
+        if (a.norm_w) {
+            float ss = sv[0].x * sv[0].x + sv[0].y * sv[0].y + sv[0].z * sv[0].z + sv[0].w * sv[0].w +
+                       sv[1].x * sv[1].x + sv[1].y * sv[1].y + sv[1].z * sv[1].z + sv[1].w * sv[1].w;
+            for (int k = tid * 4 + 2 * CONSUMERS * 4; k < a.K; k += CONSUMERS * 4) {
+                const float4 v = *reinterpret_cast<const float4*>(a.x + k);
+                ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+            }
+            ss = warp_sum(ss);
+            if (lane == 0) ssq[warp] = ss;
+            consumer_barrier();
+            float tot = 0.0f;
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        const float w = a.norm_f32 ? reinterpret_cast<const float*>(a.norm_w)[k0 + i]
-                                                   : __half2float(reinterpret_cast<const __half*>(a.norm_w)[k0 + i]);
-                        xr[j][i] = xr[j][i] * scale * w;
-                    }
-                    if (a.xn_out && blockIdx.x == 0 && grp == 0) {
-                        *reinterpret_cast<float4*>(a.xn_out + k0) = make_float4(xr[j][0], xr[j][1], xr[j][2], xr[j][3]);
-                        *reinterpret_cast<float4*>(a.xn_out + k0 + 4) = make_float4(xr[j][4], xr[j][5], xr[j][6], xr[j][7]);
-                    }
+            for (int i = 0; i < CWARPS; ++i) tot += ssq[i];
+            scale = rsqrtf(tot / (float)a.K + a.eps);
+#pragma unroll
+            for (int j = 0; j < CPT; ++j) {
+                const int p = c + j * cols;
+                const float w8[8] = {wr[j][0].x, wr[j][0].y, wr[j][0].z, wr[j][0].w,
+                                     wr[j][1].x, wr[j][1].y, wr[j][1].z, wr[j][1].w};
+#pragma unroll
+                for (int i = 0; i < 8; ++i) xr[j][i] = xr[j][i] * scale * w8[i];
+                if (p < a.pieces && a.xn_out && blockIdx.x == 0 && grp == 0) {
+                    const int k0 = p * 8;
+                    *reinterpret_cast<float4*>(a.xn_out + k0) = make_float4(xr[j][0], xr[j][1], xr[j][2], xr[j][3]);
+                    *reinterpret_cast<float4*>(a.xn_out + k0 + 4) = make_float4(xr[j][4], xr[j][5], xr[j][6], xr[j][7]);
                 }
             }
         }
@@ -335,15 +397,19 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_stream_kernel(const __grid_co
 
     constexpr uint32_t PIECE_BYTES = FMT == M40_GEMV_Q80 ? 68u : 16u;
     int it = 0;  // this group's stage counter (parity of the reduction buffer)
+    int s = grp % a.nstages;  // ring slot and use number of stage i, carried from stage to stage
+    uint32_t use = (uint32_t)(grp / a.nstages);
     for (int i = grp; i < my_groups; i += G, ++it) {
-        const int s = i % a.nstages;
+        if (i != grp) {
+            s += G;
+            while (s >= a.nstages) s -= a.nstages, ++use;
+        }
         bool ok = abort_flag == 0;
         if (ok) {  // the slot must be armed for THIS use before its parity means anything
-            const uint32_t use = (uint32_t)(i / a.nstages);
             for (uint32_t spin = 0; slot_use[s] != use && spin < WAIT_LIMIT; ++spin) {}
             ok = slot_use[s] == use;
         }
-        if (!ok || !mbar_wait(&full[s], (uint32_t)((i / a.nstages) & 1))) {
+        if (!ok || !mbar_wait(&full[s], use & 1u)) {
             abort_flag = 1;
             if (lane == 0) atomicOr(a.status, 4u);
             ok = false;
@@ -448,7 +514,7 @@ bool aligned16(const void* p) { return (((uintptr_t)p) & 15u) == 0u; }
 
 int m40_gemv_stream(M40llmCudaContext* ctx, cudaStream_t s, const float* x, int K, int fmt, int gate_up, int nseg,
                     const M40GemvSeg* segs, const M40GemvNorm* norm) {
-    if (nseg < 1 || nseg > MAX_SEGS || K <= 0 || !aligned16(x)) return 1;
+    if (nseg < 1 || nseg > MAX_SEGS - 1 || K <= 0 || !aligned16(x)) return 1;
     GemvArgs a = {};
     int cpt_max;
     uint32_t xq_bytes = 0;
@@ -462,7 +528,8 @@ int m40_gemv_stream(M40llmCudaContext* ctx, cudaStream_t s, const float* x, int 
         a.row_bytes = (uint32_t)(K / 32) * 34u;
         a.pieces = K / 64;
         cpt_max = 1;
-        xq_bytes = (uint32_t)(3 * K + (K / 32) * 4);
+        xq_bytes = (uint32_t)(12 * (K / 16 + 8) * 4 + (K / 32) * 4);  // 3 planes x 4 padded rows + block scales
+        if (norm && norm->w && K > CONSUMERS * 8 * 4) return 1;      // the norm needs the whole row in one register round
         xq_bytes = (xq_bytes + 127u) & ~127u;
     } else {
         return 1;
@@ -474,6 +541,7 @@ int m40_gemv_stream(M40llmCudaContext* ctx, cudaStream_t s, const float* x, int 
     }
     if (norm && norm->w && (!aligned16(norm->w) || (norm->xn_out && !aligned16(norm->xn_out)))) return 1;
     if ((uint64_t)a.row_bytes * nmat > STAGE_MAX || xq_bytes + 2u * a.row_bytes * nmat > SMEM_MAX) return 1;
+    // the digits are only needed until every consumer holds its slice in registers: the last ring slots reuse their bytes
 
     // Warps per group: the fewest whose per-thread register slice of x fits.
     int cw = 0, cpt = 0;
@@ -488,7 +556,7 @@ int m40_gemv_stream(M40llmCudaContext* ctx, cudaStream_t s, const float* x, int 
     }
     if (!cw) return 1;
     const int G = CWARPS / cw;
-    const uint32_t ring_max = SMEM_MAX - xq_bytes;
+    const uint32_t ring_max = SMEM_MAX;
 
     // Rows per stage: within the stage budget, a ring deep enough that every group can hold a stage while two
     // more are in flight (when the row size allows), and among those the choice that loads the persistent CTAs
@@ -528,18 +596,47 @@ int m40_gemv_stream(M40llmCudaContext* ctx, cudaStream_t s, const float* x, int 
     a.nstages = (int)(ring_max / a.stage_bytes);
     if (a.nstages > MAX_STAGES) a.nstages = MAX_STAGES;
     if (a.nstages < 2) return 1;
-    a.xq_off = (uint32_t)a.nstages * a.stage_bytes;
-    int g = 0;
-    for (int i = 0; i < nseg; ++i) {
-        a.seg[i].W = (const uint8_t*)segs[i].W;
-        a.seg[i].W2 = (const uint8_t*)segs[i].W2;
-        a.seg[i].out = segs[i].out;
-        a.seg[i].bias = segs[i].bias;
-        a.seg[i].residual = segs[i].residual;
-        a.seg[i].N = segs[i].N;
-        a.seg[i].group0 = g;
-        g += (segs[i].N + a.R - 1) / a.R;
+    // shared memory: [ring slots ...], the digits right-aligned over the last slots (or behind a short ring)
+    uint32_t smem_bytes = (uint32_t)a.nstages * a.stage_bytes;
+    if (smem_bytes < xq_bytes + 2u * a.stage_bytes) smem_bytes = xq_bytes + 2u * a.stage_bytes;  // >= 2 early slots
+    if (smem_bytes > SMEM_MAX) return 1;
+    a.xq_off = smem_bytes - xq_bytes;
+    a.first_late = xq_bytes ? (int)(a.xq_off / a.stage_bytes) : a.nstages;
+    // Row groups: a.R rows each, dealt round-robin to the CTAs. So that every CTA gets the same number of stages (a
+    // CTA with one stage more than the rest finishes a memory round trip late while the others idle), the group
+    // count is raised to the next multiple of the CTA count by giving the tail of the last matrix groups of
+    // a.R - 1 rows: x groups of R and y of R - 1 rows with x + y = groups and R x + (R - 1) y = N.
+    int g = 0, nout = 0;
+    long long groups_other = 0;
+    for (int i = 0; i + 1 < nseg; ++i) groups_other += (segs[i].N + a.R - 1) / a.R;
+    const int last_N = segs[nseg - 1].N;
+    const long long groups0 = groups_other + (last_N + a.R - 1) / a.R;
+    int tail_groups = 0;  // y
+    if (groups0 > grid_max && groups0 % grid_max != 0 && a.R >= 2 && last_N % a.R == 0) {
+        const long long want = (groups0 + grid_max - 1) / grid_max * grid_max - groups_other;
+        const long long y = (long long)a.R * want - last_N;
+        if (y > 0 && y <= want) tail_groups = (int)y;
     }
+    const int tail_rows = tail_groups * (a.R - 1);
+    for (int i = 0; i < nseg; ++i) {
+        const int main_rows = i == nseg - 1 ? segs[i].N - tail_rows : segs[i].N;
+        for (int part = 0; part < 2; ++part) {
+            const int r0 = part == 0 ? 0 : main_rows;
+            const int n = part == 0 ? main_rows : segs[i].N - main_rows;
+            if (n <= 0) continue;
+            SegDev& d = a.seg[nout++];
+            d.W = (const uint8_t*)segs[i].W + (size_t)r0 * a.row_bytes;
+            d.W2 = segs[i].W2 ? (const uint8_t*)segs[i].W2 + (size_t)r0 * a.row_bytes : nullptr;
+            d.out = segs[i].out + r0;
+            d.bias = segs[i].bias ? segs[i].bias + r0 : nullptr;
+            d.residual = segs[i].residual ? segs[i].residual + r0 : nullptr;
+            d.N = n;
+            d.group0 = g;
+            d.R = part == 0 ? a.R : a.R - 1;
+            g += (n + d.R - 1) / d.R;
+        }
+    }
+    nseg = nout;
     a.nseg = nseg;
     a.total_groups = g;
     a.K = K;
@@ -552,6 +649,7 @@ int m40_gemv_stream(M40llmCudaContext* ctx, cudaStream_t s, const float* x, int 
         a.xn_out = norm->xn_out;
     }
     const int grid = g < grid_max ? g : grid_max;
-    const size_t smem = (size_t)a.xq_off + xq_bytes;
+    const size_t smem = smem_bytes;
     return gate_up ? launch_fmt<1>(ctx, s, a, grid, smem, fmt, cpt) : launch_fmt<0>(ctx, s, a, grid, smem, fmt, cpt);
 }
+
