@@ -415,7 +415,7 @@ int m40_gemm_f32xq80_gguf(M40llmCudaContext* ctx, cudaStream_t s, const float* A
 // Q8_0 projections for batched rows on the tensor cores, 64 rows per pass. Returns 1 when not applicable.
 static int q80_tc_rows(M40llmCudaContext* ctx, cudaStream_t s, uint32_t stream_kind, const float* A, int M, int K,
                        int problems, const uint8_t* const* W, const int* N, float* const* out, const float* residual,
-                       int mode, const M40GemvNorm* norm = nullptr) {
+                       int mode, const M40GemvNorm* norm = nullptr, const M40TcChain* chain = nullptr) {
     const void* wp[3] = {W[0], problems > 1 ? W[1] : W[0], problems > 2 ? W[2] : W[0]};
     if (M < m40_tc_min_rows() || !m40_gemm_tc_q80_supported(M < 64 ? M : 64, K, problems, wp)) return 1;
     if (norm && norm->w && M % 64 == 1) return 1;  // a single trailing row would need the un-normalised path
@@ -440,7 +440,8 @@ static int q80_tc_rows(M40llmCudaContext* ctx, cudaStream_t s, uint32_t stream_k
             o[p] = out[p] ? out[p] + (size_t)m0 * N[p] : nullptr;
             r[p] = residual ? residual + (size_t)m0 * N[p] : nullptr;
         }
-        const int rc = m40_gemm_tc_q80(ctx, s, stream_kind, A + (size_t)m0 * K, rows, K, problems, W, N, o, r, mode, norm);
+        const int rc = m40_gemm_tc_q80(ctx, s, stream_kind, A + (size_t)m0 * K, rows, K, problems, W, N, o, r, mode, norm,
+                                       M <= 64 ? chain : nullptr);
         if (rc != 0) return rc;
     }
     return 0;
@@ -556,13 +557,37 @@ int m40_ffn_swiglu(M40llmCudaContext* ctx, uint32_t stream_kind, const void* d_x
     const bool want_norm = norm && norm->w;
     int rc;
     if (q80) {
+        // One pass of up to 64 rows on the tensor cores: the SwiGLU epilogue hands the down projection its
+        // activations already split into f16 hi | lo (one launch and one pass over hid fewer).
+        M40TcChain first = {}, second = {};
+        bool chained = false;
+        {
+            const void* wp[3] = {d_wg, d_wu, d_wd};
+            if ((int)rows >= m40_tc_min_rows() && rows <= 64 && m40_gemm_tc_q80_supported((int)rows, (int)hidden, 2, wp) &&
+                m40_gemm_tc_q80_supported((int)rows, (int)ffn, 1, wp + 2)) {
+                const int n1[2] = {(int)ffn, (int)ffn}, n2[1] = {(int)hidden};
+                size_t act1, part1, act2, part2;
+                m40_gemm_tc_q80_scratch(ctx, (int)rows, (int)hidden, 2, n1, &act1, &part1);
+                m40_gemm_tc_q80_scratch(ctx, (int)rows, (int)ffn, 1, n2, &act2, &part2);
+                size_t front = 2 * act1 + part1;
+                if (part2 > front) front = part2;
+                front = (front + 1023) & ~(size_t)1023;
+                first.scratch_bytes = second.scratch_bytes = front + 2 * act2;
+                first.act_off = second.act_off = front;
+                first.write_split = 1;
+                second.read_split = 1;
+                chained = true;
+            }
+        }
         {
             const uint8_t* w[2] = {(const uint8_t*)d_wg, (const uint8_t*)d_wu};
             const int n[2] = {(int)ffn, (int)ffn};
             float* o[2] = {(float*)d_hid, nullptr};
-            rc = q80_tc_rows(ctx, s, stream_kind, (const float*)d_x, (int)rows, (int)hidden, 2, w, n, o, nullptr, 1, norm);
+            rc = q80_tc_rows(ctx, s, stream_kind, (const float*)d_x, (int)rows, (int)hidden, 2, w, n, o, nullptr, 1, norm,
+                             chained ? &first : nullptr);
         }
         if (rc == 1) {
+            chained = false;
             if (want_norm) return 1;
             rc = m40_gate_up_swiglu_q80(ctx, s, (const float*)d_x, (const uint8_t*)d_wg, (const uint8_t*)d_wu,
                                         (float*)d_hid, (int)rows, (int)ffn, (int)hidden);
@@ -573,7 +598,7 @@ int m40_ffn_swiglu(M40llmCudaContext* ctx, uint32_t stream_kind, const void* d_x
             const int n[1] = {(int)hidden};
             float* o[1] = {(float*)d_out};
             rc = q80_tc_rows(ctx, s, stream_kind, (const float*)d_hid, (int)rows, (int)ffn, 1, w, n, o,
-                             (const float*)d_residual, 0);
+                             (const float*)d_residual, 0, nullptr, chained ? &second : nullptr);
         }
         if (rc != 1) return rc;
         return m40_gemm_f32xq80_gguf(ctx, s, (const float*)d_hid, (const uint8_t*)d_wd, (float*)d_out, (int)rows,

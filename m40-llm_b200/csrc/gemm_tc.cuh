@@ -14,12 +14,27 @@ int m40_gemm_tc_f16(M40llmCudaContext* ctx, cudaStream_t s, uint32_t stream_kind
                     const float* const* residual, int mode, const M40GemvNorm* norm = nullptr);
 // `norm` (optional): RMSNorm applied to X while it is split into f16 hi/lo (saves the separate norm pass).
 
+// Two Q8_0 tensor-core calls chained through the f16 hi | lo copies the second one consumes (gate|up -> down): the
+// first call's epilogue writes its result already split, the second skips its split pass. Both calls request
+// `scratch_bytes` of stream scratch; the split copies live at byte offset `act_off` (hi, then lo), past everything
+// either call keeps in front of it.
+struct M40TcChain {
+    size_t scratch_bytes;
+    size_t act_off;
+    int write_split;  // this call: epilogue also writes out[0] as f16 hi | lo at act_off
+    int read_split;   // this call: the activations are already split at act_off
+};
+// Scratch one Q8_0 tensor-core call needs: bytes of one f16 activation copy and of its partial tiles.
+void m40_gemm_tc_q80_scratch(const M40llmCudaContext* ctx, int M, int K, int problems, const int* N, size_t* act_bytes,
+                             size_t* part_bytes);
+
 // Same over Q8_0 GGUF rows (K % 256 == 0, 2 <= M <= 64 per call). mode 0: out[p] = X.W[p]^T (+ residual[p]);
 // mode 1: out[0] = silu(X.Wg^T) * (X.Wu^T).
 bool m40_gemm_tc_q80_supported(int M, int K, int problems, const void* const* W);
 int m40_gemm_tc_q80(M40llmCudaContext* ctx, cudaStream_t s, uint32_t stream_kind, const float* X, int M, int K,
                     int problems, const uint8_t* const* W, const int* N, float* const* out,
-                    const float* const* residual, int mode, const M40GemvNorm* norm = nullptr);
+                    const float* const* residual, int mode, const M40GemvNorm* norm = nullptr,
+                    const M40TcChain* chain = nullptr);
 // The f32 -> f16 hi/lo split (with optional RMSNorm per row) shared by both tensor-core paths.
 int m40_split_activations(M40llmCudaContext* ctx, cudaStream_t s, const float* X, __half* hi, __half* lo, int M, int K,
                           const M40GemvNorm* norm);

@@ -322,6 +322,8 @@ __global__ void __launch_bounds__(CTA_THREADS, 1) gemm_tc_q80_kernel(const __gri
 
 struct Q80EpiArgs {
     const float* partial;
+    __half* split_hi;  // optional (mode 1): the result as f16 hi | lo copies for a following tensor-core call
+    __half* split_lo;
     float* out[3];
     const float* residual[3];
     uint32_t N[3];
@@ -390,7 +392,14 @@ __global__ void __launch_bounds__(256) gemm_tc_q80_epilogue_kernel(Q80EpiArgs e)
         if (m >= e.M) continue;
         float a0 = acc[r];
         if (e.mode == 1) {
-            e.out[0][(size_t)m * e.N[0] + n] = (a0 / (1.0f + expf(-a0))) * up[r];
+            const float v = (a0 / (1.0f + expf(-a0))) * up[r];
+            const size_t o = (size_t)m * e.N[0] + n;
+            e.out[0][o] = v;
+            if (e.split_hi) {  // the same split as split_activations_kernel
+                const __half h = __float2half_rn(v);
+                e.split_hi[o] = h;
+                e.split_lo[o] = __float2half_rn(v - __half2float(h));
+            }
             continue;
         }
         if (e.residual[p]) a0 += e.residual[p][(size_t)m * e.N[p] + n];
@@ -465,36 +474,55 @@ bool m40_gemm_tc_q80_supported(int M, int K, int problems, const void* const* W)
     return get_encode() != nullptr;
 }
 
-int m40_gemm_tc_q80(M40llmCudaContext* ctx, cudaStream_t s, uint32_t stream_kind, const float* X, int M, int K,
-                    int problems, const uint8_t* const* W, const int* N, float* const* out,
-                    const float* const* residual, int mode, const M40GemvNorm* norm) {
-    const uint32_t M_pad = M <= 16 ? 16u : (M <= 32 ? 32u : 64u);
-    Q80Args a = {};
-    a.M = (uint32_t)M;
-    a.K = (uint32_t)K;
-    a.problems = (uint32_t)problems;
+namespace {
+// Tile / span bookkeeping shared by the launch and the scratch query.
+void q80_plan(const M40llmCudaContext* ctx, int M, int K, int problems, const int* N, Q80Args* a) {
+    a->M = (uint32_t)M;
+    a->K = (uint32_t)K;
+    a->problems = (uint32_t)problems;
     uint32_t tiles = 0;
     for (int p = 0; p < problems; ++p) {
-        a.tile_begin[p] = tiles;
+        a->tile_begin[p] = tiles;
         tiles += (uint32_t)((N[p] + BLOCK_N - 1) / BLOCK_N);
     }
-    for (int p = problems; p < 4; ++p) a.tile_begin[p] = tiles;
-    a.tiles_total = tiles;
-    a.units_per_tile = (uint32_t)K / UNIT_K;
-    a.units_total = tiles * a.units_per_tile;
-    a.ctas = (uint32_t)ctx->sm_count < a.units_total ? (uint32_t)ctx->sm_count : a.units_total;
-    if ((uint64_t)(a.units_total + 1) * (a.ctas + 1) >= (1ull << 32)) return -2;  // span arithmetic is 32-bit
-    const uint32_t upc = (a.units_total + a.ctas - 1) / a.ctas;
-    a.seg_max = upc / a.units_per_tile + 2;
+    for (int p = problems; p < 4; ++p) a->tile_begin[p] = tiles;
+    a->tiles_total = tiles;
+    a->units_per_tile = (uint32_t)K / UNIT_K;
+    a->units_total = tiles * a->units_per_tile;
+    a->ctas = (uint32_t)ctx->sm_count < a->units_total ? (uint32_t)ctx->sm_count : a->units_total;
+    const uint32_t upc = (a->units_total + a->ctas - 1) / a->ctas;
+    a->seg_max = upc / a->units_per_tile + 2;
+}
+size_t q80_act_bytes(int M, int K) { return (((size_t)M * K * 2 + 255) / 256) * 256; }
+}  // namespace
 
-    const size_t act_elems = (size_t)M * K;
-    const size_t act_bytes = ((act_elems * 2 + 255) / 256) * 256;
+void m40_gemm_tc_q80_scratch(const M40llmCudaContext* ctx, int M, int K, int problems, const int* N, size_t* act_bytes,
+                             size_t* part_bytes) {
+    Q80Args a = {};
+    q80_plan(ctx, M, K, problems, N, &a);
+    *act_bytes = q80_act_bytes(M, K);
+    *part_bytes = (size_t)a.ctas * a.seg_max * M * BLOCK_N * sizeof(float);
+}
+
+int m40_gemm_tc_q80(M40llmCudaContext* ctx, cudaStream_t s, uint32_t stream_kind, const float* X, int M, int K,
+                    int problems, const uint8_t* const* W, const int* N, float* const* out,
+                    const float* const* residual, int mode, const M40GemvNorm* norm, const M40TcChain* chain) {
+    const uint32_t M_pad = M <= 16 ? 16u : (M <= 32 ? 32u : 64u);
+    Q80Args a = {};
+    q80_plan(ctx, M, K, problems, N, &a);
+    if ((uint64_t)(a.units_total + 1) * (a.ctas + 1) >= (1ull << 32)) return -2;  // span arithmetic is 32-bit
+
+    const size_t act_bytes = q80_act_bytes(M, K);
     const size_t part_bytes = (size_t)a.ctas * a.seg_max * M * BLOCK_N * sizeof(float);
-    unsigned char* scratch = (unsigned char*)m40_ensure_scratch(ctx, stream_kind, 2 * act_bytes + part_bytes);
+    size_t need = 2 * act_bytes + part_bytes;
+    if (chain && chain->scratch_bytes > need) need = chain->scratch_bytes;
+    unsigned char* scratch = (unsigned char*)m40_ensure_scratch(ctx, stream_kind, need);
     if (!scratch) return -2;
-    __half* xh = (__half*)scratch;
-    __half* xl = (__half*)(scratch + act_bytes);
-    a.partial = (float*)(scratch + 2 * act_bytes);
+    const bool presplit = chain && chain->read_split;
+    // own split copies in front of the partial tiles; with pre-split activations the partial tiles come first
+    __half* xh = (__half*)(presplit ? scratch + chain->act_off : scratch);
+    __half* xl = (__half*)((unsigned char*)xh + act_bytes);
+    a.partial = (float*)(presplit ? scratch : scratch + 2 * act_bytes);
     a.status = ctx->d_status;
 
     const uint64_t row_bytes = (uint64_t)(K / 32) * 34;
@@ -505,7 +533,7 @@ int m40_gemm_tc_q80(M40llmCudaContext* ctx, cudaStream_t s, uint32_t stream_kind
     }
     if (!make_map_act(&mXh, xh, (uint64_t)M, (uint64_t)K, M_pad)) return -2;
     if (!make_map_act(&mXl, xl, (uint64_t)M, (uint64_t)K, M_pad)) return -2;
-    if (m40_split_activations(ctx, s, X, xh, xl, M, K, norm) != 0) return -2;
+    if (!presplit && m40_split_activations(ctx, s, X, xh, xl, M, K, norm) != 0) return -2;
     int rc;
     if (M_pad == 16) rc = launch_q80<16>(ctx, s, mW, mXh, mXl, a);
     else if (M_pad == 32) rc = launch_q80<32>(ctx, s, mW, mXh, mXl, a);
@@ -514,6 +542,10 @@ int m40_gemm_tc_q80(M40llmCudaContext* ctx, cudaStream_t s, uint32_t stream_kind
 
     Q80EpiArgs e = {};
     e.partial = a.partial;
+    if (chain && chain->write_split && mode == 1) {
+        e.split_hi = (__half*)(scratch + chain->act_off);
+        e.split_lo = (__half*)(scratch + chain->act_off + q80_act_bytes(M, N[0]));
+    }
     uint32_t maxN = 0;
     for (int p = 0; p < problems; ++p) {
         e.out[p] = out[p];
