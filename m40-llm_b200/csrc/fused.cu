@@ -102,8 +102,16 @@ extern "C" int m40llm_qkv_rmsnorm_rope_append_async(M40llmCudaContext* ctx, M40l
         float* o[3] = {(float*)d_q_out_f32, kbuf, vbuf};
         const float* b[3] = {(const float*)d_bq_f32, (const float*)d_bk_f32, (const float*)d_bv_f32};
         const M40GemvNorm norm = {d_norm_w, norm_w_dtype == 1u ? 1 : 0, eps, nullptr};
-        rc = m40_gemm_tc_f16(ctx, s, 1u, (const float*)d_x_f32, (int)rows, (int)hidden, 3, w, n, o, b, nullptr, 0, &norm);
+        // dense cache, adjacent-pair RoPE, whole 128-column tiles per matrix: the projection's epilogue rotates and
+        // appends, and no separate launch follows
+        const bool tail_in_epilogue = !kv->compressed && rope_layout == 0u && QD % 128u == 0u && KD % 128u == 0u;
+        const M40TcRopeAppend ra = {d_seq_ids, d_positions, (__half*)kv->d_k, (__half*)kv->d_v, kv->d_seq_map,
+                                    ctx->d_status, hd, kv->num_heads, kv->max_seq_len, kv->max_batch_size,
+                                    freq_base, freq_scale};
+        rc = m40_gemm_tc_f16(ctx, s, 1u, (const float*)d_x_f32, (int)rows, (int)hidden, 3, w, n, o, b, nullptr, 0, &norm,
+                             tail_in_epilogue ? &ra : nullptr);
         if (rc != 0) return rc;
+        if (tail_in_epilogue) return 0;
     } else if ((rc = m40_rms_norm_rows(ctx, d_x_f32, d_norm_w, xn, rows, hidden, eps, norm_w_dtype)) != 0) {
         return rc;
     } else {

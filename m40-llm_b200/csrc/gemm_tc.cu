@@ -247,6 +247,8 @@ struct EpiArgs {
     uint32_t N[3];
     uint32_t tile_begin[4];
     uint32_t problems, M, n_total, k_splits, mode;
+    uint32_t rope_on;
+    M40TcRopeAppend rope;
 };
 
 __global__ void __launch_bounds__(256) gemm_tc_epilogue_kernel(EpiArgs e) {
@@ -292,7 +294,32 @@ __global__ void __launch_bounds__(256) gemm_tc_epilogue_kernel(EpiArgs e) {
         }
         if (e.bias[p]) r += e.bias[p][n];
         if (e.residual[p]) r += e.residual[p][(size_t)m * e.N[p] + n];
-        e.out[p][(size_t)m * e.N[p] + n] = r;
+        if (!e.rope_on) {
+            e.out[p][(size_t)m * e.N[p] + n] = r;
+            continue;
+        }
+        // q | k | v tail (the whole warp is here: N is a multiple of 128 and m is the same for all lanes):
+        // RoPE on adjacent pairs of q and k, then q to its buffer and k, v as f16 into the cache row of this position
+        const M40TcRopeAppend& ra = e.rope;
+        const uint32_t seq = ra.seq_ids[m], pos = ra.positions[m];
+        const uint32_t d = n % ra.head_dim, head = n / ra.head_dim;
+        const float other = __shfl_xor_sync(0xffffffffu, r, 1);
+        if (seq >= ra.max_batch || pos >= ra.max_seq_len) {
+            if (p == 0 && n == 0) atomicOr(ra.status, 2u);
+            continue;
+        }
+        if (p < 2) {
+            float c, sn;
+            rope_cs(pos, d >> 1, ra.head_dim, ra.freq_base, ra.freq_scale, &c, &sn);
+            r = (d & 1u) ? other * sn + r * c : r * c - other * sn;
+        }
+        if (p == 0) {
+            e.out[0][(size_t)m * e.N[0] + n] = r;
+        } else {
+            const size_t at = kv_row_offset(seq, head, pos, ra.kv_heads, ra.max_seq_len, ra.head_dim) + d;
+            (p == 1 ? ra.d_k : ra.d_v)[at] = __float2half_rn(r);
+            if (p == 1 && n == 0) ra.d_seq_map[seq] = pos + 1u;
+        }
     }
 }
 
@@ -354,7 +381,12 @@ bool m40_gemm_tc_supported(int M, int K, int problems, const void* const* W) {
 
 int m40_gemm_tc_f16(M40llmCudaContext* ctx, cudaStream_t s, uint32_t stream_kind, const float* X, int M, int K,
                     int problems, const __half* const* W, const int* N, float* const* out, const float* const* bias,
-                    const float* const* residual, int mode, const M40GemvNorm* norm) {
+                    const float* const* residual, int mode, const M40GemvNorm* norm, const M40TcRopeAppend* rope) {
+    if (rope) {
+        if (problems != 3 || mode != 0 || rope->head_dim == 0 || rope->head_dim % 2 != 0) return -2;
+        for (int p = 0; p < 3; ++p)
+            if (N[p] % 128 != 0 || N[p] % (int)rope->head_dim != 0) return -2;
+    }
     const uint32_t M_pad = (uint32_t)((M + 15) / 16 * 16);
     TcArgs a = {};
     a.M = (uint32_t)M;
@@ -437,6 +469,10 @@ int m40_gemm_tc_f16(M40llmCudaContext* ctx, cudaStream_t s, uint32_t stream_kind
     e.n_total = a.n_total;
     e.k_splits = ks;
     e.mode = (uint32_t)mode;
+    if (rope) {
+        e.rope_on = 1u;
+        e.rope = *rope;
+    }
     dim3 egrid((maxN + 127) / 128, (unsigned)(M + 7) / 8, mode == 1 ? 1u : (unsigned)problems);
     m40_launch_dependent(gemm_tc_epilogue_kernel, egrid, dim3(256), 0, s, e);
     M40_COUNT_LAUNCH(ctx);

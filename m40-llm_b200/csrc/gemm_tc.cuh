@@ -3,6 +3,20 @@
 #include "common.cuh"
 #include "gemv_stream.cuh"  // M40GemvNorm
 
+// Optional tail of a three-problem (Wq | Wk | Wv) call: the epilogue applies RoPE (adjacent pairs) to q and k per row
+// position, writes q, and appends k / v as f16 to a dense cache, instead of storing f32 k / v for a separate launch.
+// Needs every N to be a multiple of 128 and of head_dim.
+struct M40TcRopeAppend {
+    const uint32_t* seq_ids;
+    const uint32_t* positions;
+    __half* d_k;
+    __half* d_v;
+    uint32_t* d_seq_map;
+    uint32_t* status;
+    uint32_t head_dim, kv_heads, max_seq_len, max_batch;
+    float freq_base, freq_scale;
+};
+
 // True when the tcgen05 path can take this problem set (2 <= M <= 256, K % 8 == 0, 16-byte aligned weights).
 bool m40_gemm_tc_supported(int M, int K, int problems, const void* const* W);
 
@@ -11,7 +25,8 @@ bool m40_gemm_tc_supported(int M, int K, int problems, const void* const* W);
 // mode 1: two problems (gate, up) of equal N: out[0][m][n] = silu(X.Wg^T) * (X.Wu^T).
 int m40_gemm_tc_f16(M40llmCudaContext* ctx, cudaStream_t s, uint32_t stream_kind, const float* X, int M, int K,
                     int problems, const __half* const* W, const int* N, float* const* out, const float* const* bias,
-                    const float* const* residual, int mode, const M40GemvNorm* norm = nullptr);
+                    const float* const* residual, int mode, const M40GemvNorm* norm = nullptr,
+                    const M40TcRopeAppend* rope = nullptr);
 // `norm` (optional): RMSNorm applied to X while it is split into f16 hi/lo (saves the separate norm pass).
 
 // Two Q8_0 tensor-core calls chained through the f16 hi | lo copies the second one consumes (gate|up -> down): the

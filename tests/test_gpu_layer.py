@@ -1,5 +1,7 @@
 """Whole decode layer through the C ABI against the oracle's layer (op order of src/infer/forward.rs:247-667,
 CPU form tests/forward_parity_toy.rs:309-386; the reference's toy-layer tolerance is 5e-3)."""
+import ctypes as C
+
 import numpy as np
 import pytest
 
@@ -113,9 +115,51 @@ def test_decode_layer_batched_rows_and_compressed_append(nat, O, fused_tail):
     out, q_rot, att = device_layer(nat, kv, w, x, list(range(B)), [n - 1 for n in lens], cfg, True, fused_tail)
     for b, n in enumerate(lens):
         eout, eq, eatt = O.decode_layer(cfg, x[b], w, Ks[b], Vs[b], n - 1)
+        assert_close(q_rot[b], eq, what=f"row {b} q after rope")
         assert_close(att[b], eatt, what=f"row {b} attention")
         assert_close(out[b], eout, what=f"row {b} output")
     nat.lib.m40llm_kvcache_destroy(kv)
+    nat.free_all()
+
+
+def test_batched_prologue_epilogue_rope_append_bias_and_bad_position(nat, O):
+    """Batched rows on a dense cache with adjacent RoPE: the QKV projection's epilogue rotates q / k and appends k / v
+    itself (no separate launch). With QKV bias; a row whose position lies outside the cache raises status bit 2 and
+    leaves the cache alone while the other rows are appended (kernels.cu:1297-1346 checks the same bounds)."""
+    rng = np.random.default_rng(123)
+    H, qh, kvh, hd, F = 512, 8, 2, 64, 768
+    cfg = O.LayerCfg(H, qh, kvh, hd, F, 0, 0, 1e-5, 5e5, 1.0)
+    w = make_weights(O, rng, H, qh, kvh, hd, F, False, True)
+    L, ctx = nat.lib, nat.ctx
+    B, max_seq = 4, 96
+    kv = nat.kv_dense(max_seq, B, kvh, hd)
+    positions = [10, 95, 400, 0]  # row 2 is out of range
+    x = rng.standard_normal((B, H)).astype(np.float32)
+    d = {n: nat.buf(a) for n, a in w.items()}
+    dx, dq = nat.buf(x), nat.buf(B * qh * hd * 4)
+    dids, dpos = nat.buf(np.arange(B, dtype=np.uint32)), nat.buf(np.asarray(positions, np.uint32))
+    rc = L.m40llm_qkv_rmsnorm_rope_append_async(ctx, kv, dx.ptr, d["attn_norm"].ptr, 1, cfg.eps, d["wq"].ptr, d["wk"].ptr,
+                                                d["wv"].ptr, d["bq"].ptr, d["bk"].ptr, d["bv"].ptr, dids.ptr, dpos.ptr, B,
+                                                H, qh, cfg.rope_base, cfg.rope_scale, 0, dq.ptr)
+    assert rc == 0, rc
+    nat.sync(1)
+    st = np.zeros(1, np.uint32)
+    assert L.m40llm_context_take_device_status(ctx, st.ctypes.data) == 0 and st[0] == 2
+    q = dq.download(np.float32, (B, qh * hd))
+    for b, pos in enumerate(positions):
+        if pos >= max_seq:
+            continue
+        xn = O.rms_norm(x[b], w["attn_norm"], cfg.eps)
+        eq = O.rope(O.gemm_f32xf16_gguf(xn, w["wq"]) + w["bq"], qh, hd, pos, cfg.rope_base, 1.0, 0)
+        ek = O.rope(O.gemm_f32xf16_gguf(xn, w["wk"]) + w["bk"], kvh, hd, pos, cfg.rope_base, 1.0, 0)
+        ev = O.gemm_f32xf16_gguf(xn, w["wv"]) + w["bv"]
+        assert_close(q[b], eq, what=f"row {b} q")
+        k_dev, v_dev = np.zeros((kvh, hd), np.float16), np.zeros((kvh, hd), np.float16)
+        assert L.m40llm_kvcache_debug_read_token(ctx, kv, b, pos, k_dev.ctypes.data_as(C.c_void_p),
+                                                 v_dev.ctypes.data_as(C.c_void_p)) == 0
+        assert_close(k_dev.astype(np.float32).ravel(), O.f32_to_f16(ek).astype(np.float32).ravel(), what=f"row {b} k")
+        assert_close(v_dev.astype(np.float32).ravel(), O.f32_to_f16(ev).astype(np.float32).ravel(), what=f"row {b} v")
+    L.m40llm_kvcache_destroy(kv)
     nat.free_all()
 
 
