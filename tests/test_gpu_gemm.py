@@ -111,3 +111,40 @@ def test_ffn_swiglu(nat, O, rows, H, F, q80):
     nat.sync(1)
     assert_close(do.download(np.float32, (rows, H)), exp - res, what="ffn out, no residual")
     nat.free_all()
+
+
+@pytest.mark.parametrize("fmt,N,K", [
+    ("f16", 6144, 4096),    # groups % CTAs != 0: the tail of the matrix is cut into groups one row smaller
+    ("f16", 1001, 2048),    # odd row count, fewer groups than whole deals
+    ("f16", 32000, 2048),   # lm_head shape
+    ("f16", 595, 512),      # barely more groups than CTAs
+    ("q80", 1024, 28672),   # K > 16384: activation digits made in two rounds, ring slots over a 90 KB digit area
+    ("q80", 599, 512),
+    ("q80", 11008, 4096),
+    ("q80", 5632, 2048),
+    ("q80", 2048, 5632),
+])
+def test_one_row_streaming_shapes(nat, O, fmt, N, K):
+    """One activation row through the weight-streaming kernel at shapes that exercise its stage bookkeeping
+    (equal stage counts per CTA, late ring slots, multi-round activation preparation)."""
+    rng = np.random.default_rng(N * 7 + K)
+    a = rng.standard_normal((1, K)).astype(np.float32)
+    a[0, ::97] *= 30.0  # wide dynamic range inside 32-blocks
+    a[0, 64:96] = 0.0   # an all-zero block
+    dc = nat.buf(N * 4)
+    da = nat.buf(a)
+    if fmt == "f16":
+        w = (rng.standard_normal((N, K)) * 0.05).astype(np.float16)
+        dw = nat.buf(w)
+        assert nat.lib.m40llm_gemm_f32xf16_gguf_f32_async(nat.ctx, da.ptr, dw.ptr, dc.ptr, 1, N, K, 1) == 0
+        exp = O.gemm_f32xf16_gguf(a, w)
+    else:
+        wq = O.q80_quantize((rng.standard_normal((N, K)) * 0.02).astype(np.float32))
+        dw = nat.buf(wq)
+        assert nat.lib.m40llm_gemm_f32xq80_gguf_f32_async(nat.ctx, da.ptr, dw.ptr, dc.ptr, 1, N, K, 1) == 0
+        exp = O.gemm_f32xq80_gguf(a, wq, N)
+    nat.sync(1)
+    assert_close(dc.download(np.float32, (1, N)), exp, what=f"one row {fmt} {N}x{K}")
+    st = np.zeros(1, np.uint32)
+    assert nat.lib.m40llm_context_take_device_status(nat.ctx, st.ctypes.data) == 0 and st[0] == 0
+    nat.free_all()
