@@ -198,7 +198,36 @@ __global__ void split_activations_kernel(const float* __restrict__ x, __half* __
     }
 }
 
-// One CTA per activation row: optional RMSNorm (x * rsqrt(mean(x^2) + eps) * w), then the f16 hi/lo split.
+// One CTA per activation row: RMSNorm (x * rsqrt(mean(x^2) + eps) * w), then the f16 hi/lo split. The row and its
+// norm weights are fetched once, all loads in flight together (up to 8192 columns stay in registers; wider rows are
+// read a second time for the part beyond).
+// w_f32: bit 0 = f32 weights (else f16), bit 1 = the weight pointer is not aligned for vector loads
+__device__ __forceinline__ float4 norm_w4(const void* w, int w_f32, uint32_t k) {
+    if (w_f32 & 2) {
+        float t[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+            t[i] = (w_f32 & 1) ? reinterpret_cast<const float*>(w)[k + i]
+                               : __half2float(reinterpret_cast<const __half*>(w)[k + i]);
+        return make_float4(t[0], t[1], t[2], t[3]);
+    }
+    if (w_f32) return *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(w) + k);
+    const uint2 r = *reinterpret_cast<const uint2*>(reinterpret_cast<const __half*>(w) + k);
+    const float2 lo = __half22float2(*reinterpret_cast<const __half2*>(&r.x));
+    const float2 hi = __half22float2(*reinterpret_cast<const __half2*>(&r.y));
+    return make_float4(lo.x, lo.y, hi.x, hi.y);
+}
+__device__ __forceinline__ void split_store4(const float4& x, const float4& wv, float scale, __half* hr, __half* lr) {
+    const float y[4] = {x.x * scale * wv.x, x.y * scale * wv.y, x.z * scale * wv.z, x.w * scale * wv.w};
+    __half h[4], l[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        h[i] = __float2half_rn(y[i]);
+        l[i] = __float2half_rn(y[i] - __half2float(h[i]));
+    }
+    *reinterpret_cast<uint2*>(hr) = *reinterpret_cast<const uint2*>(h);
+    *reinterpret_cast<uint2*>(lr) = *reinterpret_cast<const uint2*>(l);
+}
 __global__ void __launch_bounds__(256) norm_split_rows_kernel(const float* __restrict__ x, const void* __restrict__ w,
                                                               int w_f32, float eps, __half* __restrict__ hi,
                                                               __half* __restrict__ lo, uint32_t K) {
@@ -208,8 +237,18 @@ __global__ void __launch_bounds__(256) norm_split_rows_kernel(const float* __res
     const float* xr = x + (size_t)blockIdx.x * K;
     __half* hr = hi + (size_t)blockIdx.x * K;
     __half* lr = lo + (size_t)blockIdx.x * K;
+    constexpr int V = 8;  // float4 per thread held in registers
+    float4 xv[V], wv[V];
+#pragma unroll
+    for (int i = 0; i < V; ++i) {
+        const uint32_t k = threadIdx.x * 4u + (uint32_t)i * 1024u;
+        xv[i] = k < K ? *reinterpret_cast<const float4*>(xr + k) : make_float4(0.f, 0.f, 0.f, 0.f);
+        wv[i] = k < K ? norm_w4(w, w_f32, k) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
     float ss = 0.0f;
-    for (uint32_t k = threadIdx.x * 4u; k < K; k += 1024u) {
+#pragma unroll
+    for (int i = 0; i < V; ++i) ss += xv[i].x * xv[i].x + xv[i].y * xv[i].y + xv[i].z * xv[i].z + xv[i].w * xv[i].w;
+    for (uint32_t k = threadIdx.x * 4u + V * 1024u; k < K; k += 1024u) {
         const float4 v = *reinterpret_cast<const float4*>(xr + k);
         ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
     }
@@ -220,21 +259,13 @@ __global__ void __launch_bounds__(256) norm_split_rows_kernel(const float* __res
 #pragma unroll
     for (int i = 0; i < 8; ++i) tot += red[i];
     const float scale = rsqrtf(tot / (float)K + eps);
-    for (uint32_t k = threadIdx.x * 4u; k < K; k += 1024u) {
-        const float4 v = *reinterpret_cast<const float4*>(xr + k);
-        float t[4] = {v.x, v.y, v.z, v.w};
-        __half h[4], l[4];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const float wv = w_f32 ? reinterpret_cast<const float*>(w)[k + i]
-                                   : __half2float(reinterpret_cast<const __half*>(w)[k + i]);
-            const float y = t[i] * scale * wv;
-            h[i] = __float2half_rn(y);
-            l[i] = __float2half_rn(y - __half2float(h[i]));
-        }
-        *reinterpret_cast<uint2*>(hr + k) = *reinterpret_cast<const uint2*>(h);
-        *reinterpret_cast<uint2*>(lr + k) = *reinterpret_cast<const uint2*>(l);
+    for (int i = 0; i < V; ++i) {
+        const uint32_t k = threadIdx.x * 4u + (uint32_t)i * 1024u;
+        if (k < K) split_store4(xv[i], wv[i], scale, hr + k, lr + k);
     }
+    for (uint32_t k = threadIdx.x * 4u + V * 1024u; k < K; k += 1024u)
+        split_store4(*reinterpret_cast<const float4*>(xr + k), norm_w4(w, w_f32, k), scale, hr + k, lr + k);
 }
 
 // Adds the K splits and applies the epilogue. Thread (n, lane of 2) walks 8 activation rows of one problem.
@@ -360,8 +391,9 @@ int m40_split_activations(M40llmCudaContext* ctx, cudaStream_t s, const float* X
                           const M40GemvNorm* norm) {
     if (norm && norm->w) {
         if (K % 4 != 0 || (((uintptr_t)X) & 15u) != 0u) return -2;
-        m40_launch_dependent(norm_split_rows_kernel, dim3((unsigned)M), dim3(256), 0, s, X, norm->w, norm->w_is_f32, norm->eps,
-                             hi, lo, (uint32_t)K);
+        const bool w_vec = (((uintptr_t)norm->w) & (norm->w_is_f32 ? 15u : 7u)) == 0u;
+        m40_launch_dependent(norm_split_rows_kernel, dim3((unsigned)M), dim3(256), 0, s, X, norm->w,
+                             (norm->w_is_f32 ? 1 : 0) | (w_vec ? 0 : 2), norm->eps, hi, lo, (uint32_t)K);
     } else {
         const size_t n = (size_t)M * K;
         size_t blocks = (n + 255) / 256;
