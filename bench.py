@@ -14,7 +14,10 @@ output projection + residual, norm, Q8_0 SwiGLU FFN + residual): 32 tokens advan
           measured HBM copy bandwidth.
 `cpu_baseline` the oracle (CPU restatement of the reference math) timed on this box's host cores on a bounded
           sample of the same batch.
-With N > 1 (torchrun) every rank runs its own batch of 32 sequences (weak scaling, no collective on the path).
+`parity`  before any timing one eager step of the exact batch is compared with the oracle on four rows (shortest,
+          longest and two more): layer output and the appended K/V rows. A miss ends the run with exit code 3.
+With N > 1 (torchrun) ONE global batch of 32 x N sequences is dealt to the ranks, longest first onto the least
+loaded rank with 32 sequences each (weak scaling, no collective on the path); the slowest rank sets the step time.
 """
 from __future__ import annotations
 
@@ -32,7 +35,7 @@ import numpy as np
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
-sys.path.insert(0, os.path.join(ROOT, "tests"))
+PKG_DIR = os.path.join(ROOT, "m40-llm_b200")
 
 H, QH, KVH, HD, F = 4096, 32, 8, 128, 14336
 B, LMIN, LMAX = 32, 512, 8192
@@ -41,6 +44,20 @@ N_WEIGHT_SETS = 2  # rotated between steps so no weight byte survives in L2 from
 # Traffic of the dominant kernel from the committed ncu capture (profiles/): DRAM bytes per algorithmic byte.
 NCU_TRAFFIC_RATIO = 1.03
 CPU_BASELINE_SECONDS = 12.0  # wall time spent in the oracle for the cpu_baseline leg
+MIN_TIMED_SECONDS = 0.3      # a timed loop repeats its block of `steps` until it has run at least this long
+ATOL, RTOL = 1e-3, 2e-3      # parity tolerance: |a - e| <= ATOL + RTOL * |e|
+
+
+def load_package():
+    """The package directory carries a hyphen, so it is loaded by path."""
+    if "m40_llm_b200" in sys.modules:
+        return sys.modules["m40_llm_b200"]
+    spec = importlib.util.spec_from_file_location(
+        "m40_llm_b200", os.path.join(PKG_DIR, "__init__.py"), submodule_search_locations=[PKG_DIR])
+    mod = importlib.util.module_from_spec(spec)
+    sys.modules["m40_llm_b200"] = mod
+    spec.loader.exec_module(mod)
+    return mod
 
 
 def layer_weight_bytes():
@@ -122,9 +139,11 @@ class ClockSampler:
                 "reasons": reasons, "samples": len(sm)}
 
 
-def make_inputs(O, seed):
-    rng = np.random.default_rng(seed)
-    lens = rng.integers(LMIN, LMAX + 1, size=B).astype(np.uint32)
+def make_inputs(O, world):
+    """ONE global batch of B * world sequences (lengths, activations) and the layer weights, all from fixed seeds, so
+    that every rank derives the same batch and the same weights (weights are replicated, sequences are dealt)."""
+    rng = np.random.default_rng(0)
+    lens = rng.integers(LMIN, LMAX + 1, size=B * world).astype(np.uint32)
     sets = []
     for _ in range(N_WEIGHT_SETS):
         w = {}
@@ -135,14 +154,26 @@ def make_inputs(O, seed):
         w["attn_norm"] = np.ones(H, np.float32)
         w["ffn_norm"] = np.ones(H, np.float32)
         sets.append(w)
-    x = rng.standard_normal((B, H), dtype=np.float32)
+    x = np.random.default_rng(77).standard_normal((B * world, H), dtype=np.float32)
     return lens, sets, x
 
 
-def kv_for_sequence(rng, n):
+def kv_for_sequence(global_index, n):
+    """Cache contents of one sequence of the global batch (seeded by its index, whichever rank it lands on)."""
+    rng = np.random.default_rng(1000 + int(global_index))
     k = rng.standard_normal((n, KVH, HD), dtype=np.float32).astype(np.float16)
     v = rng.standard_normal((n, KVH, HD), dtype=np.float32).astype(np.float16)
     return k, v
+
+
+def timed_blocks(launch_block, events, steps, pilot_ms):
+    """Times `blocks` repetitions of a block of `steps` launches inside ONE event bracket, with `blocks` chosen from
+    a pilot block so that the bracket lasts at least MIN_TIMED_SECONDS. Returns (ms per step, blocks)."""
+    blocks = max(1, int(np.ceil(MIN_TIMED_SECONDS * 1e3 / max(pilot_ms, 1e-3))))
+    events.start()
+    for b in range(blocks):
+        launch_block(b * steps)
+    return events.stop_ms() / (blocks * steps), blocks
 
 
 class Layer:
@@ -213,13 +244,17 @@ def launches(nat):
     return int(n.value)
 
 
-def workload_config(att_lens, world):
+def workload_config(global_lens, world):
     """The `config` object both arms print: BASELINE.json configs[2], the configuration the metric is quoted on."""
-    sb = step_bytes(att_lens)
+    att = np.asarray(global_lens, np.int64) + 1
+    per_gpu_bytes = layer_weight_bytes() + attention_bytes(att) // max(world, 1)
     return {"workload": "llama3-8b-shaped decode layer, batch 32 varlen [512,8192], q8_0 FFN (BASELINE configs[2])",
             "hidden": H, "q_heads": QH, "kv_heads": KVH, "head_dim": HD, "ffn": F, "batch_per_gpu": B,
-            "context_sum": int(np.sum(att_lens)), "parallelism": f"independent sequences x{world}",
-            "l2": f"inputs larger than L2: {sb / 1e6:.0f} MB per step, {N_WEIGHT_SETS} weight sets rotated"}
+            "global_batch": int(B * world), "context_sum": int(att.sum()),
+            "parallelism": f"one global batch of {B * world} sequences dealt to {world} GPU(s), longest first, "
+                           f"{B} per GPU; weights replicated; no collective",
+            "l2": f"inputs larger than L2: about {per_gpu_bytes / 1e6:.0f} MB per GPU per step, {N_WEIGHT_SETS} weight "
+                  "sets rotated"}
 
 
 class CpuLayer:
@@ -228,12 +263,11 @@ class CpuLayer:
     def __init__(self, O, sets, x, lens, n_seq=8):
         self.O, self.sets, self.x, self.lens = O, sets, x, lens
         self.cfg = O.LayerCfg(H, QH, KVH, HD, F, 1, 0, EPS, THETA, 1.0)
-        rng = np.random.default_rng(1234)
         self.seqs = list(range(min(n_seq, len(lens))))
         self.caches = []
         for b in self.seqs:
             n = int(lens[b])
-            k, v = kv_for_sequence(rng, n)
+            k, v = kv_for_sequence(b, n)
             K = np.zeros((n + 1, KVH, HD), np.float16)
             V = np.zeros((n + 1, KVH, HD), np.float16)
             K[:n], V[:n] = k, v
@@ -249,21 +283,62 @@ class CpuLayer:
 
     def describe(self):
         c = [int(self.lens[b]) for b in self.seqs]
-        return f"oracle layer, one sequence per call, cycling the first {len(c)} of the {B} sequences (contexts {min(c)}..{max(c)})"
+        return (f"oracle layer, one sequence per call, cycling the first {len(c)} of the {B} sequences (contexts "
+                f"{min(c)}..{max(c)}); every call streams all {layer_weight_bytes() / 1e6:.0f} MB of layer weights for "
+                f"one token, where the GPU arm reads them once per {B}-row step")
+
+
+def parity_gate(nat, O, layer, kv, sets, x_rows, lens_rows, global_ids):
+    """One eager step of this rank's batch against the oracle, outside every timed region: four rows (shortest and
+    longest context and two more), layer output and the K/V rows the prologue appended. Returns the record for the
+    bench line; raises SystemExit(3) on a miss."""
+    rows = sorted({int(np.argmin(lens_rows)), int(np.argmax(lens_rows)), 7 % len(lens_rows), 20 % len(lens_rows)})
+    layer.enqueue(0)
+    nat.sync(1)
+    out = layer.dout.download(np.float32, (layer.rows, H))
+    cfg = O.LayerCfg(H, QH, KVH, HD, F, 1, 0, EPS, THETA, 1.0)
+    worst, fails = 0.0, []
+    for r in rows:
+        n = int(lens_rows[r])
+        k, v = kv_for_sequence(global_ids[r], n)
+        K = np.zeros((n + 1, KVH, HD), np.float16)
+        V = np.zeros((n + 1, KVH, HD), np.float16)
+        K[:n], V[:n] = k, v
+        eout, _, _ = O.decode_layer(cfg, x_rows[r], sets[0], K, V, n)
+        kd, vd = np.zeros((KVH, HD), np.float16), np.zeros((KVH, HD), np.float16)
+        rc = nat.lib.m40llm_kvcache_debug_read_token(nat.ctx, kv, r, n, kd.ctypes.data_as(C.c_void_p),
+                                                     vd.ctypes.data_as(C.c_void_p))
+        assert rc == 0, rc
+        for name, got, exp in (("out", out[r], eout), ("k", kd.astype(np.float32), K[n].astype(np.float32)),
+                               ("v", vd.astype(np.float32), V[n].astype(np.float32))):
+            err = np.abs(got.astype(np.float64) - exp.astype(np.float64))
+            excess = float(np.max(err - (ATOL + RTOL * np.abs(exp))))
+            worst = max(worst, float(err.max()))
+            if not np.all(np.isfinite(got)) or excess > 0:
+                fails.append(f"row {r} (context {n}) {name}: max err {err.max():.3e}")
+    st = np.zeros(1, np.uint32)
+    assert nat.lib.m40llm_context_take_device_status(nat.ctx, st.ctypes.data) == 0
+    if st[0] != 0:
+        fails.append(f"device status word {int(st[0])}")
+    if fails:
+        sys.stderr.write("PARITY FAILED against the oracle, nothing timed: " + "; ".join(fails) + "\n")
+        raise SystemExit(3)
+    return {"checked": "layer output and appended K/V rows of one eager step vs the oracle layer, before any timing",
+            "rows": rows, "contexts": [int(lens_rows[r]) for r in rows], "max_abs_err": worst,
+            "tolerance": f"{ATOL} + {RTOL}*|e|", "passed": True}
 
 
 def attention_only_case(nat, args):
     """The dominant kernel on a small batch (KV larger than L2, well under 1 GB on the device): the case the
     committed profiler summaries are taken on. Prints its own one-line summary, not the bench line."""
     n = args.attention_only
-    rng = np.random.default_rng(0)
-    lens = rng.integers(LMIN, LMAX + 1, size=B).astype(np.uint32)[:n]
+    lens = np.random.default_rng(0).integers(LMIN, LMAX + 1, size=B).astype(np.uint32)[:n]
     kv = nat.kv_dense(LMAX + 8, n, KVH, HD)
     for b in range(n):
-        k, v = kv_for_sequence(rng, int(lens[b]))
+        k, v = kv_for_sequence(b, int(lens[b]))
         nat.kv_fill(kv, b, k, v)
     layer = Layer(nat, kv, None, n)
-    layer.dq.upload(rng.standard_normal((n, QH * HD), dtype=np.float32))
+    layer.dq.upload(np.random.default_rng(1).standard_normal((n, QH * HD), dtype=np.float32))
     layer.dids.upload(np.arange(n, dtype=np.uint32))
     layer.dlens.upload(lens)
     ev = Events(nat)
@@ -313,13 +388,93 @@ def ffn_only_case(nat, O, args):
                       "achieved_gbs": by / ms / 1e6}), flush=True)
 
 
+def layer_only_case(nat, O, args):
+    """The whole layer chain at `--layer-only ROWS` rows on a context of 7969 tokens per row (graph replays, two
+    weight sets rotated): the case the committed launch lists of the one-row chain are taken on."""
+    rows = args.layer_only
+    _, sets, x = make_inputs(O, 1)
+    dw = [{n: nat.buf(a) for n, a in w.items()} for w in sets]
+    ctxlen = 7968
+    kv = nat.kv_dense(ctxlen + 8, rows, KVH, HD)
+    for b in range(rows):
+        k, v = kv_for_sequence(b, ctxlen)
+        nat.kv_fill(kv, b, k, v)
+    layer = Layer(nat, kv, dw, rows)
+    layer.dx.upload(x[:rows])
+    layer.dids.upload(np.arange(rows, dtype=np.uint32))
+    layer.dpos.upload(np.full(rows, ctxlen, np.uint32))
+    layer.dlens.upload(np.full(rows, ctxlen + 1, np.uint32))
+    for w in range(N_WEIGHT_SETS):
+        layer.enqueue(w)
+    nat.sync(1)
+    graphs = [layer.capture(w) for w in range(N_WEIGHT_SETS)]
+    ev = Events(nat)
+    L, ctx = nat.lib, nat.ctx
+    for i in range(3):
+        assert L.m40llm_cuda_graph_launch(ctx, graphs[i % N_WEIGHT_SETS], 1) == 0
+    nat.sync(1)
+    ev.start()
+    for i in range(args.steps):
+        assert L.m40llm_cuda_graph_launch(ctx, graphs[i % N_WEIGHT_SETS], 1) == 0
+    ms = ev.stop_ms() / args.steps
+    by = step_bytes([ctxlen + 1] * rows)
+    print(json.dumps({"case": "layer_only", "rows": rows, "context": ctxlen + 1, "algorithmic_bytes": by,
+                      "ms_per_step": ms, "achieved_gbs": by / ms / 1e6}), flush=True)
+
+
+def compressed_case(nat, ev, peak, calls=16, reps=20):
+    """Long-context compressed attention (BASELINE configs[3] shape): Qwen2.5-3B heads, context 32768 in the FP16-K /
+    q4-V cache, 512-token ring, 64-token blocks, top 64. Four caches rotate; `calls` calls are captured in ONE graph so
+    that the timing is the device's, not the launch path's."""
+    L, ctx = nat.lib, nat.ctx
+    cq, ckv, chd, cL, cR, cbs, ctop = 16, 2, 128, 32768, 512, 64, 64
+    crng = np.random.default_rng(7)
+    caches = []
+    for _ in range(4):
+        c = nat.kv_compressed(cL, 1, ckv, chd, cR, cbs, ctop)
+        nat.kv_fill(c, 0, crng.standard_normal((cL, ckv, chd), dtype=np.float32).astype(np.float16),
+                    crng.standard_normal((cL, ckv, chd), dtype=np.float32).astype(np.float16), final_len=cL)
+        caches.append(c)
+    cdq = nat.buf(crng.standard_normal(cq * chd, dtype=np.float32))
+    cdo = nat.buf(cq * chd * 4)
+    f = L.m40llm_attention_last_token_f32_gqa_block_select_exact_fp16_k_q4_v_old_direct_async
+    n0 = launches(nat)
+    assert f(ctx, caches[0], 0, cdq.ptr, cq, cL, cR, cbs, ctop, cdo.ptr) == 0
+    per_call = launches(nat) - n0
+    for i in range(7):
+        assert f(ctx, caches[i % 4], 0, cdq.ptr, cq, cL, cR, cbs, ctop, cdo.ptr) == 0
+    nat.sync(1)
+    assert L.m40llm_cuda_graph_begin_capture(ctx, 1) == 0
+    for i in range(calls):
+        assert f(ctx, caches[i % 4], 0, cdq.ptr, cq, cL, cR, cbs, ctop, cdo.ptr) == 0
+    gexec = C.c_void_p()
+    assert L.m40llm_cuda_graph_end_capture(ctx, 1, C.byref(gexec)) == 0 and gexec.value
+    for i in range(3):
+        assert L.m40llm_cuda_graph_launch(ctx, gexec, 1) == 0
+    nat.sync(1)
+    ev.start()
+    for i in range(reps):
+        assert L.m40llm_cuda_graph_launch(ctx, gexec, 1) == 0
+    cms = ev.stop_ms() / (reps * calls)
+    L.m40llm_cuda_graph_destroy(gexec)
+    old_len = cL - cR
+    # every old K once per kv head; selected q4 V + scales (<= top blocks per q head); the ring K and V
+    cbytes = old_len * ckv * chd * 2 + cq * ctop * cbs * (chd // 2 + 4) + 2 * cR * ckv * chd * 2
+    for c in caches:
+        L.m40llm_kvcache_destroy(c)
+    return {"ms_per_call": cms, "launches_per_call": per_call, "algorithmic_bytes": cbytes,
+            "achieved_gbs": cbytes / (cms * 1e-3) / 1e9, "frac_of_hbm_peak": cbytes / (cms * 1e-3) / 1e9 / peak,
+            "config": "16/2/128 heads, context 32768, ring 512, block 64, top 64"}
+
+
 def run_reference_arm(args, rank, world):
     """`--impl reference`: the reference's CPU path is Rust and cannot be built here (no cargo/rustc, no network),
-    so the timed stand-in is the oracle port of that math, on all host threads. Rank 0 only."""
+    so the timed stand-in is the oracle port of that math, on all host threads. Rank 0 only. It is ONE CPU process on
+    the box's host cores whatever --gpus says: its rate does not scale with the number of GPUs."""
     if rank != 0:
         return
     from oracle import oracle as O
-    lens, sets, x = make_inputs(O, 0)
+    lens, sets, x = make_inputs(O, world)
     # torchrun exports OMP_NUM_THREADS=1; the reference arm is meant to use every host thread it can get
     O.set_num_threads(len(os.sched_getaffinity(0)))
     cores = O.num_threads()
@@ -335,7 +490,8 @@ def run_reference_arm(args, rank, world):
         "impl": "reference", "metric": "decode_layer_tokens_per_s", "value": val, "unit": "tokens/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": per_tok * 1e3, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": workload_config(lens + 1, world),
+        "config": workload_config(lens, world),
+        "reference_scope": "one CPU process on the host cores of the box; the same rate at every --gpus",
         "cpu_baseline": {"value": val, "unit": "tokens/s", "cores": cores, "kind": "port",
                          "sample": cpu.describe() + ", one call per step, OpenMP over rows/heads"},
         "e2e": {"value": val, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -351,10 +507,15 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extras", action="store_true", help="headline line only: skip batch1, sweep, configs[1] and [3]")
     ap.add_argument("--ffn-only", type=int, default=0, metavar="ROWS",
                     help="small case for a profiler: the Q8_0 SwiGLU FFN alone for ROWS activation rows")
     ap.add_argument("--attention-only", type=int, default=0, metavar="N",
                     help="small case for a profiler: the batched attention call alone over the first N sequences")
+    ap.add_argument("--layer-only", type=int, default=0, metavar="ROWS",
+                    help="small case for a profiler: the layer chain at ROWS rows, context 7969")
+    ap.add_argument("--compressed-only", action="store_true",
+                    help="small case for a profiler: the 32K compressed attention call alone")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     rank = int(os.environ.get("RANK", "0"))
@@ -365,17 +526,17 @@ def main():
         return
 
     import torch
-    import helpers
-    from oracle import oracle as O
+    from oracle import oracle as O  # input generation (Q8_0 quantiser), the parity gate and the cpu_baseline leg
 
     torch.cuda.set_device(local_rank)
     dist = None
     if world > 1:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-    pkg = helpers.load_package()
-    nat = helpers.Native(pkg.native.lib(), device=local_rank)
+    pkg = load_package()
+    nat = pkg.native.Native(pkg.native.lib(), device=local_rank)
     L, ctx = nat.lib, nat.ctx
+    peak, peak_kind = measured_peak_gbs()
 
     if args.attention_only:
         attention_only_case(nat, args)
@@ -383,12 +544,23 @@ def main():
     if args.ffn_only:
         ffn_only_case(nat, O, args)
         return
-    lens, sets, x = make_inputs(O, rank)
+    if args.layer_only:
+        layer_only_case(nat, O, args)
+        return
+    if args.compressed_only:
+        print(json.dumps({"case": "compressed32k", **compressed_case(nat, Events(nat), peak, calls=4, reps=max(args.steps, 1))}),
+              flush=True)
+        return
+
+    # ---------------- the global batch, dealt to the ranks (src/decode_batch.rs:143-286 builds the per-GPU plan)
+    glens, sets, gx = make_inputs(O, world)
+    shards = pkg.splitk.shard_sequences(glens, world, max_per_rank=B) if world > 1 else [list(range(B))]
+    mine = shards[rank]
+    lens, x = glens[mine], np.ascontiguousarray(gx[mine])
     dw = [{n: nat.buf(a) for n, a in w.items()} for w in sets]
     kv = nat.kv_dense(LMAX + 8, B, KVH, HD)
-    rng = np.random.default_rng(1000 + rank)
     for b in range(B):
-        k, v = kv_for_sequence(rng, int(lens[b]))
+        k, v = kv_for_sequence(mine[b], int(lens[b]))
         nat.kv_fill(kv, b, k, v)
     layer = Layer(nat, kv, dw, B)
     ids = np.arange(B, dtype=np.uint32)
@@ -399,7 +571,8 @@ def main():
     layer.dpos.upload(pos)
     layer.dlens.upload(att_lens)
 
-    # eager warm-up (sizes the scratch arenas), then capture one graph per weight set
+    # ---------------- parity gate (also the eager pass that sizes the scratch arenas), then one graph per weight set
+    parity = parity_gate(nat, O, layer, kv, sets, x, lens, mine)
     for w in range(N_WEIGHT_SETS):
         layer.enqueue(w)
     nat.sync(1)
@@ -412,19 +585,24 @@ def main():
         if dist is not None:
             dist.barrier()
 
+    def graph_block(i0):
+        for i in range(i0, i0 + args.steps):
+            assert L.m40llm_cuda_graph_launch(ctx, graphs[i % N_WEIGHT_SETS], 1) == 0
+
     # ---------------- device-resident timing
     sampler = ClockSampler(local_rank)
     sampler.start()
     sampler.wait_first_sample()
     for i in range(args.warmup):
         assert L.m40llm_cuda_graph_launch(ctx, graphs[i % N_WEIGHT_SETS], 1) == 0
+    nat.sync(1)
+    ev.start()
+    graph_block(0)                      # pilot block (untimed for the result): sizes the number of timed blocks
+    pilot_ms = ev.stop_ms()
     barrier()
     n0 = launches(nat)
     t_begin = sampler.mark()
-    ev.start()
-    for i in range(args.steps):
-        assert L.m40llm_cuda_graph_launch(ctx, graphs[i % N_WEIGHT_SETS], 1) == 0
-    ms_total = ev.stop_ms()
+    ms_step, blocks = timed_blocks(graph_block, ev, args.steps, pilot_ms)
     t_end = sampler.mark()
     barrier()
     clocks = sampler.stop(t_begin, t_end)
@@ -433,20 +611,33 @@ def main():
     layer.enqueue(0)
     nat.sync(1)
     per_step_launches = launches(nat) - n1
-    ms_step = ms_total / args.steps
+    ms_step_local = ms_step
+
+    # the same loop without rotating the weight sets (what stays in the 126 MB L2 from one step to the next may hit)
+    for i in range(3):
+        assert L.m40llm_cuda_graph_launch(ctx, graphs[0], 1) == 0
+    nat.sync(1)
+    ev.start()
+    wreps = max(args.steps, 20)
+    for i in range(wreps):
+        assert L.m40llm_cuda_graph_launch(ctx, graphs[0], 1) == 0
+    ms_step_warm = ev.stop_ms() / wreps
 
     # ---------------- dominant kernel alone (batched decode attention), CUDA events on its stream
     for _ in range(3):
         layer.attention_only()
     nat.sync(1)
-    # between timed launches the other sequences' KV (570 MB per pass) evicts any reuse: input > L2
+    # between timed launches the other sequences' KV (about 600 MB per pass) evicts any reuse: input > L2
     ev.start()
-    reps = max(10, min(args.steps, 100))
+    for _ in range(20):
+        layer.attention_only()
+    apilot = ev.stop_ms()
+    reps = max(20, int(np.ceil(MIN_TIMED_SECONDS * 1e3 / max(apilot / 20, 1e-3))))
+    ev.start()
     for _ in range(reps):
         layer.attention_only()
     attn_ms = ev.stop_ms() / reps
     attn_bytes = attention_bytes(att_lens)
-    peak, peak_kind = measured_peak_gbs()
     attn_gbs = attn_bytes / (attn_ms * 1e-3) / 1e9
 
     # ---------------- end to end: the host-side layer driver (C++ mirror of the reference's batched layer forward)
@@ -479,22 +670,37 @@ def main():
 
     for i in range(max(args.warmup, 2 * N_WEIGHT_SETS)):
         e2e_step(i)
-    barrier()
     t0 = time.perf_counter()
     for i in range(args.steps):
         e2e_step(i)
+    e2e_pilot = time.perf_counter() - t0
+    e2e_blocks = max(1, int(np.ceil(MIN_TIMED_SECONDS / max(e2e_pilot, 1e-6))))
+    barrier()
+    t0 = time.perf_counter()
+    for i in range(args.steps * e2e_blocks):
+        e2e_step(i)
     nat.sync()
-    e2e_s = (time.perf_counter() - t0) / args.steps
+    e2e_s = (time.perf_counter() - t0) / (args.steps * e2e_blocks)
     e2e_replays = hl.graph_replays()
+    # the end-to-end call's result is the layer's: one more (untimed) call on weight set 0, the set whose eager step
+    # the launch count above left in the device-resident output buffer
+    e2e_step(0)
+    e2e_err = float(np.max(np.abs(hout.numpy() - layer.dout.download(np.float32, (B, H)))))
 
+    per_rank = None
     if dist is not None:
         t = torch.tensor([ms_step, e2e_s], device="cuda", dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms_step, e2e_s = float(t[0]), float(t[1])
+        mine_t = torch.tensor([ms_step_local, float(att_lens.sum()), attn_ms], device="cuda", dtype=torch.float64)
+        allr = [torch.zeros_like(mine_t) for _ in range(world)]
+        dist.all_gather(allr, mine_t)
+        per_rank = [{"rank": r, "ms_per_step": float(a[0]), "context_sum": int(a[1]), "attention_ms": float(a[2])}
+                    for r, a in enumerate(allr)]
 
     # ---------------- batch-1 step (the 70%-of-HBM target is stated on batch 1): own graph, rows = 1
     extra = {}
-    if rank == 0:
+    if rank == 0 and not args.no_extras:
         l1 = Layer(nat, kv, dw, 1)
         l1.dx.upload(x[:1])
         longest = int(np.argmax(lens))
@@ -508,10 +714,11 @@ def main():
         for i in range(5):
             assert L.m40llm_cuda_graph_launch(ctx, g1[i % N_WEIGHT_SETS], 1) == 0
         nat.sync(1)
+        reps1 = max(args.steps, 2000)
         ev.start()
-        for i in range(args.steps):
+        for i in range(reps1):
             assert L.m40llm_cuda_graph_launch(ctx, g1[i % N_WEIGHT_SETS], 1) == 0
-        ms1 = ev.stop_ms() / args.steps
+        ms1 = ev.stop_ms() / reps1
         b1 = step_bytes([lens[longest] + 1])
         extra["batch1"] = {"tokens_per_s": 1e3 / ms1, "ms_per_step": ms1, "context": int(lens[longest]) + 1,
                            "algorithmic_bytes": b1, "achieved_gbs": b1 / (ms1 * 1e-3) / 1e9,
@@ -519,16 +726,22 @@ def main():
 
     # ---------------- batch sweep (BASELINE configs[4]): the same layer at 1 / 8 / 32 / 128 / 256 sequences with
     # contexts U[128, 16384], one graph per weight set. Cache contents do not matter for the time (zero-filled at
-    # creation); lengths and positions are what the kernels read.
-    if rank == 0:
+    # creation); lengths and positions are what the kernels read. With N > 1 the 32-, 128- and 256-sequence batches
+    # are dealt to the ranks (strong scaling: the total work is fixed, the slowest rank sets the time).
+    if not args.no_extras:
         sweep = []
         srng = np.random.default_rng(21)
         for sb in (1, 8, 32, 128, 256):
-            slens = srng.integers(128, 16385, size=sb).astype(np.uint32)
-            skv = nat.kv_dense(16384 + 8, sb, KVH, HD)
-            sl = Layer(nat, skv, dw, sb)
-            sl.dx.upload(srng.standard_normal((sb, H), dtype=np.float32))
-            sl.dids.upload(np.arange(sb, dtype=np.uint32))
+            slens_g = srng.integers(128, 16385, size=sb).astype(np.uint32)
+            sx_g = srng.standard_normal((sb, H), dtype=np.float32)
+            if world > 1 and sb < 32:
+                continue
+            sh = pkg.splitk.shard_sequences(slens_g, world, max_per_rank=(sb + world - 1) // world)[rank]
+            slens, n_loc = slens_g[sh], len(sh)
+            skv = nat.kv_dense(16384 + 8, n_loc, KVH, HD)
+            sl = Layer(nat, skv, dw, n_loc)
+            sl.dx.upload(sx_g[sh])
+            sl.dids.upload(np.arange(n_loc, dtype=np.uint32))
             sl.dpos.upload(slens)
             sl.dlens.upload(slens + 1)
             for w in range(N_WEIGHT_SETS):
@@ -537,69 +750,39 @@ def main():
             sg = [sl.capture(w) for w in range(N_WEIGHT_SETS)]
             for i in range(4):
                 assert L.m40llm_cuda_graph_launch(ctx, sg[i % N_WEIGHT_SETS], 1) == 0
-            nat.sync(1)
-            sreps = 100 if sb <= 32 else 30
+            barrier()
+            sreps = 200 if n_loc <= 32 else 60
             ev.start()
             for i in range(sreps):
                 assert L.m40llm_cuda_graph_launch(ctx, sg[i % N_WEIGHT_SETS], 1) == 0
             sms = ev.stop_ms() / sreps
-            sbytes = step_bytes(slens + 1)
-            sweep.append({"batch": sb, "context_sum": int(slens.sum()) + sb, "ms_per_step": sms,
+            sms_all = [sms]
+            if dist is not None:
+                t = torch.tensor([sms], device="cuda", dtype=torch.float64)
+                allr = [torch.zeros_like(t) for _ in range(world)]
+                dist.all_gather(allr, t)
+                sms_all = [float(a[0]) for a in allr]
+                sms = max(sms_all)
+            # bytes the whole job moves per step: every GPU streams the weights, the KV is read once
+            sbytes = step_bytes(slens_g + 1) + (world - 1) * layer_weight_bytes()
+            sweep.append({"batch": sb, "context_sum": int(slens_g.sum()) + sb, "ms_per_step": sms,
                           "tokens_per_s": sb / (sms * 1e-3), "algorithmic_bytes": sbytes,
-                          "frac_of_hbm_peak": sbytes / (sms * 1e-3) / 1e9 / peak})
+                          "frac_of_hbm_peak": sbytes / (sms * 1e-3) / 1e9 / (peak * world),
+                          **({"ms_per_rank": sms_all} if world > 1 else {})})
             for gx in sg:
                 L.m40llm_cuda_graph_destroy(gx)
             L.m40llm_kvcache_destroy(skv)
             for bname in ("dx", "dq", "datt", "dx1", "dx1n", "dhid", "dout", "dids", "dpos", "dlens"):
                 getattr(sl, bname).free()
-        extra["batch_sweep"] = sweep
+        if rank == 0:
+            extra["batch_sweep" if world == 1 else "batch_sweep_strong_scaling"] = sweep
 
-    # ---------------- long-context compressed attention (BASELINE configs[3] shape), rank 0: Qwen2.5-3B heads,
-    # context 32768 in the FP16-K / q4-V cache, 512-token ring, 64-token blocks, top 64. Four caches rotate.
-    if rank == 0:
-        cq, ckv, chd, cL, cR, cbs, ctop = 16, 2, 128, 32768, 512, 64, 64
-        crng = np.random.default_rng(7)
-        caches = []
-        for _ in range(4):
-            c = nat.kv_compressed(cL, 1, ckv, chd, cR, cbs, ctop)
-            nat.kv_fill(c, 0, crng.standard_normal((cL, ckv, chd), dtype=np.float32).astype(np.float16),
-                        crng.standard_normal((cL, ckv, chd), dtype=np.float32).astype(np.float16), final_len=cL)
-            caches.append(c)
-        cdq = nat.buf(crng.standard_normal(cq * chd, dtype=np.float32))
-        cdo = nat.buf(cq * chd * 4)
-        f = L.m40llm_attention_last_token_f32_gqa_block_select_exact_fp16_k_q4_v_old_direct_async
-        for i in range(8):
-            assert f(ctx, caches[i % 4], 0, cdq.ptr, cq, cL, cR, cbs, ctop, cdo.ptr) == 0
-        nat.sync(1)
-        # 16 calls (4 per cache) captured in ONE graph so that the timing is the device's, not the launch path's
-        CALLS = 16
-        assert L.m40llm_cuda_graph_begin_capture(ctx, 1) == 0
-        for i in range(CALLS):
-            assert f(ctx, caches[i % 4], 0, cdq.ptr, cq, cL, cR, cbs, ctop, cdo.ptr) == 0
-        gexec = C.c_void_p()
-        assert L.m40llm_cuda_graph_end_capture(ctx, 1, C.byref(gexec)) == 0 and gexec.value
-        for i in range(3):
-            assert L.m40llm_cuda_graph_launch(ctx, gexec, 1) == 0
-        nat.sync(1)
-        ev.start()
-        creps = 20
-        for i in range(creps):
-            assert L.m40llm_cuda_graph_launch(ctx, gexec, 1) == 0
-        cms = ev.stop_ms() / (creps * CALLS)
-        L.m40llm_cuda_graph_destroy(gexec)
-        old_len = cL - cR
-        # every old K once per kv head; selected q4 V + scales (<= top blocks per q head); the ring K and V
-        cbytes = old_len * ckv * chd * 2 + cq * ctop * cbs * (chd // 2 + 4) + 2 * cR * ckv * chd * 2
-        extra["compressed32k"] = {"ms_per_call": cms, "algorithmic_bytes": cbytes,
-                                  "achieved_gbs": cbytes / (cms * 1e-3) / 1e9,
-                                  "frac_of_hbm_peak": cbytes / (cms * 1e-3) / 1e9 / peak,
-                                  "config": "16/2/128 heads, context 32768, ring 512, block 64, top 64"}
-        for c in caches:
-            L.m40llm_kvcache_destroy(c)
+    if rank == 0 and not args.no_extras:
+        extra["compressed32k"] = compressed_case(nat, ev, peak)
 
     # ---------------- whole-model greedy decode at BASELINE configs[1] (TinyLlama-1.1B shape, batch 1, context 2048):
     # 22 distinct random f16 layers + lm_head, one CUDA graph per token step, ids chosen on the device.
-    if rank == 0:
+    if rank == 0 and not args.no_extras:
         tH, tQ, tKV, tHD, tF, tV, tL, tCTX, tSTEPS = 2048, 32, 4, 64, 5632, 32000, 22, 2048, 96
         g = torch.Generator(device="cuda")
         g.manual_seed(11)
@@ -621,7 +804,7 @@ def main():
             lw.append(W)
         thead = host.ModelHead(rnd(tV, tH, std=0.5), ones.data_ptr(), rnd(tV, tH), tV)
         torch.cuda.synchronize()
-        tkv = nat.kv_dense(tCTX + tSTEPS + 8, tL, tKV, tHD)
+        tkv = nat.kv_dense(tCTX + 3 * tSTEPS + 8, tL, tKV, tHD)
         trng = np.random.default_rng(5)
         for l in range(tL):
             k, v = (trng.standard_normal((tCTX, tKV, tHD), dtype=np.float32).astype(np.float16) for _ in range(2))
@@ -631,15 +814,16 @@ def main():
         tm.generate(4, use_graph=True, want_ids=False)            # eager step + capture + first replays
         nat.sync()
         t0 = time.perf_counter()
-        ids, _ = tm.generate(tSTEPS, use_graph=True)
-        t_tok = (time.perf_counter() - t0) / tSTEPS
-        tbytes = tL * ((2 * tQ * tHD * tH + 2 * tKV * tHD * tH + 3 * tF * tH) * 2 + 2 * (tCTX + tSTEPS // 2) * tKV * tHD * 2) + tV * tH * 2
+        tm.generate(tSTEPS, use_graph=True)
+        tm.generate(tSTEPS, use_graph=True)
+        t_tok = (time.perf_counter() - t0) / (2 * tSTEPS)
+        tbytes = tL * ((2 * tQ * tHD * tH + 2 * tKV * tHD * tH + 3 * tF * tH) * 2 + 2 * (tCTX + tSTEPS) * tKV * tHD * 2) + tV * tH * 2
         extra["tinyllama_c1"] = {"tokens_per_s": 1.0 / t_tok, "ms_per_token": t_tok * 1e3, "layers": tL, "context": tCTX,
-                                 "steps": tSTEPS, "graph_replays": tm.graph_replays(),
+                                 "steps": 2 * tSTEPS, "graph_replays": tm.graph_replays(),
                                  "launches_per_token": tm.launches_per_step(), "algorithmic_bytes_per_token": tbytes,
                                  "achieved_gbs": tbytes / t_tok / 1e9, "frac_of_hbm_peak": tbytes / t_tok / 1e9 / peak,
-                                 "timing": "wall clock around the generate call (graph replays back to back, one "
-                                           "device-to-host read of the ids at the end)"}
+                                 "timing": "wall clock around two generate calls (graph replays back to back, one "
+                                           "device-to-host read of the ids at the end of each)"}
         tm.close()
         L.m40llm_kvcache_destroy(tkv)
         del keep
@@ -648,7 +832,7 @@ def main():
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         O.set_num_threads(len(os.sched_getaffinity(0)))
-        cl = CpuLayer(O, sets, x, lens)
+        cl = CpuLayer(O, sets, gx, glens)
         cl.step(0)
         spent, n = 0.0, 0
         while spent < CPU_BASELINE_SECONDS:
@@ -657,25 +841,42 @@ def main():
         cpu = {"value": n / spent, "unit": "tokens/s", "cores": O.num_threads(), "kind": "port",
                "sample": cl.describe() + f", {n} calls in {spent:.1f} s"}
 
+    if dist is not None:
+        ok = torch.tensor([1.0 if parity["passed"] else 0.0, parity["max_abs_err"]], device="cuda", dtype=torch.float64)
+        dist.all_reduce(ok, op=dist.ReduceOp.MAX)
+        parity["max_abs_err_all_ranks"] = float(ok[1])
+
     if rank == 0:
-        sb = step_bytes(att_lens)
+        # whole-job bytes per step: every GPU streams its own copy of the weights plus its sequences' KV
+        sb = step_bytes(glens + 1) + (world - 1) * layer_weight_bytes()
+        sb0 = step_bytes(att_lens)
         line = {
             "metric": "decode_layer_tokens_per_s", "value": world * B / (ms_step * 1e-3), "unit": "tokens/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
+            "timed_steps": blocks * args.steps,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "f32", "data": "synthetic",
-            "config": workload_config(att_lens, world),
+            "config": workload_config(glens, world),
+            "parity": parity,
             "step_algorithmic_bytes": sb, "step_achieved_gbs": sb / (ms_step * 1e-3) / 1e9,
-            "step_frac_of_hbm_peak": sb / (ms_step * 1e-3) / 1e9 / peak,
-            "roofline": {"kernel": "batched decode attention (attention + split merge)", "bound": "hbm",
-                         "achieved": attn_gbs, "peak": peak, "unit": "GB/s", "frac": attn_gbs / peak,
+            "step_frac_of_hbm_peak": sb / (ms_step * 1e-3) / 1e9 / (peak * world),
+            "warm_l2": {"ms_per_step": ms_step_warm, "step_frac_of_hbm_peak": sb0 / (ms_step_warm * 1e-3) / 1e9 / peak,
+                        "note": "rank 0, one weight set replayed back to back (no rotation); the headline rotates "
+                                f"{N_WEIGHT_SETS} sets so that no weight byte is reused from L2"},
+            "roofline": {"kernel": "batched decode attention (attention + split merge), rank 0's sequences",
+                         "bound": "hbm", "achieved": attn_gbs, "peak": peak, "unit": "GB/s", "frac": attn_gbs / peak,
                          "peak_kind": f"of {peak_kind}", "algorithmic_bytes": attn_bytes, "ms_per_launch": attn_ms,
+                         "launches_timed": reps,
                          "traffic": None if NCU_TRAFFIC_RATIO is None else NCU_TRAFFIC_RATIO * attn_bytes},
             "e2e": {"value": world * B / e2e_s, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "graph_replays": e2e_replays},
-            "gpu_launches": per_step_launches * args.steps,
+                    "graph_replays": e2e_replays, "timed_steps": args.steps * e2e_blocks,
+                    "max_abs_diff_vs_device_resident_step": e2e_err},
+            "gpu_launches": per_step_launches * args.steps * blocks,
+            "launches_per_step": per_step_launches,
             "clocks": clocks,
         }
+        if per_rank is not None:
+            line["per_rank"] = per_rank
         line.update(extra)
         if cpu is not None:
             line["cpu_baseline"] = cpu

@@ -36,6 +36,8 @@ typedef struct M40llmCudaEvent M40llmCudaEvent;
 #define M40LLM_ERR_UNSUPPORTED (-100)
 /* Returned by the additive entry points when a size exceeds a documented limit. */
 #define M40LLM_ERR_LIMIT (-101)
+/* Returned by the allocation-free entry point when the address of its fixed device array cannot be looked up. */
+#define M40LLM_ERR_SYMBOL (-102)
 
 /* Telemetry structs, src/cuda.rs:46-85 <-> cuda/kernels.cu:84-115. */
 typedef struct { float prob_mass, logit_max, logit_mean; uint32_t count; } M40llmAttentionGroupStats;
@@ -422,7 +424,8 @@ int m40llm_kvcache_debug_write_range(M40llmCudaContext* ctx, M40llmKVCache* kv, 
 int m40llm_kvcache_debug_read_old_token(M40llmCudaContext* ctx, M40llmKVCache* kv, uint32_t seq_id, uint32_t token,
                                         void* out_k_f16, void* out_q4_v, float* out_scale);
 /* Device error word of the context: bit 0 = a batched-attention row carried an out-of-range
- * sequence id or length and was skipped. Reading clears it. */
+ * sequence id or length and was skipped (no cache data is read for it and its output row is written as zeros,
+ * whatever the number of splits). Reading clears it. */
 int m40llm_context_take_device_status(M40llmCudaContext* ctx, uint32_t* out_status);
 /* Stream-ordered host <-> device copies on one of the context's streams (the reference only has the synchronous
  * m40llm_memcpy_h2d / _d2h, cuda/kernels.cu). The host buffer must stay valid until the stream has passed the copy;
@@ -454,14 +457,22 @@ int m40llm_advance_positions_async(M40llmCudaContext* ctx, uint32_t* d_positions
  * fixed 4 MiB device array that belongs to the loaded library. For callers that cannot take an allocating call (all
  * HBM already given to a KV pool; code that must not enter the allocator or its implicit device synchronisation).
  * The first call on each device looks up the array's address (cudaGetSymbolAddress) and should come before any
- * stream capture. Returns M40LLM_ERR_LIMIT when q_heads * splits * (2 + head_dim) floats exceed 2^20,
- * M40LLM_ERR_UNSUPPORTED for head_dim other than 64/128 or more than 16 q heads per kv head. All calls on a device
- * share the array: calls that overlap in time (other streams, other contexts) race and must be serialised. */
+ * stream capture; the first call per head shape on a device also raises that kernel's shared-memory limit
+ * (cudaFuncSetAttribute), which allocates nothing either. Returns M40LLM_ERR_LIMIT when
+ * q_heads * splits * (2 + head_dim) floats exceed 2^20; M40LLM_ERR_UNSUPPORTED for head_dim other than 64/128, more
+ * than 16 q heads per kv head, or a d_q_f32 that is not 8-byte aligned; M40LLM_ERR_SYMBOL when the array's address
+ * cannot be looked up (a CUDA runtime failure, printed to stderr). All calls on a device share the array: calls
+ * that overlap in time (other streams, other contexts) race and must be serialised. */
 int m40llm_attention_last_token_f32_gqa_static_async(M40llmCudaContext* ctx, const M40llmKVCache* kv,
                                                      uint32_t seq_id, const void* d_q_f32, uint32_t q_heads,
                                                      uint32_t seq_len, void* d_out_f32);
 /* Number of kernels this library has launched on `ctx` since creation (launch accounting for benchmarks). */
 int m40llm_context_launch_count(M40llmCudaContext* ctx, uint64_t* out_count);
+/* How many times a scratch arena of `ctx` has grown since creation. Growth happens only in eager (uncaptured)
+ * calls; an arena that was outgrown stays allocated until the context is destroyed, so a CUDA graph captured
+ * earlier keeps working on the memory it was captured with. A harness can watch this counter to see that a call
+ * allocated. */
+int m40llm_context_scratch_generation(M40llmCudaContext* ctx, uint64_t* out_generation);
 /* The raw CUDA stream handle of a stream kind, for harnesses that time with their own events. */
 int m40llm_context_stream_handle(M40llmCudaContext* ctx, uint32_t stream_kind, void** out_stream);
 

@@ -28,7 +28,10 @@ __global__ void __launch_bounds__(128) attn_decode_generic_kernel(DenseAttnArgs 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
     const uint32_t hd = a.hd, G = a.q_heads / a.kv_heads;
     uint32_t seq = 0, t0 = 0, t1 = 0;
-    if (!attn_resolve_row(a, row, split, &seq, &t0, &t1)) return;
+    if (!attn_resolve_row(a, row, split, &seq, &t0, &t1)) {
+        attn_write_rejected_row(a, row, split, kvh, a.write_partials || a.splits > 1);
+        return;
+    }
     const __half* Kh = a.K + kv_row_offset(seq, kvh, 0, a.kv_heads, a.max_seq_len, hd);
     const __half* Vh = a.V + kv_row_offset(seq, kvh, 0, a.kv_heads, a.max_seq_len, hd);
     float* sm_m = sm;                    // [4][GC]

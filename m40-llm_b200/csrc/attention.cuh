@@ -80,3 +80,21 @@ __device__ __forceinline__ bool attn_resolve_row(const DenseAttnArgs& a, uint32_
     *t1 = se > *t0 ? se : *t0;
     return true;
 }
+
+// A row whose sequence id or length is out of range reads no cache data. So that its output never depends on
+// what the partial arena held before, every CTA of the row still leaves a defined result: an empty partial
+// (l = 0, which the merge kernels turn into a zero row) when partials are in use, zeros in `out` otherwise.
+__device__ __forceinline__ void attn_write_rejected_row(const DenseAttnArgs& a, uint32_t row, uint32_t split,
+                                                        uint32_t kvh, bool partial) {
+    const uint32_t G = a.q_heads / a.kv_heads;
+    if (partial) {
+        for (uint32_t i = threadIdx.x; i < G; i += blockDim.x) {
+            const size_t pi = ((size_t)row * a.q_heads + kvh * G + i) * a.splits + split;
+            a.part_m[pi] = -INFINITY;
+            a.part_l[pi] = 0.0f;
+        }
+    } else {
+        for (uint32_t i = threadIdx.x; i < G * a.hd; i += blockDim.x)
+            a.out[((size_t)row * a.q_heads + kvh * G) * a.hd + i] = 0.0f;
+    }
+}

@@ -16,9 +16,10 @@
 //     different streams or contexts of the same device overwrite each other's partials: callers serialise them;
 //   * the array's device address is looked up with cudaGetSymbolAddress the first time a device is used, with
 //     that device current. That first call per device is the set-up call and should be made before any stream
-//     capture begins; later calls only launch kernels;
-//   * only the shapes of the tiled kernel are taken (head_dim 64 or 128, at most 16 q heads per kv head);
-//     others get M40LLM_ERR_UNSUPPORTED.
+//     capture begins. The first call per head shape on a device also raises that kernel's shared-memory limit
+//     (cudaFuncSetAttribute; no allocation). Later calls only launch kernels;
+//   * only the shapes of the tiled kernel are taken (head_dim 64 or 128, at most 16 q heads per kv head, q
+//     8-byte aligned); others get M40LLM_ERR_UNSUPPORTED.
 #include "attention.cuh"
 
 #include <mutex>
@@ -43,7 +44,7 @@ int static_partials(M40llmCudaContext* ctx, float** out) {
         if (e != cudaSuccess || !p) {
             fprintf(stderr, "m40llm: cudaGetSymbolAddress(static attention partials) failed on device %d: %s\n", dev,
                     cudaGetErrorString(e));
-            return -4;
+            return M40LLM_ERR_SYMBOL;
         }
         g_partials_addr[dev] = (float*)p;
     }

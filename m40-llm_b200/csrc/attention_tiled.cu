@@ -13,6 +13,8 @@
 // synchronisation per tile is the pipeline hand-over.
 #include "attention.cuh"
 
+#include <atomic>
+
 namespace {
 
 constexpr int TILE = 64;
@@ -86,8 +88,11 @@ __global__ void __launch_bounds__(128, 2) attn_decode_tiled_kernel(DenseAttnArgs
     const uint32_t g = lane >> 2, t4 = lane & 3u;
     const uint32_t G = a.q_heads / a.kv_heads;
     uint32_t seq = 0, t0 = 0, t1 = 0;
-    if (!attn_resolve_row(a, row, split, &seq, &t0, &t1)) return;
     const bool partial = a.write_partials || a.splits > 1;
+    if (!attn_resolve_row(a, row, split, &seq, &t0, &t1)) {
+        attn_write_rejected_row(a, row, split, kvh, partial);
+        return;
+    }
     if (t0 >= t1) {  // nothing in this chunk: an empty partial (l = 0) that the merge ignores
         if (partial) {
             for (uint32_t i = tid; i < G; i += blockDim.x) {
@@ -286,12 +291,14 @@ __global__ void __launch_bounds__(128, 2) attn_decode_tiled_kernel(DenseAttnArgs
 template <int HD, bool G_HI>
 int launch(M40llmCudaContext* ctx, const DenseAttnArgs& a, uint32_t rows) {
     auto kern = attn_decode_tiled_kernel<HD, G_HI>;
-    static unsigned long long configured = 0ull;  // per-device bit: the attribute is per device
+    // per-device bit: the attribute is per device. Contexts on several threads may race to set it; setting it twice
+    // is harmless, losing a bit is not, hence the atomic.
+    static std::atomic<unsigned long long> configured{0ull};
     const unsigned long long bit = 1ull << (ctx->device_id & 63);
-    if (!(configured & bit)) {
+    if (!(configured.load(std::memory_order_acquire) & bit)) {
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, TiledCfg<HD>::SMEM) != cudaSuccess)
             return -4;
-        configured |= bit;
+        configured.fetch_or(bit, std::memory_order_release);
     }
     dim3 grid(a.splits, a.kv_heads, rows);
     const cudaError_t e = m40_launch_dependent(kern, grid, dim3(128), (size_t)TiledCfg<HD>::SMEM, ctx->decode_stream, a);

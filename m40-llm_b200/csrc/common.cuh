@@ -14,6 +14,11 @@
 // events, a growable scratch arena and a device status word.
 // Mirrors the handle of cuda/kernels.cu:25-37 in the reference.
 // ----------------------------------------------------------------------------
+struct M40RetiredArena {
+    void* ptr;
+    M40RetiredArena* next;
+};
+
 struct M40llmCudaContext {
     int device_id;
     int sm_count;
@@ -27,9 +32,13 @@ struct M40llmCudaContext {
     // streams never shares scratch; level 0 belongs to leaf operations (GEMM partials and
     // activation copies, attention partials), level 1 to composite operations that call leaf
     // operations while their own temporaries are live (the fused attention prologue).
-    // Grown (never shrunk) outside of stream capture by m40_ensure_scratch().
+    // Grown (never shrunk) outside of stream capture by m40_ensure_scratch(). An arena that was outgrown is kept
+    // on the `retired` list until the context dies, because captured graphs may still point into it;
+    // `scratch_generation` counts the growths.
     void* scratch[2][2];
     size_t scratch_bytes[2][2];
+    M40RetiredArena* retired;
+    unsigned long long scratch_generation;
     // Last block selection (u32 [q_heads][64] + f32 scores), for the debug read-back.
     uint32_t* d_selected_blocks;
     float* d_selected_scores;
@@ -107,9 +116,9 @@ static inline cudaStream_t m40_stream(M40llmCudaContext* ctx, uint32_t kind) {
 }
 
 // Returns a scratch pointer of at least `bytes` for the given stream kind, growing the
-// arena when needed. Growth frees the old arena after synchronising that stream, so it
-// must not happen during stream capture: callers that may be captured size their needs
-// from static bounds so the arena is already large enough after the first call.
+// arena when needed. Growth allocates (cudaMalloc), so it must not happen during stream
+// capture and returns null there: a configuration runs eagerly once before it is captured.
+// The outgrown arena stays allocated (retired) so that graphs captured against it remain valid.
 void* m40_ensure_scratch(M40llmCudaContext* ctx, uint32_t kind, size_t bytes, uint32_t level = 0);
 
 #define M40_COUNT_LAUNCH(ctx) ((ctx)->launches++)

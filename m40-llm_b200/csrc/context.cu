@@ -12,21 +12,31 @@ void* m40_ensure_scratch(M40llmCudaContext* ctx, uint32_t kind, size_t bytes, ui
     cudaStream_t s = m40_stream(ctx, kind);
     cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
     if (cudaStreamIsCapturing(s, &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone) return nullptr;
+    // Grow at least geometrically so that the arenas retired below add up to less than the live one.
     size_t want = bytes < (size_t)(8u << 20) ? (size_t)(8u << 20) : bytes;
+    if (want < 2 * ctx->scratch_bytes[kind][level]) want = 2 * ctx->scratch_bytes[kind][level];
     want = (want + ((size_t)1 << 20) - 1) & ~(((size_t)1 << 20) - 1);
-    if (ctx->scratch[kind][level]) {
-        cudaStreamSynchronize(s);
-        cudaFree(ctx->scratch[kind][level]);
-        ctx->scratch[kind][level] = nullptr;
-        ctx->scratch_bytes[kind][level] = 0;
-    }
     void* p = nullptr;
     if (cudaMalloc(&p, want) != cudaSuccess) {
         cudaGetLastError();
         return nullptr;
     }
+    if (ctx->scratch[kind][level]) {
+        // A CUDA graph captured earlier has the old arena's addresses baked into its kernel arguments and may be
+        // replayed at any later time, so the old arena is retired, not freed: it stays valid (and private to
+        // those graphs, which only ever use it consistently) until the context is destroyed.
+        M40RetiredArena* r = (M40RetiredArena*)malloc(sizeof(M40RetiredArena));
+        if (!r) {
+            cudaFree(p);
+            return nullptr;
+        }
+        r->ptr = ctx->scratch[kind][level];
+        r->next = ctx->retired;
+        ctx->retired = r;
+    }
     ctx->scratch[kind][level] = p;
     ctx->scratch_bytes[kind][level] = want;
+    ctx->scratch_generation++;
     return p;
 }
 
@@ -99,6 +109,12 @@ void m40llm_destroy_context(M40llmCudaContext* ctx) {
     for (int k = 0; k < 2; ++k)
         for (int l = 0; l < 2; ++l)
             if (ctx->scratch[k][l]) cudaFree(ctx->scratch[k][l]);
+    while (ctx->retired) {
+        M40RetiredArena* r = ctx->retired;
+        ctx->retired = r->next;
+        cudaFree(r->ptr);
+        free(r);
+    }
     if (ctx->d_status) cudaFree(ctx->d_status);
     if (ctx->d_selected_blocks) cudaFree(ctx->d_selected_blocks);
     if (ctx->d_selected_scores) cudaFree(ctx->d_selected_scores);
@@ -379,6 +395,12 @@ int m40llm_context_take_device_status(M40llmCudaContext* ctx, uint32_t* out_stat
 int m40llm_context_launch_count(M40llmCudaContext* ctx, uint64_t* out_count) {
     if (!ctx || !out_count) return -1;
     *out_count = (uint64_t)ctx->launches;
+    return 0;
+}
+
+int m40llm_context_scratch_generation(M40llmCudaContext* ctx, uint64_t* out_generation) {
+    if (!ctx || !out_generation) return -1;
+    *out_generation = (uint64_t)ctx->scratch_generation;
     return 0;
 }
 

@@ -111,8 +111,14 @@ bool dev_alloc_zero(T** p, size_t count) {
     return cudaMemset(*p, 0, count * sizeof(T)) == cudaSuccess;
 }
 
-int read_current_len(M40llmKVCache* kv, uint32_t seq_id, uint32_t* out) {
-    return cudaMemcpy(out, kv->d_seq_map + seq_id, sizeof(uint32_t), cudaMemcpyDeviceToHost) == cudaSuccess ? 0 : -1;
+// The host reads the sequence's length to choose the slot of the new token (cuda/kernels.cu reads it with a blocking
+// cudaMemcpy, which on the reference's blocking streams waits for an append still in flight). The streams here are
+// non-blocking, so the read rides the decode stream, where every append writes the length, and waits for it: two
+// appends issued back to back see each other.
+int read_current_len(M40llmCudaContext* ctx, M40llmKVCache* kv, uint32_t seq_id, uint32_t* out) {
+    cudaStream_t s = ctx->decode_stream;
+    if (cudaMemcpyAsync(out, kv->d_seq_map + seq_id, sizeof(uint32_t), cudaMemcpyDeviceToHost, s) != cudaSuccess) return -1;
+    return cudaStreamSynchronize(s) == cudaSuccess ? 0 : -1;
 }
 
 }  // namespace
@@ -223,7 +229,7 @@ int m40llm_kvcache_append_token(M40llmCudaContext* ctx, M40llmKVCache* kv, uint3
     if (seq_id >= kv->max_batch_size) return -2;
     if (m40_ensure_device(ctx) != 0 || !kv->d_k) return -3;
     uint32_t cur = 0;
-    if (read_current_len(kv, seq_id, &cur) != 0) return -3;
+    if (read_current_len(ctx, kv, seq_id, &cur) != 0) return -3;
     if (cur >= kv->max_seq_len) return -4;
     dense_append_f16_kernel<<<kv->num_heads, 128, 0, ctx->decode_stream>>>(
         (const __half*)k_dev, (const __half*)v_dev, kv->d_k, kv->d_v, seq_id, kv->max_seq_len, kv->num_heads,
@@ -243,7 +249,7 @@ int m40llm_kvcache_append_token_f32_async(M40llmCudaContext* ctx, M40llmKVCache*
     if (seq_id >= kv->max_batch_size) return -2;
     if (m40_ensure_device(ctx) != 0 || !kv->d_k) return -3;
     uint32_t cur = 0;
-    if (read_current_len(kv, seq_id, &cur) != 0) return -3;
+    if (read_current_len(ctx, kv, seq_id, &cur) != 0) return -3;
     if (cur >= kv->max_seq_len) return -4;
     dense_append_kernel<<<kv->num_heads, 64, 0, ctx->decode_stream>>>(
         (const float*)k_dev_f32, (const float*)v_dev_f32, kv->d_k, kv->d_v, kv->d_seq_map, seq_id, kv->max_seq_len,
@@ -269,7 +275,7 @@ int m40llm_kvcache_append_token_f32_rope_k_layout_async(M40llmCudaContext* ctx, 
     if (kv->head_dim % 2 != 0) return -4;
     if (m40_ensure_device(ctx) != 0 || !kv->d_k) return -5;
     uint32_t cur = 0;
-    if (read_current_len(kv, seq_id, &cur) != 0) return -5;
+    if (read_current_len(ctx, kv, seq_id, &cur) != 0) return -5;
     if (cur >= kv->max_seq_len) return -6;
     dense_append_kernel<<<kv->num_heads, 64, 0, ctx->decode_stream>>>(
         (const float*)k_dev_f32, (const float*)v_dev_f32, kv->d_k, kv->d_v, kv->d_seq_map, seq_id, kv->max_seq_len,

@@ -54,14 +54,21 @@ def token_ranges(seq_len: int, world: int, align: int = 64) -> list[tuple[int, i
     return [(min(b * align, seq_len), min(e * align, seq_len)) for b, e in block_ranges(tiles, world)]
 
 
-def shard_sequences(context_lens: Sequence[int], world: int) -> list[list[int]]:
+def shard_sequences(context_lens: Sequence[int], world: int, max_per_rank: int | None = None) -> list[list[int]]:
     """Deals independent sequences to ranks, longest first onto the least-loaded rank (decode attention cost is
-    linear in context length). Returns the sequence indices of every rank, each list in ascending order."""
+    linear in context length). `max_per_rank` caps the number of sequences a rank takes (the projections cost per
+    row, so a scheduler keeps row counts equal while balancing tokens); full ranks are skipped. Returns the sequence
+    indices of every rank, each list in ascending order."""
+    if world <= 0:
+        raise ValueError("world must be > 0")
+    if max_per_rank is not None and max_per_rank * world < len(context_lens):
+        raise ValueError("max_per_rank * world is smaller than the number of sequences")
     loads = [0] * world
     out: list[list[int]] = [[] for _ in range(world)]
     order = sorted(range(len(context_lens)), key=lambda i: (-int(context_lens[i]), i))
     for i in order:
-        r = min(range(world), key=lambda j: (loads[j], j))
+        open_ranks = [j for j in range(world) if max_per_rank is None or len(out[j]) < max_per_rank]
+        r = min(open_ranks, key=lambda j: (loads[j], j))
         out[r].append(i)
         loads[r] += int(context_lens[i])
     return [sorted(s) for s in out]

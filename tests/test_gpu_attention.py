@@ -148,3 +148,44 @@ def test_argument_errors(nat):
     assert L.m40llm_attention_last_token_f32_gqa_dense_recent_async(nat.ctx, kv, 0, q.ptr, 8, 4, 2, q.ptr) == -100
     L.m40llm_kvcache_destroy(kv)
     nat.free_all()
+
+
+@pytest.mark.parametrize("max_seq,hd", [(64, 64), (4096, 128), (2048, 48)])
+def test_batched_async_rejected_row_is_zero_and_flagged(nat, O, max_seq, hd):
+    """The async batched call cannot return a per-row code: a row whose length or slot is out of range reads no
+    cache data, raises status bit 1 and gets a zero output row whether the launch uses one split (short cache), many
+    (long cache) or the generic kernel (head_dim 48); the other rows are unaffected. The output buffer is poisoned
+    first and the arena is dirtied by a previous call so that stale partials would show."""
+    rng = np.random.default_rng(max_seq)
+    qh, kvh, B = 8, 2, 4
+    kv = nat.kv_dense(max_seq, B, kvh, hd)
+    lens = np.array([max_seq, 17, max_seq - 3, 5], np.uint32)
+    K = np.zeros((B, max_seq, kvh, hd), np.float16)
+    V = np.zeros((B, max_seq, kvh, hd), np.float16)
+    for b in range(B):
+        K[b, :lens[b]] = rng.standard_normal((lens[b], kvh, hd)).astype(np.float16)
+        V[b, :lens[b]] = rng.standard_normal((lens[b], kvh, hd)).astype(np.float16)
+        nat.kv_fill(kv, b, K[b, :lens[b]], V[b, :lens[b]])
+    q = rng.standard_normal((B, qh, hd)).astype(np.float32)
+    ids = np.arange(B, dtype=np.uint32)
+    dq, do, dids, dlens = nat.buf(q), nat.buf(q.nbytes), nat.buf(ids), nat.buf(lens)
+    f = nat.lib.m40llm_attention_last_token_f32_gqa_batched_async
+    assert f(nat.ctx, kv, dids.ptr, dlens.ptr, B, dq.ptr, qh, do.ptr) == 0  # fills the partial arena with real data
+    nat.sync(1)
+    good = do.download(np.float32, q.shape)
+    assert_close(good, O.attention_gqa_batched(K, V, ids, lens, q, qh), what="clean batch")
+    for bad_row, bad_len, bad_id in ((2, max_seq + 1, 2), (0, 0, 0), (1, 17, B + 3)):
+        l2, i2 = lens.copy(), ids.copy()
+        l2[bad_row], i2[bad_row] = bad_len, bad_id
+        dlens.upload(l2)
+        dids.upload(i2)
+        do.upload(np.full(q.shape, 7.0, np.float32))
+        assert f(nat.ctx, kv, dids.ptr, dlens.ptr, B, dq.ptr, qh, do.ptr) == 0
+        st = np.zeros(1, np.uint32)
+        assert nat.lib.m40llm_context_take_device_status(nat.ctx, st.ctypes.data) == 0 and st[0] == 1
+        got = do.download(np.float32, q.shape)
+        assert np.all(got[bad_row] == 0.0), f"rejected row {bad_row} not zero"
+        keep = [b for b in range(B) if b != bad_row]
+        assert np.array_equal(got[keep], good[keep])
+    nat.lib.m40llm_kvcache_destroy(kv)
+    nat.free_all()

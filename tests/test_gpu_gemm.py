@@ -67,7 +67,9 @@ def test_materialize_and_f32_gemm(nat, O):
 @pytest.mark.parametrize("M,N,K", [(1, 8, 32), (1, 64, 128), (1, 4096, 4096), (3, 1000, 1024), (1, 4096, 14336), (8, 512, 4096),
                                    # batched rows: the tcgen05 Q8_0 path (K % 256 == 0), incl. N tails, row chunks of 64
                                    (2, 128, 256), (16, 8, 256), (17, 300, 512), (32, 4096, 4096), (32, 4096, 14336), (64, 256, 1024),
-                                   (65, 128, 256), (100, 520, 768), (32, 14336, 4096), (5, 200, 384)])
+                                   (65, 128, 256), (100, 520, 768), (32, 14336, 4096), (5, 200, 384),
+                                   # 2-4 chained 64-row passes sharing one arena (the batch sweep's 128 and 256 rows)
+                                   (128, 4096, 4096), (256, 512, 1024), (129, 256, 512), (256, 4096, 14336)])
 def test_gemm_q80(nat, O, M, N, K):
     rng = np.random.default_rng(M + N + K)
     a = rng.standard_normal((M, K)).astype(np.float32)
@@ -82,6 +84,8 @@ def test_gemm_q80(nat, O, M, N, K):
 
 @pytest.mark.parametrize("rows,H,F,q80", [(1, 256, 384, True), (1, 4096, 14336, True), (4, 1024, 2816, True),
                                            (32, 4096, 14336, True), (8, 256, 512, True), (70, 512, 1024, True), (32, 2048, 5632, False),
+                                           (128, 1024, 2816, True), (256, 512, 1024, True), (65, 512, 1024, True),
+                                           (128, 4096, 14336, True), (256, 2048, 5632, False),
                                            (1, 2048, 5632, False), (3, 512, 1024, False)])
 def test_ffn_swiglu(nat, O, rows, H, F, q80):
     """hid = silu(x.Wg) * (x.Wu); out = residual + hid.Wd  (src/infer/gemm.rs:91-163 + kernels.cu:880-891)."""

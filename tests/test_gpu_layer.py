@@ -244,3 +244,126 @@ def test_host_layer_driver_compressed_mode(nat, O, pkg):
     layer.close()
     nat.lib.m40llm_kvcache_destroy(kv)
     nat.free_all()
+
+
+def test_graph_replay_survives_scratch_growth(O, pkg):
+    """A captured layer graph has the scratch arena's addresses baked in. A later eager call that needs a larger
+    arena must not invalidate it: small batch with graph -> a call that outgrows the arena -> the small batch's graph
+    again, every step against the oracle. Runs on a context of its own so that the arena starts at its initial size."""
+    import helpers
+
+    own = helpers.Native(pkg.native.lib())
+    try:
+        rng = np.random.default_rng(15)
+        H, qh, kvh, hd, F = 512, 8, 2, 64, 1024
+        cfg = O.LayerCfg(H, qh, kvh, hd, F, 1, 0, 1e-5, 1e4, 1.0)
+        w = make_weights(O, rng, H, qh, kvh, hd, F, True, False)
+        W = _host_weights(pkg, own, w, True)
+        lens = [300, 7, 130, 65]
+        max_seq = 320
+        kv = own.kv_dense(max_seq, 4, kvh, hd)
+        Ks = [np.zeros((max_seq, kvh, hd), np.float16) for _ in lens]
+        Vs = [np.zeros((max_seq, kvh, hd), np.float16) for _ in lens]
+        for b, n in enumerate(lens):
+            Ks[b][:n] = rng.standard_normal((n, kvh, hd)).astype(np.float16)
+            Vs[b][:n] = rng.standard_normal((n, kvh, hd)).astype(np.float16)
+            own.kv_fill(kv, b, Ks[b][:n], Vs[b][:n])
+        layer = pkg.host.DecodeLayer(own.ctx, pkg.host.LayerCfg(H, qh, kvh, hd, F, 0, 1e-5, 1e4, 1.0), 4)
+        x = rng.standard_normal((4, H)).astype(np.float32)
+
+        def generation():
+            g = np.zeros(1, np.uint64)
+            assert own.lib.m40llm_context_scratch_generation(own.ctx, g.ctypes.data) == 0
+            return int(g[0])
+
+        def step(i):
+            nonlocal x
+            reqs = [(b, b, lens[b] + i + 1, True) for b in range(4)]
+            out = layer.forward_host(kv, W, pkg.host.dense_kv_cfg(), reqs, x, use_graph=True)
+            for b in range(4):
+                eout, _, _ = O.decode_layer(cfg, x[b], w, Ks[b], Vs[b], lens[b] + i)
+                assert_close(out[b], eout, what=f"step {i} row {b}")
+            x = out.copy()
+
+        step(0)  # eager + capture
+        step(1)  # replay
+        assert layer.graph_replays() == 1
+        g0 = generation()
+        # 256 rows x 64 q heads x 8 splits x (2 + 64) floats of attention partials = 34.6 MB > the 32 MB arena
+        big_rows, bq, bkv, bhd, bmax = 256, 64, 4, 64, 8192
+        big = own.kv_dense(bmax, big_rows, bkv, bhd)
+        dq = own.buf(rng.standard_normal((big_rows, bq * bhd)).astype(np.float32))
+        do = own.buf(big_rows * bq * bhd * 4)
+        dids = own.buf(np.arange(big_rows, dtype=np.uint32))
+        dlens = own.buf(np.full(big_rows, bmax, np.uint32))
+        assert own.lib.m40llm_attention_last_token_f32_gqa_batched_async(own.ctx, big, dids.ptr, dlens.ptr, big_rows,
+                                                                         dq.ptr, bq, do.ptr) == 0
+        own.sync(1)
+        assert generation() > g0, "the large call was meant to outgrow the scratch arena"
+        step(2)  # replays the graph captured against the old arena
+        step(3)
+        assert layer.graph_replays() == 3
+        layer.close()
+        own.lib.m40llm_kvcache_destroy(big)
+        own.lib.m40llm_kvcache_destroy(kv)
+    finally:
+        own.free_all()
+        own.lib.m40llm_destroy_context(own.ctx)
+
+
+def _batched_layer_case(nat, O, H, qh, kvh, hd, F, base, lens, fused_tail, seed, check_rows=None):
+    """Fills a dense cache with `lens[b] - 1` random tokens per sequence, runs the batched layer for one new token per
+    sequence and compares rows (all, or `check_rows`) with the oracle's single-sequence layer, including the K/V row
+    the prologue appended."""
+    rng = np.random.default_rng(seed)
+    cfg = O.LayerCfg(H, qh, kvh, hd, F, 1, 0, 1e-5, base, 1.0)
+    w = make_weights(O, rng, H, qh, kvh, hd, F, True, False)
+    B, max_seq = len(lens), max(lens) + 2
+    kv = nat.kv_dense(max_seq, B, kvh, hd)
+    pre = {}
+    for b, n in enumerate(lens):
+        k = rng.standard_normal((n - 1, kvh, hd), dtype=np.float32).astype(np.float16)
+        v = rng.standard_normal((n - 1, kvh, hd), dtype=np.float32).astype(np.float16)
+        if n > 1:
+            nat.kv_fill(kv, b, k, v)
+        pre[b] = (k, v)
+    x = rng.standard_normal((B, H)).astype(np.float32)
+    out, q_rot, att = device_layer(nat, kv, w, x, list(range(B)), [n - 1 for n in lens], cfg, True, fused_tail)
+    for b in (range(B) if check_rows is None else check_rows):
+        n = lens[b]
+        K = np.zeros((n + 1, kvh, hd), np.float16)
+        V = np.zeros((n + 1, kvh, hd), np.float16)
+        K[:n - 1], V[:n - 1] = pre[b]
+        eout, eq, eatt = O.decode_layer(cfg, x[b], w, K, V, n - 1)
+        assert_close(q_rot[b], eq, what=f"row {b} q after rope")
+        assert_close(att[b], eatt, what=f"row {b} attention")
+        assert_close(out[b], eout, what=f"row {b} output")
+        k_dev, v_dev = np.zeros((kvh, hd), np.float16), np.zeros((kvh, hd), np.float16)
+        assert nat.lib.m40llm_kvcache_debug_read_token(nat.ctx, kv, b, n - 1, k_dev.ctypes.data_as(C.c_void_p),
+                                                       v_dev.ctypes.data_as(C.c_void_p)) == 0
+        assert_close(k_dev.astype(np.float32), K[n - 1].astype(np.float32), what=f"row {b} appended k")
+        assert_close(v_dev.astype(np.float32), V[n - 1].astype(np.float32), what=f"row {b} appended v")
+    st = np.zeros(1, np.uint32)
+    assert nat.lib.m40llm_context_take_device_status(nat.ctx, st.ctypes.data) == 0 and st[0] == 0
+    nat.lib.m40llm_kvcache_destroy(kv)
+    nat.free_all()
+
+
+@pytest.mark.parametrize("fused_tail", [False, True])
+def test_llama3_8b_layer_32_rows(nat, O, fused_tail):
+    """The configuration the benchmark is quoted on, as a whole: hidden 4096, 32/8 heads of 128, Q8_0 FFN 14336,
+    RoPE theta 5e5 applied by the projection's epilogue, 32 rows with contexts between 512 and 8192."""
+    lens = [int(n) for n in np.random.default_rng(0).integers(512, 8193, size=32)]
+    lens[3], lens[17] = 512, 8192
+    _batched_layer_case(nat, O, 4096, 32, 8, 128, 14336, 5e5, lens, fused_tail, seed=4096 + 32)
+
+
+@pytest.mark.parametrize("rows,H,qh,kvh,hd,F", [(65, 512, 8, 2, 64, 1024),      # a trailing single row after a 64-row pass
+                                                 (128, 1024, 8, 2, 128, 2816),   # two passes, head_dim 128 epilogue
+                                                 (256, 512, 4, 1, 128, 768)])    # four passes
+def test_batched_layer_many_rows(nat, O, rows, H, qh, kvh, hd, F):
+    """Row counts of the batch sweep (128, 256) and the 64k+1 case, where the FFN norm cannot ride on the tensor-core
+    path's activation split; every 7th row and the last are compared."""
+    lens = [int(n) for n in np.random.default_rng(rows).integers(1, 300, size=rows)]
+    rows_to_check = sorted(set(range(0, rows, 7)) | {rows - 1, 63, 64})
+    _batched_layer_case(nat, O, H, qh, kvh, hd, F, 5e5, lens, True, seed=rows, check_rows=rows_to_check)

@@ -50,6 +50,15 @@ def test_shard_sequences_balances_contexts():
         assert max(loads) - min(loads) <= int(lens.max())      # longest-first greedy bound
         assert max(loads) <= 1.02 * sum(loads) / w
     assert splitk.shard_sequences([5, 5, 5], 2) == [[0, 2], [1]]
+    # equal row counts per rank (the weak-scaling deal: 32 sequences each) still balance the tokens
+    for w in (2, 4, 8):
+        lens = rng.integers(512, 8193, size=32 * w)
+        shards = splitk.shard_sequences(lens, w, max_per_rank=32)
+        assert all(len(s) == 32 for s in shards) and sorted(i for s in shards for i in s) == list(range(32 * w))
+        loads = [int(lens[s].sum()) for s in shards]
+        assert max(loads) <= 1.01 * sum(loads) / w
+    with pytest.raises(ValueError):
+        splitk.shard_sequences([1, 2, 3], 2, max_per_rank=1)
     assert splitk.shard_sequences([], 2) == [[], []]
 
 

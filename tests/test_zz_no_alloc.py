@@ -11,6 +11,12 @@ pytestmark = pytest.mark.gpu
 ERR_UNSUPPORTED, ERR_LIMIT = -100, -101
 
 
+def scratch_generation(nat):
+    g = np.zeros(1, np.uint64)
+    assert nat.lib.m40llm_context_scratch_generation(nat.ctx, g.ctypes.data) == 0
+    return int(g[0])
+
+
 def both(nat, kv, seq, q, qh, L):
     """(regular entry point, static entry point) outputs for the same call."""
     dq, d_ref, d_new = nat.buf(q), nat.buf(q.nbytes), nat.buf(q.nbytes)
@@ -57,3 +63,37 @@ def test_static_rejects_what_it_cannot_hold(nat):
     assert L.m40llm_attention_last_token_f32_gqa_static_async(nat.ctx, kv, 0, dq.ptr, 4, 16, do.ptr) == ERR_UNSUPPORTED
     L.m40llm_kvcache_destroy(kv)
     nat.free_all()
+
+
+def test_static_call_allocates_nothing(pkg, O):
+    """The property the entry point exists for. On a context of its own, where the regular attention path has never
+    run, multi-split static calls leave the context's scratch arenas as they were (the growth counter does not move)
+    and, once the kernels' code is resident after a first call, the device's free memory does not change."""
+    import helpers
+    import torch
+
+    own = helpers.Native(pkg.native.lib())
+    try:
+        qh, kvh, hd, max_seq = 32, 8, 128, 8192
+        rng = np.random.default_rng(99)
+        kv = own.kv_dense(max_seq, 1, kvh, hd)
+        k = rng.standard_normal((max_seq, kvh, hd)).astype(np.float16)
+        v = rng.standard_normal((max_seq, kvh, hd)).astype(np.float16)
+        own.kv_fill(kv, 0, k, v)
+        q = rng.standard_normal(qh * hd).astype(np.float32)
+        dq, do = own.buf(q), own.buf(q.nbytes)
+        gen0 = scratch_generation(own)
+        f = own.lib.m40llm_attention_last_token_f32_gqa_static_async
+        assert f(own.ctx, kv, 0, dq.ptr, qh, max_seq, do.ptr) == 0  # set-up call: symbol lookup, kernel attributes
+        own.sync(1)
+        free0 = torch.cuda.mem_get_info(0)[0]
+        for L in (max_seq, 5000, 129, max_seq):
+            assert f(own.ctx, kv, 0, dq.ptr, qh, L, do.ptr) == 0
+            own.sync(1)
+            assert_close(do.download(np.float32, q.shape), O.attention_gqa(k, v, q, qh, L), what=f"own context L{L}")
+        assert torch.cuda.mem_get_info(0)[0] == free0, "device free memory moved across static calls"
+        assert scratch_generation(own) == gen0, "a static call grew a scratch arena"
+        own.lib.m40llm_kvcache_destroy(kv)
+    finally:
+        own.free_all()
+        own.lib.m40llm_destroy_context(own.ctx)
