@@ -769,8 +769,8 @@ def main():
                           "tokens_per_s": sb / (sms * 1e-3), "algorithmic_bytes": sbytes,
                           "frac_of_hbm_peak": sbytes / (sms * 1e-3) / 1e9 / (peak * world),
                           **({"ms_per_rank": sms_all} if world > 1 else {})})
-            for gx in sg:
-                L.m40llm_cuda_graph_destroy(gx)
+            for sgraph in sg:
+                L.m40llm_cuda_graph_destroy(sgraph)
             L.m40llm_kvcache_destroy(skv)
             for bname in ("dx", "dq", "datt", "dx1", "dx1n", "dhid", "dout", "dids", "dpos", "dlens"):
                 getattr(sl, bname).free()

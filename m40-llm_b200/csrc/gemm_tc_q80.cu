@@ -13,7 +13,13 @@
 //               operand, and the operand ring is seven sub-blocks deep;
 //   MMA         D[128 x M_pad] += hi.Xh + hi.Xl + lo.Xh with the A operand read from tensor memory and the
 //               activations (split the same way) from shared memory, f32 accumulators in TMEM, one accumulator per
-//               tile segment (two alternate between segments);
+//               tile segment (two alternate between segments). One thread can issue a tcgen05.mma (or commit) only
+//               every ~45 cycles whatever its width, while the tensor core needs ~33 + 16 cycles for a 128 x 16 weight
+//               operand against 64 + 32 activation columns: with one issuing thread the kernel is issue-bound. Up to
+//               32 rows two threads issue side by side, one the hi.[Xh | Xl] products and one the lo.Xh products,
+//               into separate accumulator columns (no ordering between the two is needed), and each sub-block is
+//               committed once per thread to ONE completion barrier that frees both the operand stage and the
+//               activation slot;
 //   epilogue    the worker threads read their row of D back (tcgen05.ld) at the end of a segment.
 //
 // Work is split stream-K style: the (tile, 256-k unit) space is cut into one contiguous span per CTA (one CTA per
@@ -38,10 +44,22 @@ constexpr uint32_t RAW_BYTES = BLOCK_N * RAW_ROW_BYTES; // 34816
 constexpr uint32_t RS = 4, TB = 2;                     // ring depths: raw stages, TMEM accumulators
 constexpr uint32_t A_COLS = BLOCK_K;                   // TMEM columns of one converted sub-block: 32 hi + 32 lo
 constexpr uint32_t TMEM_COLS = 512;
-__host__ __device__ constexpr uint32_t acc_cols(int m_pad) { return 2u * (uint32_t)m_pad; }  // [hi.Xh + lo.Xh | hi.Xl]
-__host__ __device__ constexpr uint32_t a_stages(int m_pad) { return (TMEM_COLS - TB * acc_cols(m_pad)) / A_COLS; }  // 7, 6, 4
+// Two issuing threads (see above) up to 32 rows; at 64 rows the accumulators leave no room for a third column group.
+__host__ __device__ constexpr bool dual_issue(int m_pad) { return m_pad <= 32; }
+__host__ __device__ constexpr uint32_t n_issuers(int m_pad) { return dual_issue(m_pad) ? 2u : 1u; }
+// dual: [hi.Xh | hi.Xl | lo.Xh]; single: [hi.Xh + lo.Xh | hi.Xl]
+__host__ __device__ constexpr uint32_t acc_cols(int m_pad) { return (dual_issue(m_pad) ? 3u : 2u) * (uint32_t)m_pad; }
+__host__ __device__ constexpr uint32_t a_stages(int m_pad) { return (TMEM_COLS - TB * acc_cols(m_pad)) / A_COLS; }  // 6, 5, 4
+// First TMEM column of accumulator buffer tb (TB == 2). Every accumulator starts at a multiple of its own width:
+// dual issue lays the two buffers out as [hi 0 | lo 0 | lo 1 | hi 1] with hi 2 m_pad and lo m_pad columns wide.
+__host__ __device__ constexpr uint32_t acc_hi_col(int m_pad, uint32_t tb) {
+    return dual_issue(m_pad) ? (tb ? 4u * (uint32_t)m_pad : 0u) : tb * acc_cols(m_pad);
+}
+__host__ __device__ constexpr uint32_t acc_lo_col(int m_pad, uint32_t tb) { return (2u + tb) * (uint32_t)m_pad; }  // dual only
 // Activation tiles: their bytes are counted on the operand stage's barrier, but they live in a ring of their own that
 // is a few slots deeper, so that a tile is requested when its stage's previous use has been ISSUED, not completed.
+// The completion barriers form a ring of the same depth: done[u % b_slots] flips when every MMA of sub-block u has
+// finished, which frees activation slot u % b_slots at once and operand stage u % a_stages for sub-block u + a_stages.
 __host__ __device__ constexpr uint32_t b_slots(int m_pad) { return a_stages(m_pad) + (m_pad <= 32 ? 3u : 0u); }
 
 struct Q80Args {
@@ -61,13 +79,14 @@ __device__ __forceinline__ void span_of(const Q80Args& a, uint32_t cta, uint32_t
 
 struct Q80Smem {
     unsigned char* s_raw;
-    uint64_t *raw_full, *raw_empty, *a_full, *a_empty, *t_full, *t_empty;
+    uint64_t *raw_full, *raw_empty, *a_full, *done, *t_full, *t_empty;
     volatile uint32_t* abort_flag;
 };
 
 constexpr uint32_t WORKER_WARPS = 16;                    // 4 threads per weight row
 constexpr uint32_t WORKER_THREADS = WORKER_WARPS * 32;   // 512
-constexpr uint32_t CTA_THREADS = 96 + WORKER_THREADS;    // + weight producer, MMA issuer, activation producer warps
+constexpr uint32_t SERVICE_WARPS = 4;                    // weight producer, MMA issuer, activation producer, 2nd issuer
+constexpr uint32_t CTA_THREADS = SERVICE_WARPS * 32 + WORKER_THREADS;
 
 // One worker thread owns weight row r of the tile and, in every raw stage, the C4-th 64-k sub-block (two Q8_0
 // blocks, bytes [68*C4, 68*C4+68) of the row: 4-byte aligned). At the end of a tile segment it reads columns
@@ -76,7 +95,7 @@ template <int M_PAD, int C4>
 __device__ __forceinline__ void q80_worker(const Q80Args& a, const Q80Smem& sm, uint32_t tmem_base, uint32_t u0,
                                            uint32_t u1, uint32_t lane_group, uint32_t lane) {
     constexpr int COLS = M_PAD / 4;
-    constexpr uint32_t AST = a_stages(M_PAD);
+    constexpr uint32_t AST = a_stages(M_PAD), BS = b_slots(M_PAD);
     constexpr uint32_t A_COL0 = TB * acc_cols(M_PAD);
     const uint32_t r = lane_group * 32 + lane;  // weight row of the tile == TMEM lane
     const uint32_t tmem_lane = tmem_base + ((lane_group * 32u) << 16);
@@ -105,7 +124,8 @@ __device__ __forceinline__ void q80_worker(const Q80Args& a, const Q80Smem& sm, 
                 const uint4 t = chunk[i];
                 L[4 * i] = t.x, L[4 * i + 1] = t.y, L[4 * i + 2] = t.z, L[4 * i + 3] = t.w;
             }
-            if (u >= AST && !wwait(&sm.a_empty[as], ((u / AST) - 1) & 1u)) { ok = false; break; }
+            // the stage is free once every MMA of the sub-block that used it last (u - AST) has completed
+            if (u >= AST && !wwait(&sm.done[(u - AST) % BS], ((u - AST) / BS) & 1u)) { ok = false; break; }
             tc_fence_after();
             const __half2 bias = __float2half2_rn(1152.0f);
             const uint32_t col = tmem_lane + A_COL0 + as * A_COLS;
@@ -146,11 +166,16 @@ __device__ __forceinline__ void q80_worker(const Q80Args& a, const Q80Smem& sm, 
         const uint32_t tb = seg % TB;
         if (!wwait(&sm.t_full[tb], (seg / TB) & 1u)) { ok = false; break; }
         tc_fence_after();
-        uint32_t x[COLS], y[COLS];
-        const uint32_t taddr = tmem_base + ((lane_group * 32u) << 16) + tb * acc_cols(M_PAD) + C4 * COLS;
+        uint32_t x[COLS], y[COLS], z[COLS];
+        const uint32_t tlane = tmem_base + ((lane_group * 32u) << 16) + C4 * COLS;
+        const uint32_t taddr = tlane + acc_hi_col(M_PAD, tb);
         if (COLS == 4) { tmem_ld_x4(taddr, x); tmem_ld_x4(taddr + M_PAD, y); }
         else if (COLS == 8) { tmem_ld_x8(taddr, x); tmem_ld_x8(taddr + M_PAD, y); }
         else { tmem_ld_x16(taddr, x); tmem_ld_x16(taddr + M_PAD, y); }
+        if (dual_issue(M_PAD)) {  // the lo.Xh products have their own column group
+            if (COLS == 4) tmem_ld_x4(tlane + acc_lo_col(M_PAD, tb), z);
+            else tmem_ld_x8(tlane + acc_lo_col(M_PAD, tb), z);
+        }
         tmem_ld_wait();
         tc_fence_before();
         __syncwarp();
@@ -159,7 +184,9 @@ __device__ __forceinline__ void q80_worker(const Q80Args& a, const Q80Smem& sm, 
 #pragma unroll
         for (int j = 0; j < COLS; ++j) {
             const uint32_t m = C4 * COLS + j;
-            if (m < a.M) dstp[(size_t)m * BLOCK_N] = __uint_as_float(x[j]) + __uint_as_float(y[j]);
+            float v = __uint_as_float(x[j]) + __uint_as_float(y[j]);
+            if (dual_issue(M_PAD)) v += __uint_as_float(z[j]);
+            if (m < a.M) dstp[(size_t)m * BLOCK_N] = v;
         }
         pos += kb_end - kb_begin;
         ++seg;
@@ -183,12 +210,12 @@ __global__ void __launch_bounds__(CTA_THREADS, 1) gemm_tc_q80_kernel(const __gri
     unsigned char* s_raw = smem;                             // RS x RAW_BYTES
     unsigned char* s_b = s_raw + RS * RAW_BYTES;             // BS x (hi, lo); 1024-aligned: RAW_BYTES = 34 KB
     uint64_t* bars = reinterpret_cast<uint64_t*>(s_b + BS * 2 * B_BYTES);
+    constexpr uint32_t NI = n_issuers(M_PAD);
     uint64_t* raw_full = bars;
     uint64_t* raw_empty = raw_full + RS;
     uint64_t* a_full = raw_empty + RS;
-    uint64_t* a_empty = a_full + AST;
-    uint64_t* b_empty = a_empty + AST;
-    uint64_t* t_full = b_empty + BS;
+    uint64_t* done = a_full + AST;
+    uint64_t* t_full = done + BS;
     uint64_t* t_empty = t_full + TB;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(t_empty + TB);
     volatile uint32_t* abort_flag = tmem_slot + 1;
@@ -203,9 +230,9 @@ __global__ void __launch_bounds__(CTA_THREADS, 1) gemm_tc_q80_kernel(const __gri
         for (uint32_t i = 0; i < RS; ++i) { mbar_init(&raw_full[i], 1); mbar_init(&raw_empty[i], WORKER_WARPS); }
         // a stage is full when its 4 worker warps have arrived AND the activation tile's bytes have landed (the
         // activation producer's expect_tx is the fifth arrival); one commit frees it for both
-        for (uint32_t i = 0; i < AST; ++i) { mbar_init(&a_full[i], 5); mbar_init(&a_empty[i], 1); }
-        for (uint32_t i = 0; i < BS; ++i) mbar_init(&b_empty[i], 1);
-        for (uint32_t i = 0; i < TB; ++i) { mbar_init(&t_full[i], 1); mbar_init(&t_empty[i], WORKER_WARPS); }
+        for (uint32_t i = 0; i < AST; ++i) mbar_init(&a_full[i], 5);
+        for (uint32_t i = 0; i < BS; ++i) mbar_init(&done[i], NI);  // one commit per issuing thread
+        for (uint32_t i = 0; i < TB; ++i) { mbar_init(&t_full[i], NI); mbar_init(&t_empty[i], WORKER_WARPS); }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -246,7 +273,7 @@ __global__ void __launch_bounds__(CTA_THREADS, 1) gemm_tc_q80_kernel(const __gri
                     const uint32_t u = i * 4 + sub, as = u % AST, bs = u % BS;
                     // the slot must be free (the MMAs of sub-block u - BS have completed) and the stage barrier must
                     // have finished its previous use (sub-block u - AST was handed to the MMA issuer)
-                    if (u >= BS && !mbar_wait(&b_empty[bs], ((u / BS) - 1) & 1u)) { ok = false; break; }
+                    if (u >= BS && !mbar_wait(&done[bs], ((u / BS) - 1) & 1u)) { ok = false; break; }
                     if (u >= AST && !mbar_wait(&a_full[as], ((u / AST) - 1) & 1u)) { ok = false; break; }
                     if (*abort_flag) { ok = false; break; }
                     mbar_expect_tx(&a_full[as], 2 * B_BYTES);
@@ -257,11 +284,13 @@ __global__ void __launch_bounds__(CTA_THREADS, 1) gemm_tc_q80_kernel(const __gri
             }
             if (!ok) *abort_flag = 1;
         }
-    } else if (warp == 1) {
-        // ---------------- MMA issuer: one accumulator per tile segment, TMEM buffer = segment % TB
-        if (lane == 0) {
-            // one MMA takes hi against [Xh | Xl] (the two activation tiles are contiguous rows of one operand), a
-            // second adds lo.Xh into the first half: the weight operand passes the tensor core twice, not three times
+    } else if (warp == 1 || warp == 3) {
+        // ---------------- MMA issuers: one accumulator per tile segment, TMEM buffer = segment % TB. Warp 1 issues
+        // hi against [Xh | Xl] (the two activation tiles are contiguous rows of one operand); the lo.Xh products go
+        // to warp 3 and their own accumulator columns (dual issue) or follow from warp 1 into the first half.
+        constexpr bool DUAL = dual_issue(M_PAD);
+        const bool lo_thread = warp == 3;
+        if (lane == 0 && (DUAL || !lo_thread)) {
             const uint32_t idesc2 = make_idesc(2 * M_PAD), idesc1 = make_idesc(M_PAD);
             bool ok = true;
             // the loop below is this kernel's critical path: stage index and phase are carried, not recomputed
@@ -274,7 +303,7 @@ __global__ void __launch_bounds__(CTA_THREADS, 1) gemm_tc_q80_kernel(const __gri
                 const uint32_t tb = seg % TB;
                 if (seg >= TB && !mbar_wait(&t_empty[tb], ((seg / TB) - 1) & 1u)) { ok = false; break; }
                 tc_fence_after();
-                const uint32_t d_tmem = tmem_base + tb * acc_cols(M_PAD);
+                const uint32_t d_tmem = tmem_base + (DUAL && lo_thread ? acc_lo_col(M_PAD, tb) : acc_hi_col(M_PAD, tb));
                 const uint32_t n_sub = (kb_end - kb_begin) * 4;
                 for (uint32_t j = 0; j < n_sub && ok; ++j) {
                     if (!mbar_wait(&a_full[as], ph)) { ok = false; break; }
@@ -285,11 +314,15 @@ __global__ void __launch_bounds__(CTA_THREADS, 1) gemm_tc_q80_kernel(const __gri
                     for (uint32_t kk = 0; kk < BLOCK_K / UMMA_K; ++kk) {
                         const uint64_t b_x = make_desc_sw128(sb + kk * UMMA_K * 2);  // rows [0, M_PAD) = Xh, [M_PAD, 2 M_PAD) = Xl
                         const uint32_t a_hi = ta + kk * (UMMA_K / 2), a_lo = a_hi + 32;
-                        umma_f16_ts(d_tmem, a_hi, b_x, idesc2, (j | kk) != 0u);
-                        umma_f16_ts(d_tmem, a_lo, b_x, idesc1, 1u);
+                        if (DUAL) {
+                            if (lo_thread) umma_f16_ts(d_tmem, a_lo, b_x, idesc1, (j | kk) != 0u);
+                            else umma_f16_ts(d_tmem, a_hi, b_x, idesc2, (j | kk) != 0u);
+                        } else {
+                            umma_f16_ts(d_tmem, a_hi, b_x, idesc2, (j | kk) != 0u);
+                            umma_f16_ts(d_tmem, a_lo, b_x, idesc1, 1u);
+                        }
                     }
-                    umma_commit(&a_empty[as]);  // frees the operand stage for the workers
-                    umma_commit(&b_empty[bs]);  // and the activation slot
+                    umma_commit(&done[bs]);  // this thread's share of sub-block done: operand stage and activation slot
                     if (++as == AST) as = 0, ph ^= 1u;
                     if (++bs == BS) bs = 0;
                 }
@@ -300,18 +333,18 @@ __global__ void __launch_bounds__(CTA_THREADS, 1) gemm_tc_q80_kernel(const __gri
             if (!ok) *abort_flag = 1;
         }
     } else {
-        // ---------------- workers: warps 3..18; TMEM lane group = warp % 4, row quarter = (warp - 3) / 4
-        Q80Smem sm = {s_raw, raw_full, raw_empty, a_full, a_empty, t_full, t_empty, abort_flag};
+        // ---------------- workers: warps 4..19; TMEM lane group = warp % 4, k quarter of a raw stage = (warp - 4) / 4
+        Q80Smem sm = {s_raw, raw_full, raw_empty, a_full, done, t_full, t_empty, abort_flag};
         pdl_wait();  // the partials written at segment ends reuse scratch that earlier kernels may still read
         const uint32_t lane_group = warp & 3u;
-        switch ((warp - 3u) >> 2) {
+        switch ((warp - SERVICE_WARPS) >> 2) {
             case 0: q80_worker<M_PAD, 0>(a, sm, tmem_base, u0, u1, lane_group, lane); break;
             case 1: q80_worker<M_PAD, 1>(a, sm, tmem_base, u0, u1, lane_group, lane); break;
             case 2: q80_worker<M_PAD, 2>(a, sm, tmem_base, u0, u1, lane_group, lane); break;
             default: q80_worker<M_PAD, 3>(a, sm, tmem_base, u0, u1, lane_group, lane); break;
         }
     }
-    if (*abort_flag && threadIdx.x == 96) atomicOr(a.status, 4u);
+    if (*abort_flag && threadIdx.x == SERVICE_WARPS * 32) atomicOr(a.status, 4u);
     tc_fence_before();
     __syncthreads();
     if (warp == 1) {
