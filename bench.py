@@ -4,7 +4,7 @@
 
 Workload (BASELINE.json configs[2]): hidden 4096, 32 q heads / 8 kv heads, head_dim 128, FFN 14336 with Q8_0
 weights, FP16 attention weights, batch 32 with per-sequence contexts uniform in [512, 8192], RoPE theta 5e5.
-One step = one pass of the layer over the batch (fused norm+QKV+RoPE+append, batched decode attention,
+One step = one pass of the layer over the batch (fused norm+QKV+RoPE+append+batched decode attention, then
 output projection + residual, norm, Q8_0 SwiGLU FFN + residual): 32 tokens advance one layer.
 
 `value`   tokens/s with inputs resident in HBM, the layer replayed as one CUDA graph on the decode stream.
@@ -194,12 +194,10 @@ class Layer:
 
     def enqueue(self, wset):
         L, ctx, d, r = self.nat.lib, self.nat.ctx, self.dw[wset], self.rows
-        rc = L.m40llm_qkv_rmsnorm_rope_append_async(ctx, self.kv, self.dx.ptr, d["attn_norm"].ptr, 1, EPS, d["wq"].ptr,
-                                                    d["wk"].ptr, d["wv"].ptr, None, None, None, self.dids.ptr,
-                                                    self.dpos.ptr, r, H, QH, THETA, 1.0, 0, self.dq.ptr)
-        assert rc == 0, rc
-        rc = L.m40llm_attention_last_token_f32_gqa_batched_async(ctx, self.kv, self.dids.ptr, self.dlens.ptr, r,
-                                                                 self.dq.ptr, QH, self.datt.ptr)
+        rc = L.m40llm_qkv_rope_append_attention_async(ctx, self.kv, self.dx.ptr, d["attn_norm"].ptr, 1, EPS, d["wq"].ptr,
+                                                      d["wk"].ptr, d["wv"].ptr, None, None, None, self.dids.ptr,
+                                                      self.dpos.ptr, self.dlens.ptr, r, H, QH, THETA, 1.0, 0, self.dq.ptr,
+                                                      self.datt.ptr)
         assert rc == 0, rc
         rc = L.m40llm_attn_out_ffn_async(ctx, self.datt.ptr, d["wo"].ptr, self.dx.ptr, d["ffn_norm"].ptr, 1, EPS,
                                          d["wg"].ptr, d["wu"].ptr, d["wd"].ptr, 1, self.dx1.ptr, self.dhid.ptr,

@@ -385,6 +385,22 @@ int m40llm_attn_out_ffn_async(M40llmCudaContext* ctx, const void* d_att_f32, con
                               const void* d_ffn_norm_w, uint32_t norm_w_dtype, float eps, const void* d_wg,
                               const void* d_wu, const void* d_wd, uint32_t ffn_q80, void* d_x1_f32, void* d_hid_f32,
                               void* d_out_f32, uint32_t rows, uint32_t hidden, uint32_t q_dim, uint32_t ffn);
+/* Steps 1-6 of the layer in one call (src/infer/forward.rs:307-470 issues them as norm, three GEMMs, bias adds, RoPE,
+ * append and attention): m40llm_qkv_rmsnorm_rope_append_async followed by
+ * m40llm_attention_last_token_f32_gqa_batched_async over d_seq_lens, with the same arguments and the same results in
+ * d_q_out_f32 (q after RoPE), the cache and d_att_out_f32. Dense caches only (a compressed cache returns
+ * M40LLM_ERR_UNSUPPORTED after the prologue: its attention is per row). With one row, head_dim 64 or 128 and at most
+ * 16 q heads per kv head the whole of RoPE, append, attention and split merge is ONE kernel after the projection; that
+ * path requires d_seq_lens[r] == d_positions[r] + 1 (the new token is the last attended one) and reports a row that
+ * breaks it through status bit 1 with a zero output row. Decode stream. */
+int m40llm_qkv_rope_append_attention_async(M40llmCudaContext* ctx, M40llmKVCache* kv, const void* d_x_f32,
+                                           const void* d_norm_w, uint32_t norm_w_dtype, float eps,
+                                           const void* d_wq_f16, const void* d_wk_f16, const void* d_wv_f16,
+                                           const void* d_bq_f32, const void* d_bk_f32, const void* d_bv_f32,
+                                           const uint32_t* d_seq_ids, const uint32_t* d_positions,
+                                           const uint32_t* d_seq_lens, uint32_t rows, uint32_t hidden, uint32_t q_heads,
+                                           float freq_base, float freq_scale, uint32_t rope_layout, void* d_q_out_f32,
+                                           void* d_att_out_f32);
 /* Split-K attention for one long sequence sharded over ranks: attends tokens [tok_begin, tok_end) of a dense
  * cache and writes the unnormalised triple per q head: m [q_heads], l [q_heads], o [q_heads][head_dim]. */
 int m40llm_attention_last_token_f32_gqa_partial_async(M40llmCudaContext* ctx, const M40llmKVCache* kv,

@@ -57,6 +57,14 @@ int m40_attention_fold_partials(M40llmCudaContext* ctx, const float* m, const fl
 // Returns 0 when launched, 1 when the shape is not one the tiled kernel takes, < 0 on launch failure.
 int m40_attention_dense_tiled(M40llmCudaContext* ctx, const DenseAttnArgs& a, uint32_t rows);
 
+// One launch for rows whose new token is appended in the same step: RoPE(q) -> q_out, RoPE(k) + f16 append of k / v,
+// attention over the cache and the new token, split merge through distributed shared memory. Needs
+// positions[r] + 1 == seq_lens[r]. Returns 0 when launched, 1 when the shape / device does not take it.
+int m40_attention_fused_row(M40llmCudaContext* ctx, M40llmKVCache* kv, const float* q_raw, const float* k_new,
+                            const float* v_new, const uint32_t* seq_ids, const uint32_t* positions,
+                            const uint32_t* seq_lens, uint32_t rows, uint32_t q_heads, float freq_base,
+                            float freq_scale, uint32_t layout, float* q_out, float* out);
+
 // Token range of (row, split): shared by both kernels so partial layouts agree.
 __device__ __forceinline__ bool attn_resolve_row(const DenseAttnArgs& a, uint32_t row, uint32_t split, uint32_t* seq,
                                                  uint32_t* t0, uint32_t* t1) {

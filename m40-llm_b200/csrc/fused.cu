@@ -6,6 +6,9 @@
 // on the decode stream for any number of rows: the norm, three projections that share the
 // normalised activations (bias folded into their epilogue), and one rope+append launch that
 // covers every row, q head and kv head.
+#include <stdlib.h>
+
+#include "attention.cuh"
 #include "common.cuh"
 #include "gemm.cuh"
 #include "gemm_tc.cuh"
@@ -131,6 +134,71 @@ extern "C" int m40llm_qkv_rmsnorm_rope_append_async(M40llmCudaContext* ctx, M40l
                                                q_heads, freq_base, freq_scale, rope_layout, ctx->d_status);
     M40_COUNT_LAUNCH(ctx);
     return e == cudaSuccess && cudaGetLastError() == cudaSuccess ? 0 : -6;
+}
+
+int m40llm_attention_last_token_f32_gqa_batched_async(M40llmCudaContext* ctx, const M40llmKVCache* kv,
+                                                      const uint32_t* d_seq_ids, const uint32_t* d_seq_lens,
+                                                      uint32_t batch_size, const void* d_q_f32, uint32_t q_heads,
+                                                      void* d_out_f32);
+
+// Steps 1-6 of the layer in one call (src/infer/forward.rs:307-470): the prologue above followed by the batched decode
+// attention. One row on a dense cache takes two launches: the streaming Wq | Wk | Wv projection (norm and bias
+// folded in) and the cluster kernel that rotates, appends, attends and merges. Everything else is the two entry
+// points back to back.
+extern "C" int m40llm_qkv_rope_append_attention_async(
+    M40llmCudaContext* ctx, M40llmKVCache* kv, const void* d_x_f32, const void* d_norm_w, uint32_t norm_w_dtype, float eps,
+    const void* d_wq_f16, const void* d_wk_f16, const void* d_wv_f16, const void* d_bq_f32, const void* d_bk_f32,
+    const void* d_bv_f32, const uint32_t* d_seq_ids, const uint32_t* d_positions, const uint32_t* d_seq_lens, uint32_t rows,
+    uint32_t hidden, uint32_t q_heads, float freq_base, float freq_scale, uint32_t rope_layout, void* d_q_out_f32,
+    void* d_att_out_f32) {
+    if (!ctx || !kv || !d_x_f32 || !d_norm_w || !d_wq_f16 || !d_wk_f16 || !d_wv_f16 || !d_seq_ids || !d_positions ||
+        !d_seq_lens || !d_q_out_f32 || !d_att_out_f32)
+        return -1;
+    if (rows == 0 || hidden == 0 || q_heads == 0 || kv->num_heads == 0 || q_heads % kv->num_heads != 0) return -2;
+    if (norm_w_dtype > 1) return -4;
+    if (m40_ensure_device(ctx) != 0) return -1;
+    const uint32_t hd = kv->head_dim, QD = q_heads * hd, KD = kv->num_heads * hd;
+    const bool one_launch_attention = rows == 1 && !kv->compressed && kv->d_k && kv->d_v && (hd == 64 || hd == 128) &&
+                                      q_heads / kv->num_heads <= 16 && getenv("M40LLM_NO_FUSED_ROW") == nullptr;
+    if (one_launch_attention) {
+        const size_t need = (size_t)rows * ((size_t)QD + 2 * (size_t)KD) * sizeof(float);
+        float* scratch = (float*)m40_ensure_scratch(ctx, 1, need, 1);
+        if (!scratch) return -5;
+        float* qraw = scratch;
+        float* kbuf = qraw + (size_t)rows * QD;
+        float* vbuf = kbuf + (size_t)rows * KD;
+        const M40GemvSeg segs[3] = {{d_wq_f16, nullptr, qraw, (const float*)d_bq_f32, nullptr, (int)QD},
+                                    {d_wk_f16, nullptr, kbuf, (const float*)d_bk_f32, nullptr, (int)KD},
+                                    {d_wv_f16, nullptr, vbuf, (const float*)d_bv_f32, nullptr, (int)KD}};
+        const M40GemvNorm norm = {d_norm_w, norm_w_dtype == 1u ? 1 : 0, eps, nullptr};
+        int rc = m40_gemv_stream(ctx, ctx->decode_stream, (const float*)d_x_f32, (int)hidden, M40_GEMV_F16, 0, 3, segs, &norm);
+        if (rc < 0) return rc;
+        if (rc == 0) {
+            rc = m40_attention_fused_row(ctx, kv, qraw, kbuf, vbuf, d_seq_ids, d_positions, d_seq_lens, rows, q_heads,
+                                         freq_base, freq_scale, rope_layout, (float*)d_q_out_f32, (float*)d_att_out_f32);
+            if (rc <= 0) return rc;
+            // the device does not take the cluster kernel: finish with the separate rope/append and attention launches
+            dim3 grid(q_heads + kv->num_heads, rows);
+            const cudaError_t ce = cudaMemcpyAsync(d_q_out_f32, qraw, (size_t)rows * QD * sizeof(float),
+                                                   cudaMemcpyDeviceToDevice, ctx->decode_stream);
+            if (ce != cudaSuccess) return -6;
+            rope_q_append_kv_rows_kernel<<<grid, 64, 0, ctx->decode_stream>>>((float*)d_q_out_f32, kbuf, vbuf, *kv, d_seq_ids,
+                                                                              d_positions, q_heads, freq_base, freq_scale,
+                                                                              rope_layout, ctx->d_status);
+            M40_COUNT_LAUNCH(ctx);
+            if (cudaGetLastError() != cudaSuccess) return -6;
+            return m40llm_attention_last_token_f32_gqa_batched_async(ctx, kv, d_seq_ids, d_seq_lens, rows, d_q_out_f32,
+                                                                     q_heads, d_att_out_f32);
+        }
+        // the projection shape does not stream: the general prologue below handles it
+    }
+    const int rc = m40llm_qkv_rmsnorm_rope_append_async(ctx, kv, d_x_f32, d_norm_w, norm_w_dtype, eps, d_wq_f16, d_wk_f16,
+                                                        d_wv_f16, d_bq_f32, d_bk_f32, d_bv_f32, d_seq_ids, d_positions, rows,
+                                                        hidden, q_heads, freq_base, freq_scale, rope_layout, d_q_out_f32);
+    if (rc != 0) return rc;
+    if (kv->compressed) return M40LLM_ERR_UNSUPPORTED;  // compressed caches attend per row through their own entry point
+    return m40llm_attention_last_token_f32_gqa_batched_async(ctx, kv, d_seq_ids, d_seq_lens, rows, d_q_out_f32, q_heads,
+                                                             d_att_out_f32);
 }
 
 // Steps 9-13 of the layer (src/infer/forward.rs:470-667): x1 = x + att.Wo; xn = rmsnorm(x1) * w;

@@ -33,15 +33,19 @@ int DecodeLayer::enqueue(M40llmKVCache* kv, const LayerWeights& w, const KvCompr
                          const DecodeBatchPlan& plan, const CudaDecodeBatchPlan& dplan, const void* d_x, void* d_out) {
     const uint32_t rows = plan.batch_size();
     const uint32_t H = cfg_.hidden, QD = cfg_.q_heads * cfg_.head_dim;
-    int rc = m40llm_qkv_rmsnorm_rope_append_async(ctx_, kv, d_x, w.attn_norm, 1u, cfg_.rms_eps, w.wq, w.wk, w.wv, w.bq,
-                                                  w.bk, w.bv, dplan.d_sequence_ids(), dplan.d_positions(), rows, H,
-                                                  cfg_.q_heads, cfg_.rope_base, cfg_.rope_scale, cfg_.rope_layout, d_q_);
-    if (rc != 0) return fail(rc, "qkv_rmsnorm_rope_append");
+    int rc;
     if (kvcfg.mode == KvCompressMode::Off) {
-        rc = m40llm_attention_last_token_f32_gqa_batched_async(ctx_, kv, dplan.d_sequence_ids(), dplan.d_sequence_lens(),
-                                                               rows, d_q_, cfg_.q_heads, d_att_);
-        if (rc != 0) return fail(rc, "attention_gqa_batched");
+        // steps 1-6 in one call: at one row the RoPE, the append, the attention and its split merge are one kernel
+        rc = m40llm_qkv_rope_append_attention_async(ctx_, kv, d_x, w.attn_norm, 1u, cfg_.rms_eps, w.wq, w.wk, w.wv, w.bq,
+                                                    w.bk, w.bv, dplan.d_sequence_ids(), dplan.d_positions(),
+                                                    dplan.d_sequence_lens(), rows, H, cfg_.q_heads, cfg_.rope_base,
+                                                    cfg_.rope_scale, cfg_.rope_layout, d_q_, d_att_);
+        if (rc != 0) return fail(rc, "qkv_rope_append_attention");
     } else {
+        rc = m40llm_qkv_rmsnorm_rope_append_async(ctx_, kv, d_x, w.attn_norm, 1u, cfg_.rms_eps, w.wq, w.wk, w.wv, w.bq, w.bk,
+                                                  w.bv, dplan.d_sequence_ids(), dplan.d_positions(), rows, H, cfg_.q_heads,
+                                                  cfg_.rope_base, cfg_.rope_scale, cfg_.rope_layout, d_q_);
+        if (rc != 0) return fail(rc, "qkv_rmsnorm_rope_append");
         // src/infer/kv.rs:562-575: the default compressed configuration goes to the FP16-K/q4-V direct entry point,
         // one call per row (each row has its own sequence and block selection)
         const auto& e = plan.entries();

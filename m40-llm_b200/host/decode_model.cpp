@@ -63,13 +63,11 @@ int DecodeModel::enqueue_step() {
     for (size_t l = 0; l < layers_.size(); ++l) {
         const LayerWeights& w = layers_[l];
         const uint32_t* slots = (const uint32_t*)d_slots_ + l * r;
-        rc = m40llm_qkv_rmsnorm_rope_append_async(ctx_, kv_, x, w.attn_norm, 1u, cfg_.rms_eps, w.wq, w.wk, w.wv, w.bq, w.bk,
-                                                  w.bv, slots, (const uint32_t*)d_pos_, r, H, cfg_.q_heads, cfg_.rope_base,
-                                                  cfg_.rope_scale, cfg_.rope_layout, d_q_);
-        if (rc != 0) return fail(rc, "qkv_rmsnorm_rope_append");
-        rc = m40llm_attention_last_token_f32_gqa_batched_async(ctx_, kv_, slots, (const uint32_t*)d_lens_, r, d_q_,
-                                                               cfg_.q_heads, d_att_);
-        if (rc != 0) return fail(rc, "attention_batched");
+        rc = m40llm_qkv_rope_append_attention_async(ctx_, kv_, x, w.attn_norm, 1u, cfg_.rms_eps, w.wq, w.wk, w.wv, w.bq, w.bk,
+                                                    w.bv, slots, (const uint32_t*)d_pos_, (const uint32_t*)d_lens_, r, H,
+                                                    cfg_.q_heads, cfg_.rope_base, cfg_.rope_scale, cfg_.rope_layout, d_q_,
+                                                    d_att_);
+        if (rc != 0) return fail(rc, "qkv_rope_append_attention");
         rc = m40llm_attn_out_ffn_async(ctx_, d_att_, w.wo, x, w.ffn_norm, 1u, cfg_.rms_eps, w.wg, w.wu, w.wd,
                                        w.ffn_q80 ? 1u : 0u, d_x1_, d_hid_, y, r, H, QD, cfg_.ffn);
         if (rc != 0) return fail(rc, "attn_out_ffn");

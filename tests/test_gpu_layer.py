@@ -26,7 +26,7 @@ def make_weights(O, rng, H, qh, kvh, hd, F, q80, bias):
     return w
 
 
-def device_layer(nat, kv, w, x_rows, seq_ids, positions, cfg, q80, fused_tail=False):
+def device_layer(nat, kv, w, x_rows, seq_ids, positions, cfg, q80, fused_tail=False, one_call_front=False):
     """The layer as the fused entry points issue it: prologue, batched attention, then either the reference's op
     sequence (Wo, residual, norm, FFN + residual) or the single composite call for steps 9-13."""
     L, ctx = nat.lib, nat.ctx
@@ -38,11 +38,18 @@ def device_layer(nat, kv, w, x_rows, seq_ids, positions, cfg, q80, fused_tail=Fa
     dids, dpos = nat.buf(np.asarray(seq_ids, np.uint32)), nat.buf(np.asarray(positions, np.uint32))
     dlens = nat.buf(np.asarray(positions, np.uint32) + 1)
     g = lambda n: d[n].ptr if n in d else None
-    rc = L.m40llm_qkv_rmsnorm_rope_append_async(ctx, kv, dx.ptr, d["attn_norm"].ptr, 1, cfg.eps, d["wq"].ptr, d["wk"].ptr,
-                                                d["wv"].ptr, g("bq"), g("bk"), g("bv"), dids.ptr, dpos.ptr, rows, H,
-                                                cfg.q_heads, cfg.rope_base, cfg.rope_scale, cfg.rope_layout, dq.ptr)
-    assert rc == 0, rc
-    assert L.m40llm_attention_last_token_f32_gqa_batched_async(ctx, kv, dids.ptr, dlens.ptr, rows, dq.ptr, cfg.q_heads, datt.ptr) == 0
+    if one_call_front:  # steps 1-6 through the single entry point (one row: projection + one cluster kernel)
+        rc = L.m40llm_qkv_rope_append_attention_async(ctx, kv, dx.ptr, d["attn_norm"].ptr, 1, cfg.eps, d["wq"].ptr,
+                                                      d["wk"].ptr, d["wv"].ptr, g("bq"), g("bk"), g("bv"), dids.ptr, dpos.ptr,
+                                                      dlens.ptr, rows, H, cfg.q_heads, cfg.rope_base, cfg.rope_scale,
+                                                      cfg.rope_layout, dq.ptr, datt.ptr)
+        assert rc == 0, rc
+    else:
+        rc = L.m40llm_qkv_rmsnorm_rope_append_async(ctx, kv, dx.ptr, d["attn_norm"].ptr, 1, cfg.eps, d["wq"].ptr, d["wk"].ptr,
+                                                    d["wv"].ptr, g("bq"), g("bk"), g("bv"), dids.ptr, dpos.ptr, rows, H,
+                                                    cfg.q_heads, cfg.rope_base, cfg.rope_scale, cfg.rope_layout, dq.ptr)
+        assert rc == 0, rc
+        assert L.m40llm_attention_last_token_f32_gqa_batched_async(ctx, kv, dids.ptr, dlens.ptr, rows, dq.ptr, cfg.q_heads, datt.ptr) == 0
     if fused_tail:
         rc = L.m40llm_attn_out_ffn_async(ctx, datt.ptr, d["wo"].ptr, dx.ptr, d["ffn_norm"].ptr, 1, cfg.eps, d["wg"].ptr,
                                          d["wu"].ptr, d["wd"].ptr, 1 if q80 else 0, dx1.ptr, dhid.ptr, dout.ptr, rows,
@@ -67,8 +74,8 @@ def device_layer(nat, kv, w, x_rows, seq_ids, positions, cfg, q80, fused_tail=Fa
     (2048, 16, 2, 128, 1024, False, 1, True, 1e6, 200),  # Qwen heads: NeoX RoPE + QKV bias
     (4096, 32, 8, 128, 14336, True, 0, False, 5e5, 600), # Llama-3-8B-shaped layer, Q8_0 FFN
 ])
-@pytest.mark.parametrize("fused_tail", [False, True])
-def test_decode_layer_single_row(nat, O, H, qh, kvh, hd, F, q80, layout, bias, base, ctx_len, fused_tail):
+@pytest.mark.parametrize("fused_tail,one_call_front", [(False, False), (True, False), (True, True)])
+def test_decode_layer_single_row(nat, O, H, qh, kvh, hd, F, q80, layout, bias, base, ctx_len, fused_tail, one_call_front):
     rng = np.random.default_rng(H + F)
     cfg = O.LayerCfg(H, qh, kvh, hd, F, 1 if q80 else 0, layout, 1e-5, base, 1.0)
     w = make_weights(O, rng, H, qh, kvh, hd, F, q80, bias)
@@ -83,8 +90,13 @@ def test_decode_layer_single_row(nat, O, H, qh, kvh, hd, F, q80, layout, bias, b
     # two consecutive tokens (tests/forward_parity_toy.rs runs one and two tokens)
     for step in range(2):
         pos = ctx_len + step
-        out, q_rot, att = device_layer(nat, kv, w, x[None, :], [0], [pos], cfg, q80, fused_tail)
+        out, q_rot, att = device_layer(nat, kv, w, x[None, :], [0], [pos], cfg, q80, fused_tail, one_call_front)
         eout, eq, eatt = O.decode_layer(cfg, x, w, K, V, pos)
+        k_dev, v_dev = np.zeros((kvh, hd), np.float16), np.zeros((kvh, hd), np.float16)
+        assert nat.lib.m40llm_kvcache_debug_read_token(nat.ctx, kv, 0, pos, k_dev.ctypes.data_as(C.c_void_p),
+                                                       v_dev.ctypes.data_as(C.c_void_p)) == 0
+        assert_close(k_dev.astype(np.float32), K[pos].astype(np.float32), what=f"appended k, step {step}")
+        assert_close(v_dev.astype(np.float32), V[pos].astype(np.float32), what=f"appended v, step {step}")
         assert_close(q_rot[0], eq, what=f"q after rope, step {step}")
         assert_close(att[0], eatt, what=f"attention, step {step}")
         assert_close(out[0], eout, what=f"layer output, step {step}")
@@ -367,3 +379,61 @@ def test_batched_layer_many_rows(nat, O, rows, H, qh, kvh, hd, F):
     lens = [int(n) for n in np.random.default_rng(rows).integers(1, 300, size=rows)]
     rows_to_check = sorted(set(range(0, rows, 7)) | {rows - 1, 63, 64})
     _batched_layer_case(nat, O, H, qh, kvh, hd, F, 5e5, lens, True, seed=rows, check_rows=rows_to_check)
+
+
+@pytest.mark.parametrize("qh,kvh,hd,layout,ctx_len", [
+    (8, 2, 64, 0, 0),        # empty cache: the new token is the only one attended
+    (8, 2, 64, 1, 1),
+    (32, 8, 128, 0, 63), (32, 8, 128, 0, 64), (32, 8, 128, 0, 65),   # around one tile
+    (32, 8, 128, 0, 1023), (32, 8, 128, 0, 1024), (32, 8, 128, 0, 1025),  # around 16 slices of one tile
+    (16, 2, 128, 1, 5000),   # Qwen heads, NeoX RoPE
+    (32, 4, 64, 0, 2048),    # TinyLlama heads
+    (32, 2, 64, 0, 777),     # 16 q heads per kv head (rows 8..15 of the MMA live)
+    (24, 8, 128, 0, 300),    # 3 q heads per kv head
+    (32, 8, 128, 0, 16383),
+])
+def test_one_launch_row_attention(nat, O, qh, kvh, hd, layout, ctx_len):
+    """m40llm_qkv_rope_append_attention_async at one row against the op-by-op oracle: q after RoPE, the appended K/V
+    row, the recorded sequence length and the attention output, at contexts around the kernel's slice boundaries."""
+    rng = np.random.default_rng(ctx_len + qh + hd)
+    H, base = 256, 5e5
+    w = make_weights(O, rng, H, qh, kvh, hd, 128, False, True)
+    max_seq = ctx_len + 3
+    K = np.zeros((max_seq, kvh, hd), np.float16)
+    V = np.zeros((max_seq, kvh, hd), np.float16)
+    K[:ctx_len] = rng.standard_normal((ctx_len, kvh, hd)).astype(np.float16)
+    V[:ctx_len] = rng.standard_normal((ctx_len, kvh, hd)).astype(np.float16)
+    kv = nat.kv_dense(max_seq, 2, kvh, hd)
+    if ctx_len:
+        nat.kv_fill(kv, 1, K[:ctx_len], V[:ctx_len])
+    L, ctx = nat.lib, nat.ctx
+    d = {n: nat.buf(a) for n, a in w.items()}
+    x = rng.standard_normal((1, H)).astype(np.float32)
+    dx, dq, datt = nat.buf(x), nat.buf(qh * hd * 4), nat.buf(qh * hd * 4)
+    dids, dpos, dlens = nat.buf(np.array([1], np.uint32)), nat.buf(np.array([ctx_len], np.uint32)), nat.buf(np.array([ctx_len + 1], np.uint32))
+    call = lambda: L.m40llm_qkv_rope_append_attention_async(
+        ctx, kv, dx.ptr, d["attn_norm"].ptr, 1, 1e-5, d["wq"].ptr, d["wk"].ptr, d["wv"].ptr, d["bq"].ptr, d["bk"].ptr,
+        d["bv"].ptr, dids.ptr, dpos.ptr, dlens.ptr, 1, H, qh, base, 1.0, layout, dq.ptr, datt.ptr)
+    assert call() == 0
+    nat.sync(1)
+    xn = O.rms_norm(x[0], w["attn_norm"], 1e-5)
+    eq = O.rope(O.gemm_f32xf16_gguf(xn, w["wq"]) + w["bq"], qh, hd, ctx_len, base, 1.0, layout)
+    ek = O.f32_to_f16(O.rope(O.gemm_f32xf16_gguf(xn, w["wk"]) + w["bk"], kvh, hd, ctx_len, base, 1.0, layout)).reshape(kvh, hd)
+    ev = O.f32_to_f16(O.gemm_f32xf16_gguf(xn, w["wv"]) + w["bv"]).reshape(kvh, hd)
+    K[ctx_len], V[ctx_len] = ek, ev
+    assert_close(dq.download(np.float32, (qh * hd,)), eq, what="q after rope")
+    k_dev, v_dev = np.zeros((kvh, hd), np.float16), np.zeros((kvh, hd), np.float16)
+    assert L.m40llm_kvcache_debug_read_token(ctx, kv, 1, ctx_len, k_dev.ctypes.data_as(C.c_void_p), v_dev.ctypes.data_as(C.c_void_p)) == 0
+    assert_close(k_dev.astype(np.float32), ek.astype(np.float32), what="appended k")
+    assert_close(v_dev.astype(np.float32), ev.astype(np.float32), what="appended v")
+    assert_close(datt.download(np.float32, (qh * hd,)), O.attention_gqa(K, V, eq, qh, ctx_len + 1), what="attention")
+    st = np.zeros(1, np.uint32)
+    assert L.m40llm_context_take_device_status(ctx, st.ctypes.data) == 0 and st[0] == 0
+    # the one-launch path needs the new token to be the last attended one: otherwise the row is flagged and zeroed
+    dlens.upload(np.array([ctx_len + 2], np.uint32))
+    datt.upload(np.full(qh * hd, 3.0, np.float32))
+    assert call() == 0
+    assert L.m40llm_context_take_device_status(ctx, st.ctypes.data) == 0 and st[0] == 1
+    assert not datt.download(np.float32, (qh * hd,)).any()
+    L.m40llm_kvcache_destroy(kv)
+    nat.free_all()
