@@ -424,6 +424,23 @@ int m40llm_attention_compressed_selected_partial_async(M40llmCudaContext* ctx, c
                                                        uint32_t block_begin, uint32_t block_end,
                                                        uint32_t include_recent, void* d_m_f32, void* d_l_f32,
                                                        void* d_o_f32);
+/* Split-K selection, device side. m40llm_topk_pairs_async ranks the n candidate scores of every q head
+ * (d_scores_f32 [q_heads][score_stride], candidate i = block index_base + i; n <= 4096) and writes the best top_n <= 64
+ * as (f32 score, u32 block) pairs, descending, ties to the lower block, NaN and scores <= -1e30 never chosen, unused
+ * slots (-1e30, 0xffffffff): d_pairs_out [q_heads][64][2] 32-bit words. That array is one rank's message of the
+ * all-gather. m40llm_topk_merge_pairs_async applies the same rule to the gathered candidates d_pairs
+ * [parts][q_heads][64][2] and writes the global block list d_blocks_out [q_heads][64] (the form
+ * m40llm_attention_compressed_selected_partial_async takes) and, when given, the scores d_scores_out_f32
+ * [q_heads][64]. The rule is the single-GPU selection's (cuda/kernels.cu:2861-2930), so every rank derives the
+ * identical list without a further exchange. Decode stream, no host synchronisation. */
+int m40llm_topk_pairs_async(M40llmCudaContext* ctx, const void* d_scores_f32, uint32_t q_heads, uint32_t n,
+                            uint32_t score_stride, uint32_t index_base, uint32_t top_n, void* d_pairs_out);
+int m40llm_topk_merge_pairs_async(M40llmCudaContext* ctx, const void* d_pairs, uint32_t parts, uint32_t q_heads,
+                                  uint32_t top_n, uint32_t* d_blocks_out, void* d_scores_out_f32);
+/* Merge of all-gathered triples that arrive as ONE message per rank: d_triples [parts][q_heads * (2 + head_dim)] with
+ * each message laid out m [q_heads] | l [q_heads] | o [q_heads][head_dim]; out [q_heads * head_dim]. */
+int m40llm_attention_merge_gathered_async(M40llmCudaContext* ctx, const void* d_triples_f32, uint32_t parts,
+                                          uint32_t q_heads, uint32_t head_dim, void* d_out_f32);
 /* Device-side result of the last block selection run on `ctx`: u32 [q_heads][64] block indices in
  * descending score order, 0xffffffff padded. Copies to host after synchronising the decode stream. */
 int m40llm_kvcache_debug_last_selected_blocks(M40llmCudaContext* ctx, uint32_t q_heads, uint32_t* out_blocks_host,
@@ -489,6 +506,11 @@ int m40llm_context_launch_count(M40llmCudaContext* ctx, uint64_t* out_count);
  * earlier keeps working on the memory it was captured with. A harness can watch this counter to see that a call
  * allocated. */
 int m40llm_context_scratch_generation(M40llmCudaContext* ctx, uint64_t* out_generation);
+/* Performance hint, never required: the weights that the call AFTER the next one will stream first (the next layer's
+ * Wq while this layer's FFN runs). The last one-row streaming launch of the next m40llm_attn_out_ffn_async call pulls
+ * the first bytes of that range (at most 12 MiB) into L2 while it drains, so that the following projection's first
+ * loads hit L2 instead of an idle HBM. Consumed by that call; NULL or 0 clears it. Host-side only, no launch. */
+int m40llm_prefetch_hint(M40llmCudaContext* ctx, const void* d_next_weights, size_t bytes);
 /* The raw CUDA stream handle of a stream kind, for harnesses that time with their own events. */
 int m40llm_context_stream_handle(M40llmCudaContext* ctx, uint32_t stream_kind, void** out_stream);
 

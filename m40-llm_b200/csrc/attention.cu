@@ -365,17 +365,21 @@ int m40_attention_fold_partials(M40llmCudaContext* ctx, const float* m, const fl
     return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 
-int m40_attention_merge(M40llmCudaContext* ctx, const float* m, const float* l, const float* o, uint32_t parts,
-                        uint32_t q_heads, uint32_t hd, float* out) {
+// m, l [part][...] with `stride_m` floats between parts, o with `stride_o` floats between parts.
+static int merge_strided(M40llmCudaContext* ctx, const float* m, const float* l, const float* o, uint32_t parts,
+                         uint32_t q_heads, uint32_t hd, float* out, size_t stride_m, size_t stride_o) {
     dim3 grid(q_heads, 1);
-    if (merge_wide_ok(o, out, hd, parts, (size_t)q_heads * hd))
-        attn_merge_wide_kernel<<<grid, 256, 0, ctx->decode_stream>>>(m, l, o, out, q_heads, hd, parts, (size_t)q_heads,
-                                                                    (size_t)q_heads * hd, 1u);
+    if (merge_wide_ok(o, out, hd, parts, stride_o))
+        attn_merge_wide_kernel<<<grid, 256, 0, ctx->decode_stream>>>(m, l, o, out, q_heads, hd, parts, stride_m, stride_o, 1u);
     else
-        attn_merge_kernel<<<grid, 128, 0, ctx->decode_stream>>>(m, l, o, out, q_heads, hd, parts, (size_t)q_heads,
-                                                               (size_t)q_heads * hd, 1u);
+        attn_merge_kernel<<<grid, 128, 0, ctx->decode_stream>>>(m, l, o, out, q_heads, hd, parts, stride_m, stride_o, 1u);
     M40_COUNT_LAUNCH(ctx);
     return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+int m40_attention_merge(M40llmCudaContext* ctx, const float* m, const float* l, const float* o, uint32_t parts,
+                        uint32_t q_heads, uint32_t hd, float* out) {
+    return merge_strided(ctx, m, l, o, parts, q_heads, hd, out, (size_t)q_heads, (size_t)q_heads * hd);
 }
 
 
@@ -506,6 +510,17 @@ int m40llm_attention_last_token_f32_gqa_partial_async(M40llmCudaContext* ctx, co
     c.part_l = (float*)d_l_f32;
     c.part_o = (float*)d_o_f32;
     return m40_attention_dense(ctx, kv, c);
+}
+
+int m40llm_attention_merge_gathered_async(M40llmCudaContext* ctx, const void* d_triples_f32, uint32_t parts,
+                                          uint32_t q_heads, uint32_t head_dim, void* d_out_f32) {
+    if (!ctx || !d_triples_f32 || !d_out_f32) return -1;
+    if (parts == 0 || q_heads == 0 || head_dim == 0) return -2;
+    if (m40_ensure_device(ctx) != 0) return -1;
+    const float* base = (const float*)d_triples_f32;
+    const size_t stride = (size_t)q_heads * (2u + head_dim);
+    return merge_strided(ctx, base, base + q_heads, base + 2u * (size_t)q_heads, parts, q_heads, head_dim,
+                         (float*)d_out_f32, stride, stride);
 }
 
 int m40llm_attention_merge_partials_async(M40llmCudaContext* ctx, const void* d_m_f32, const void* d_l_f32,

@@ -91,41 +91,75 @@ __global__ void __launch_bounds__(128) block_score_kernel(SelArgs a) {
     }
 }
 
-// ---- 2a. top-k by rank. grid q_heads, 1024 threads, for nb <= 4096. A block's place in the descending list is the
-// number of selectable blocks that beat it (greater score, or equal score and lower index), which is exactly the
-// order the iterative arg-max below produces; every thread ranks its own blocks against all of shared memory, so the
-// whole selection is one pass with one barrier. Scores that are NaN or <= -1e30 are never selectable.
-__global__ void __launch_bounds__(1024) topk_rank_kernel(SelArgs a) {
-    extern __shared__ float sc[];  // nb scores, unselectable ones replaced by -inf
+// ---- 2a. top-k by rank, for up to 4096 candidates per q head. A candidate's place in the descending list is the
+// number of selectable candidates that beat it (greater score, or equal score and lower block index), which is exactly
+// the order the iterative arg-max below produces, so the whole selection is one pass. Scores that are NaN or <= -1e30
+// are never selectable. The candidates of a head are cut into `slices` (gridDim.y) so that the ranking spreads over
+// the whole GPU instead of one CTA per head: CTA (h, s) ranks its slice against all candidates held in shared memory
+// and writes the winners among them; list positions past the number of selectable candidates are filled as empty.
+//
+// Candidate c of head h: score at scores[h * head_stride + (c / per_part) * part_stride + (c % per_part) * elem_stride],
+// block index = ids[same offset] when `ids` is given (gathered (score, index) pairs), else index_base + c.
+struct RankArgs {
+    const float* scores;
+    const uint32_t* ids;
+    uint32_t* out_ids;     // [q_heads][64 * out_stride], element (h, r) at (h * 64 + r) * out_stride
+    float* out_scores;     // same addressing
+    size_t head_stride, part_stride;
+    uint32_t per_part, elem_stride, n, index_base, top_n, out_stride;
+};
+
+__global__ void __launch_bounds__(256) rank_topk_kernel(RankArgs a) {
+    extern __shared__ float rk_smem[];
+    float* sc = rk_smem;                                    // n scores, unselectable ones replaced by -inf
+    uint32_t* id = reinterpret_cast<uint32_t*>(sc + a.n);   // n block indices
+    __shared__ uint32_t s_selectable;
     pdl_wait();
     pdl_trigger();
-    const uint32_t h = blockIdx.x;
-    for (uint32_t i = threadIdx.x; i < a.nb; i += blockDim.x) {
-        const float s = a.scores[(size_t)h * a.score_stride + i];
-        sc[i] = s > -1e30f ? s : -INFINITY;  // false for NaN too
-    }
-    for (uint32_t i = threadIdx.x; i < 64u; i += blockDim.x) {
-        a.sel_blocks[h * 64u + i] = 0xffffffffu;
-        a.sel_scores[h * 64u + i] = -1e30f;
-    }
+    const uint32_t h = blockIdx.x, slice = blockIdx.y, slices = gridDim.y, tid = threadIdx.x;
+    if (tid == 0) s_selectable = 0;
     __syncthreads();
-    // four adjacent lanes share one block i and scan a quarter of the others each
-    const uint32_t part = threadIdx.x & 3u, q0 = (a.nb * part) / 4u, q1 = (a.nb * (part + 1u)) / 4u;
-    for (uint32_t i0 = 0; i0 < a.nb; i0 += blockDim.x / 4u) {
-        const uint32_t i = i0 + threadIdx.x / 4u;
-        const float s = i < a.nb ? sc[i] : -INFINITY;
+    uint32_t mine = 0;
+    for (uint32_t c = tid; c < a.n; c += blockDim.x) {
+        const size_t off = (size_t)h * a.head_stride + (size_t)(c / a.per_part) * a.part_stride +
+                           (size_t)(c % a.per_part) * a.elem_stride;
+        const float s = a.scores[off];
+        const uint32_t b = a.ids ? a.ids[off] : a.index_base + c;
+        const bool ok = s > -1e30f && b != 0xffffffffu;  // false for NaN too
+        sc[c] = ok ? s : -INFINITY;
+        id[c] = b;
+        mine += ok ? 1u : 0u;
+    }
+    mine = (uint32_t)__reduce_add_sync(0xffffffffu, mine);
+    if ((tid & 31u) == 0u && mine) atomicAdd(&s_selectable, mine);
+    __syncthreads();
+    const uint32_t filled = min(s_selectable, a.top_n);  // list positions that will receive a winner
+    // empty tail of the list, dealt to the slices
+    for (uint32_t r = filled + slice * blockDim.x + tid; r < 64u; r += slices * blockDim.x) {
+        a.out_ids[((size_t)h * 64u + r) * a.out_stride] = 0xffffffffu;
+        a.out_scores[((size_t)h * 64u + r) * a.out_stride] = -1e30f;
+    }
+    // four adjacent lanes share one candidate of this slice and scan a quarter of all candidates each
+    const uint32_t per_slice = (a.n + slices - 1u) / slices;
+    const uint32_t c0 = slice * per_slice, c1 = min(c0 + per_slice, a.n);
+    const uint32_t part = tid & 3u, q0 = (a.n * part) / 4u, q1 = (a.n * (part + 1u)) / 4u;
+    for (uint32_t i0 = c0; i0 < c1; i0 += blockDim.x / 4u) {
+        const uint32_t i = i0 + tid / 4u;
+        const float s = i < c1 ? sc[i] : -INFINITY;
+        const uint32_t bi = i < c1 ? id[i] : 0u;
         uint32_t rank = 0;
         if (s != -INFINITY) {
+#pragma unroll 4
             for (uint32_t j = q0; j < q1; ++j) {
                 const float o = sc[j];
-                rank += (o > s || (o == s && j < i)) ? 1u : 0u;  // equal score, lower index: ahead
+                rank += (o > s || (o == s && id[j] < bi)) ? 1u : 0u;  // equal score, lower block index: ahead
             }
         }
         rank += __shfl_xor_sync(0xffffffffu, rank, 1);
         rank += __shfl_xor_sync(0xffffffffu, rank, 2);
-        if (part == 0 && s != -INFINITY && rank < a.top_n) {
-            a.sel_blocks[h * 64u + rank] = i;
-            a.sel_scores[h * 64u + rank] = s;
+        if (part == 0 && s != -INFINITY && rank < a.top_n && rank < 64u) {
+            a.out_ids[((size_t)h * 64u + rank) * a.out_stride] = bi;
+            a.out_scores[((size_t)h * 64u + rank) * a.out_stride] = s;
         }
     }
 }
@@ -414,14 +448,38 @@ int launch_scores(M40llmCudaContext* ctx, const SelArgs& a) {
     return e == cudaSuccess && cudaGetLastError() == cudaSuccess ? 0 : -8;
 }
 
+// Ranks `r.n` candidates per q head into the top-`r.top_n` list (see rank_topk_kernel). n <= 4096.
+int launch_rank(M40llmCudaContext* ctx, const RankArgs& r, uint32_t q_heads) {
+    // enough CTAs to spread the n^2 comparisons over the GPU, never more slices than 64-candidate groups
+    uint32_t slices = ((uint32_t)ctx->sm_count + q_heads - 1u) / q_heads;
+    const uint32_t max_slices = (r.n + 63u) / 64u;
+    if (slices > max_slices) slices = max_slices;
+    if (slices < 1u) slices = 1u;
+    const size_t smem = (size_t)(r.n ? r.n : 1u) * 8u;
+    const cudaError_t e = m40_launch_dependent(rank_topk_kernel, dim3(q_heads, slices), dim3(256), smem, ctx->decode_stream, r);
+    M40_COUNT_LAUNCH(ctx);
+    return e == cudaSuccess && cudaGetLastError() == cudaSuccess ? 0 : -8;
+}
+
 int launch_topk(M40llmCudaContext* ctx, const SelArgs& a) {
-    const size_t smem = (size_t)(a.nb ? a.nb : 1u) * sizeof(float);
-    if (smem > 200u * 1024u) return -7;
     if (a.nb <= 4096u) {
-        const cudaError_t e = m40_launch_dependent(topk_rank_kernel, dim3(a.q_heads), dim3(1024), smem, ctx->decode_stream, a);
-        M40_COUNT_LAUNCH(ctx);
-        return e == cudaSuccess && cudaGetLastError() == cudaSuccess ? 0 : -8;
+        RankArgs r = {};
+        r.scores = a.scores;
+        r.ids = nullptr;
+        r.out_ids = a.sel_blocks;
+        r.out_scores = a.sel_scores;
+        r.head_stride = a.score_stride;
+        r.part_stride = 0;
+        r.per_part = a.nb ? a.nb : 1u;
+        r.elem_stride = 1;
+        r.n = a.nb;
+        r.index_base = 0;
+        r.top_n = a.top_n;
+        r.out_stride = 1;
+        return launch_rank(ctx, r, a.q_heads);
     }
+    const size_t smem = (size_t)a.nb * sizeof(float);
+    if (smem > 200u * 1024u) return -7;
     if (smem > 48u * 1024u)
         cudaFuncSetAttribute(topk_blocks_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     topk_blocks_kernel<<<a.q_heads, 128, smem, ctx->decode_stream>>>(a);
@@ -587,6 +645,46 @@ int m40llm_attention_compressed_selected_partial_async(M40llmCudaContext* ctx, c
     if (rc != 0) return rc;
     return m40_attention_fold_partials(ctx, a.part_m, a.part_l, a.part_o, a.splits, q_heads, a.hd, (float*)d_m_f32,
                                        (float*)d_l_f32, (float*)d_o_f32) == 0 ? 0 : -8;
+}
+
+int m40llm_topk_pairs_async(M40llmCudaContext* ctx, const void* d_scores_f32, uint32_t q_heads, uint32_t n,
+                            uint32_t score_stride, uint32_t index_base, uint32_t top_n, void* d_pairs_out) {
+    if (!ctx || !d_scores_f32 || !d_pairs_out) return -1;
+    if (q_heads == 0 || top_n == 0 || top_n > 64 || n > 4096 || score_stride < n) return -2;
+    if (m40_ensure_device(ctx) != 0) return -1;
+    RankArgs r = {};
+    r.scores = (const float*)d_scores_f32;
+    r.out_scores = (float*)d_pairs_out;
+    r.out_ids = (uint32_t*)d_pairs_out + 1;
+    r.head_stride = score_stride;
+    r.per_part = n ? n : 1u;
+    r.elem_stride = 1;
+    r.n = n;
+    r.index_base = index_base;
+    r.top_n = top_n;
+    r.out_stride = 2;
+    return launch_rank(ctx, r, q_heads);
+}
+
+int m40llm_topk_merge_pairs_async(M40llmCudaContext* ctx, const void* d_pairs, uint32_t parts, uint32_t q_heads,
+                                  uint32_t top_n, uint32_t* d_blocks_out, void* d_scores_out_f32) {
+    if (!ctx || !d_pairs || !d_blocks_out) return -1;
+    if (q_heads == 0 || parts == 0 || top_n == 0 || top_n > 64 || parts > 64) return -2;
+    if (q_heads > ctx->selected_capacity_heads) return -7;
+    if (m40_ensure_device(ctx) != 0) return -1;
+    RankArgs r = {};
+    r.scores = (const float*)d_pairs;
+    r.ids = (const uint32_t*)d_pairs + 1;
+    r.out_ids = d_blocks_out;
+    r.out_scores = d_scores_out_f32 ? (float*)d_scores_out_f32 : ctx->d_selected_scores;
+    r.head_stride = 64u * 2u;
+    r.part_stride = (size_t)q_heads * 64u * 2u;
+    r.per_part = 64;
+    r.elem_stride = 2;
+    r.n = parts * 64u;
+    r.top_n = top_n;
+    r.out_stride = 1;
+    return launch_rank(ctx, r, q_heads);
 }
 
 int m40llm_kvcache_debug_last_selected_blocks(M40llmCudaContext* ctx, uint32_t q_heads, uint32_t* out_blocks_host,

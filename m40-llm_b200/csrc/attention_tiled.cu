@@ -67,6 +67,16 @@ __device__ __forceinline__ void split_h2(float x, float y, uint32_t* hi, uint32_
     *lo = pack_h2(x - __half2float(hx), y - __half2float(hy));
 }
 
+// Barrier over the 128 threads that stream one token range together: the whole CTA in the batched kernel, one of
+// two warp groups (named barrier 1 or 2) in the one-launch row kernel.
+struct CtaBarrier {
+    __device__ __forceinline__ void sync() const { __syncthreads(); }
+};
+struct GroupBarrier {
+    uint32_t id;
+    __device__ __forceinline__ void sync() const { asm volatile("bar.sync %0, 128;" ::"r"(id) : "memory"); }
+};
+
 template <int HD, int STAGES_>
 struct TiledCfgN {
     static constexpr int CHUNKS = HD / 8;                  // 16-byte pieces per row
@@ -117,14 +127,15 @@ __device__ __forceinline__ void tiled_prefetch(const __half* Kh, const __half* V
 // leaves every warp's (m, l, O) in shared memory: sm_m [4][16], sm_l [4][16], sm_o [4][16][HD] at the start of
 // smem_raw (the pipeline buffers are dead by then); m is in the base-2 domain of the pre-scaled q. `q0` points at the
 // group's first head ([G][HD] f32, global or shared), rows g >= G are zero. Ends with a CTA barrier.
-template <typename Cfg, int HD, bool G_HI>
+template <typename Cfg, int HD, bool G_HI, typename Bar>
 __device__ __forceinline__ void tiled_stream(const __half* Kh, const __half* Vh, unsigned char* smem_raw, uint32_t t0,
-                                             uint32_t t1, const float* q0base, uint32_t G, float inv_sqrt) {
+                                             uint32_t t1, const float* q0base, uint32_t G, float inv_sqrt, uint32_t tid,
+                                             const Bar bar) {
     constexpr int KS = HD / 16;   // k-steps of Q K^T
     constexpr int NT = HD / 8;    // n8 tiles of the output
     __half* sK = reinterpret_cast<__half*>(smem_raw);
     __half* sV = reinterpret_cast<__half*>(smem_raw + Cfg::STAGES * Cfg::TILE_BYTES);
-    const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
+    const uint32_t warp = tid >> 5, lane = tid & 31u;
     const uint32_t g = lane >> 2, t4 = lane & 3u;
 
     // ---- Q fragments (A operand), pre-scaled by 1/sqrt(hd) * log2(e), split into hi + lo f16
@@ -162,7 +173,7 @@ __device__ __forceinline__ void tiled_stream(const __half* Kh, const __half* Vh,
     const uint32_t n_tiles = (t1 - t0 + TILE - 1) / TILE;
     for (uint32_t tile = 0; tile < n_tiles; ++tile) {
         cp_async_wait<Cfg::STAGES - 2>();
-        __syncthreads();
+        bar.sync();
         {
             const uint32_t nxt = tile + Cfg::STAGES - 1;
             if (nxt < n_tiles) tiled_load_tile<Cfg, HD>(Kh, Vh, sK, sV, t0, t1, nxt, nxt % Cfg::STAGES, tid);
@@ -237,7 +248,7 @@ __device__ __forceinline__ void tiled_stream(const __half* Kh, const __half* Vh,
         }
     }
     cp_async_wait<0>();
-    __syncthreads();
+    bar.sync();
 
     // ---- the four warps' partials through shared memory (reusing the pipeline buffers)
     float* sm_m = reinterpret_cast<float*>(smem_raw);  // [4][16]
@@ -259,7 +270,7 @@ __device__ __forceinline__ void tiled_stream(const __half* Kh, const __half* Vh,
             dst[8 * HD + 1] = o[n][3];
         }
     }
-    __syncthreads();
+    bar.sync();
 }
 
 // G_HI: the group has more than 8 q heads (rows 8..15 of the MMA are live).
@@ -292,7 +303,8 @@ __global__ void __launch_bounds__(128, 2) attn_decode_tiled_kernel(DenseAttnArgs
     const __half* Kh = a.K + kv_row_offset(seq, kvh, 0, a.kv_heads, a.max_seq_len, HD);
     const __half* Vh = a.V + kv_row_offset(seq, kvh, 0, a.kv_heads, a.max_seq_len, HD);
     tiled_prefetch<Cfg, HD>(Kh, Vh, smem_raw, t0, t1, tid);
-    tiled_stream<Cfg, HD, G_HI>(Kh, Vh, smem_raw, t0, t1, a.q + ((size_t)row * a.q_heads + kvh * G) * HD, G, a.inv_sqrt);
+    tiled_stream<Cfg, HD, G_HI>(Kh, Vh, smem_raw, t0, t1, a.q + ((size_t)row * a.q_heads + kvh * G) * HD, G, a.inv_sqrt, tid,
+                                CtaBarrier{});
 
     const float* sm_m = reinterpret_cast<const float*>(smem_raw);
     const float* sm_l = sm_m + 64;
@@ -328,8 +340,8 @@ __global__ void __launch_bounds__(128, 2) attn_decode_tiled_kernel(DenseAttnArgs
 // Single-launch decode attention for rows whose new token is being appended in the same step: RoPE of q, RoPE of k +
 // f16 append of k / v, attention over the cache and over the new token, and the merge of the token splits.
 //
-// One thread-block CLUSTER of CL CTAs owns (row, kv head); CTA r streams the r-th slice of the tokens already in the
-// cache, [0, position), exactly as the batched kernel does. The new token never makes the round trip through the
+// One thread-block CLUSTER of CL CTAs owns (row, kv head); each CTA's two warp groups stream one slice each of the
+// tokens already in the cache, [0, position), exactly as a CTA of the batched kernel does. The new token never makes the round trip through the
 // cache: the last CTA of the cluster rotates k, stores the f16 rows for later steps and attends the f16-rounded values
 // straight from shared memory as one more partial. The CL partial (m, l, O) triples then meet through distributed
 // shared memory: every CTA reduces 1/CL of the outputs over its peers' triples and writes the normalised result. No
@@ -356,22 +368,27 @@ struct FusedRowArgs {
 };
 
 constexpr int FUSED_CL = 16;  // CTAs per cluster (non-portable size; needs the opt-in attribute)
+constexpr int FUSED_WG = 2;   // warp groups per CTA, each streaming its own half of the CTA's slice
 
+// One CTA per SM: two warp groups with 96 KB of pipeline each. (A single group of four warps per CTA tops out near
+// 20 GB/s, so 16 x kv_heads CTAs alone would leave most of HBM idle.)
 template <int HD>
-using FusedCfg = TiledCfgN<HD, HD == 128 ? 4 : 8>;  // 128 KB of pipeline per CTA: one CTA per SM, 96 KB in flight
+using FusedCfg = TiledCfgN<HD, HD == 128 ? 3 : 6>;
 
 template <int HD, bool G_HI>
-__global__ void __launch_bounds__(128, 1) attn_decode_fused_row_kernel(FusedRowArgs a) {
+__global__ void __launch_bounds__(128 * FUSED_WG, 1) attn_decode_fused_row_kernel(FusedRowArgs a) {
     using Cfg = FusedCfg<HD>;
     constexpr uint32_t HALF = HD / 2;
+    constexpr uint32_t NW = 4 * FUSED_WG;  // warps holding a partial
     extern __shared__ __align__(128) unsigned char smem_raw[];
     __shared__ float2 s_cs[HALF];                  // (cos, sin) per pair at this row's position
     __shared__ __align__(16) float s_q[16][HD];    // rotated q of the group (rows >= G stay zero)
     __shared__ float s_kn[HD], s_vn[HD];           // the new token's k (rotated) and v, rounded through f16
-    __shared__ float s_new[16];            // its score per q head, base-2 domain
+    __shared__ float s_new[16];                    // its score per q head, base-2 domain
     cg::cluster_group cluster = cg::this_cluster();
     const uint32_t rank = blockIdx.x, kvh = blockIdx.y, row = blockIdx.z;
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
+    const uint32_t wg = tid >> 7, gtid = tid & 127u;
     const uint32_t G = a.q_heads / a.kv_heads;
 
     pdl_wait();  // q, k, v of this step come from the projection kernel before this one
@@ -384,13 +401,14 @@ __global__ void __launch_bounds__(128, 1) attn_decode_fused_row_kernel(FusedRowA
             for (uint32_t i = tid; i < G * HD; i += blockDim.x) a.out[((size_t)row * a.q_heads + kvh * G) * HD + i] = 0.0f;
         return;
     }
-    // tokens already in the cache: [0, pos), cut into CL slices of whole 64-token tiles
-    uint32_t chunk = (pos + FUSED_CL - 1) / FUSED_CL;
+    // tokens already in the cache: [0, pos), cut into CL x WG slices of whole 64-token tiles
+    uint32_t chunk = (pos + FUSED_CL * FUSED_WG - 1) / (FUSED_CL * FUSED_WG);
     chunk = (chunk + TILE - 1) / TILE * TILE;
-    const uint32_t t0 = min(rank * chunk, pos), t1 = min(t0 + chunk, pos);
+    const uint32_t t0 = min((rank * FUSED_WG + wg) * chunk, pos), t1 = min(t0 + chunk, pos);
     __half* Kh = a.K + kv_row_offset(seq, kvh, 0, a.kv_heads, a.max_seq_len, HD);
     __half* Vh = a.V + kv_row_offset(seq, kvh, 0, a.kv_heads, a.max_seq_len, HD);
-    tiled_prefetch<Cfg, HD>(Kh, Vh, smem_raw, t0, t1, tid);
+    unsigned char* my_smem = smem_raw + (size_t)wg * Cfg::SMEM;
+    tiled_prefetch<Cfg, HD>(Kh, Vh, my_smem, t0, t1, gtid);
 
     // ---- rotation table, rotated q, and (last CTA) the new token
     if (tid < HALF) {
@@ -416,11 +434,12 @@ __global__ void __launch_bounds__(128, 1) attn_decode_fused_row_kernel(FusedRowA
         }
     }
     const bool has_new = rank == FUSED_CL - 1;
-    if (has_new && tid < HALF) {
-        const uint32_t i0 = a.layout == 1u ? tid : 2u * tid, i1 = a.layout == 1u ? tid + HALF : 2u * tid + 1u;
+    if (has_new && tid >= 128u && tid - 128u < HALF) {  // second warp group: the first is busy with q
+        const uint32_t i = tid - 128u;
+        const uint32_t i0 = a.layout == 1u ? i : 2u * i, i1 = a.layout == 1u ? i + HALF : 2u * i + 1u;
         const float* kn = a.k_new + ((size_t)row * a.kv_heads + kvh) * HD;
         const float* vn = a.v_new + ((size_t)row * a.kv_heads + kvh) * HD;
-        const float2 cs = s_cs[tid];
+        const float2 cs = s_cs[i];
         const float x = kn[i0], y = kn[i1];
         const __half k0 = __float2half_rn(x * cs.x - y * cs.y), k1 = __float2half_rn(x * cs.y + y * cs.x);
         const __half v0 = __float2half_rn(vn[i0]), v1 = __float2half_rn(vn[i1]);
@@ -429,11 +448,11 @@ __global__ void __launch_bounds__(128, 1) attn_decode_fused_row_kernel(FusedRowA
         Vh[rowoff + i0] = v0, Vh[rowoff + i1] = v1;
         s_kn[i0] = __half2float(k0), s_kn[i1] = __half2float(k1);
         s_vn[i0] = __half2float(v0), s_vn[i1] = __half2float(v1);
-        if (kvh == 0 && tid == 0) a.seq_map[seq] = pos + 1u;
+        if (kvh == 0 && i == 0) a.seq_map[seq] = pos + 1u;
     }
     __syncthreads();
     if (has_new) {  // score of the new token per q head, in the base-2 domain of the streamed scores
-        for (uint32_t hh = warp; hh < G; hh += 4u) {
+        for (uint32_t hh = warp; hh < G; hh += NW) {
             float dot = 0.0f;
             for (uint32_t d = lane; d < HD; d += 32u) dot = fmaf(s_q[hh][d], s_kn[d], dot);
             dot = warp_sum(dot);
@@ -441,28 +460,30 @@ __global__ void __launch_bounds__(128, 1) attn_decode_fused_row_kernel(FusedRowA
         }
     }
 
-    // ---- the cached tokens of this CTA's slice (ends with a CTA barrier, which also publishes s_new)
-    tiled_stream<Cfg, HD, G_HI>(Kh, Vh, smem_raw, t0, t1, &s_q[0][0], G, a.inv_sqrt);
+    // ---- the cached tokens of this warp group's slice
+    tiled_stream<Cfg, HD, G_HI>(Kh, Vh, my_smem, t0, t1, &s_q[0][0], G, a.inv_sqrt, gtid, GroupBarrier{1u + wg});
+    __syncthreads();  // both groups' partials (and s_new) are in shared memory
 
-    // ---- this CTA's triple per q head: c_m [16], c_l [16], c_o [16][HD] behind the warp partials
-    float* sm_m = reinterpret_cast<float*>(smem_raw);
-    float* sm_l = sm_m + 64;
-    float* sm_o = sm_l + 64;
-    float* c_m = sm_o + 4 * 16 * HD;
+    // ---- this CTA's triple per q head: c_m [16], c_l [16], c_o [16][HD] behind the first group's warp partials
+    float* c_m = reinterpret_cast<float*>(smem_raw) + 128 + 4 * 16 * HD;
     float* c_l = c_m + 16;
     float* c_o = c_l + 16;
     for (uint32_t idx = tid; idx < G * HD; idx += blockDim.x) {
         const uint32_t hh = idx / HD, d = idx % HD;
         float M = has_new ? s_new[hh] : -INFINITY;
 #pragma unroll
-        for (int w = 0; w < 4; ++w) M = fmaxf(M, sm_m[w * 16 + hh]);
+        for (uint32_t w = 0; w < NW; ++w) {
+            const float* gm = reinterpret_cast<const float*>(smem_raw + (size_t)(w >> 2) * Cfg::SMEM);
+            M = fmaxf(M, gm[(w & 3u) * 16 + hh]);
+        }
         float L = 0.0f, O = 0.0f;
 #pragma unroll
-        for (int w = 0; w < 4; ++w) {
-            const float mw = sm_m[w * 16 + hh];
+        for (uint32_t w = 0; w < NW; ++w) {
+            const float* gm = reinterpret_cast<const float*>(smem_raw + (size_t)(w >> 2) * Cfg::SMEM);
+            const float mw = gm[(w & 3u) * 16 + hh];
             const float e = mw == -INFINITY ? 0.0f : fast_exp2(mw - M);
-            L += sm_l[w * 16 + hh] * e;
-            O += sm_o[((size_t)w * 16 + hh) * HD + d] * e;
+            L += gm[64 + (w & 3u) * 16 + hh] * e;
+            O += gm[128 + ((size_t)(w & 3u) * 16 + hh) * HD + d] * e;
         }
         if (has_new) {
             const float e = fast_exp2(s_new[hh] - M);
@@ -509,11 +530,12 @@ __global__ void __launch_bounds__(128, 1) attn_decode_fused_row_kernel(FusedRowA
 template <int HD, bool G_HI>
 int launch_fused_row(M40llmCudaContext* ctx, const FusedRowArgs& a, uint32_t rows) {
     auto kern = attn_decode_fused_row_kernel<HD, G_HI>;
-    constexpr size_t smem = FusedCfg<HD>::SMEM;
-    static_assert(smem >= (size_t)(128 + 4 * 16 * HD + 32 + 16 * HD) * sizeof(float), "partials must fit the pipeline buffers");
+    constexpr size_t smem = (size_t)FUSED_WG * FusedCfg<HD>::SMEM;
+    static_assert(FusedCfg<HD>::SMEM >= (size_t)(128 + 4 * 16 * HD + 32 + 16 * HD) * sizeof(float),
+                  "partials must fit one group's pipeline buffers");
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(FUSED_CL, a.kv_heads, rows);
-    cfg.blockDim = dim3(128);
+    cfg.blockDim = dim3(128 * FUSED_WG);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = ctx->decode_stream;
     cudaLaunchAttribute attr[2];

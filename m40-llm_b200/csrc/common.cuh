@@ -46,7 +46,20 @@ struct M40llmCudaContext {
     // Device status word (bit 0: a batched-attention row was out of range and skipped).
     uint32_t* d_status;
     unsigned long long launches;
+    // Prefetch hint for the next streaming launch on the decode stream: up to two ranges it pulls into L2 while it
+    // drains (the head of the weights that the launch after it will stream). Consumed and cleared by that launch.
+    const void* pf_hint_ptr[2];
+    size_t pf_hint_bytes[2];
 };
+
+// Leaves a prefetch hint (see M40llmCudaContext::pf_hint_ptr); each range is capped at `cap` bytes.
+static inline void m40_set_prefetch_hint(M40llmCudaContext* ctx, const void* p0, size_t b0, const void* p1, size_t b1) {
+    const size_t cap = (size_t)12u << 20;
+    ctx->pf_hint_ptr[0] = p0;
+    ctx->pf_hint_bytes[0] = p0 ? (b0 < cap ? b0 : cap) : 0;
+    ctx->pf_hint_ptr[1] = p1;
+    ctx->pf_hint_bytes[1] = p1 ? (b1 < cap ? b1 : cap) : 0;
+}
 
 struct M40llmCudaGraphExec {
     cudaGraph_t graph;

@@ -404,6 +404,12 @@ int m40llm_context_scratch_generation(M40llmCudaContext* ctx, uint64_t* out_gene
     return 0;
 }
 
+int m40llm_prefetch_hint(M40llmCudaContext* ctx, const void* d_next_weights, size_t bytes) {
+    if (!ctx) return -1;
+    m40_set_prefetch_hint(ctx, d_next_weights, bytes, nullptr, 0);
+    return 0;
+}
+
 int m40llm_context_stream_handle(M40llmCudaContext* ctx, uint32_t stream_kind, void** out_stream) {
     if (!ctx || !out_stream) return -1;
     cudaStream_t s = m40_stream(ctx, stream_kind);

@@ -6,12 +6,15 @@ Two ways the path shards (one 8-GPU box):
   collective at all;
 * one long sequence, split-K: every rank owns a contiguous range of the sequence's KV blocks, computes an
   unnormalised (max, sum, out) triple per q head over its range and the triples are all-gathered and merged. With
-  the compressed cache (FP16 K / q4 V, top-k block selection) there is one more exchange before that: ranks
-  all-gather the block scores of their ranges so that every rank derives the same global top-k list.
+  the compressed cache (FP16 K / q4 V, top-k block selection) there is one more exchange before that: every rank
+  scores its own blocks, keeps its local top-k as (score, block) pairs and the pairs are all-gathered, so that every
+  rank derives the same global top-k list (same rule, ties to the lower block).
 
-The exchange payloads are tiny (Qwen2.5-3B shape at 32K context: 16 heads x 504 scores = 32 KB; triples 16 x 130
+The exchange payloads are tiny (Qwen2.5-3B shape at 32K context: 16 heads x 64 pairs = 8 KB per rank; triples 16 x 130
 floats = 8 KB per rank), so they go through the library collective (NCCL over NVLink on GPUs, gloo on CPU ranks).
-Gathered data always lands in the receiving rank's own memory before a kernel reads it.
+Gathered data always lands in the receiving rank's own memory before a kernel reads it. On GPUs the whole chain
+(scores, local top-k, all-gather, global top-k, attention, all-gather, merge) is enqueued on the context's decode
+stream with no host synchronisation in between (`DeviceSplitK`).
 
 The compute legs are callables so that the same orchestration runs over the CUDA entry points (`NativeLegs`, the
 product) and over any other implementation of the legs (the CPU tests pass a numpy restatement and run two gloo
@@ -150,42 +153,84 @@ def gather_triples(m: torch.Tensor, l: torch.Tensor, o: torch.Tensor, group=None
 # ----------------------------------------------------------------------------- orchestration
 @dataclass
 class Legs:
-    """The compute legs of one rank. `score(b0, b1) -> [q_heads, b1-b0]` f32 tensor; `attend_blocks(blocks
-    [q_heads, 64] u32 ndarray, b0, b1, include_recent) -> (m, l, o)` tensors; `attend_tokens(t0, t1) -> (m, l, o)`
-    for the dense cache; `merge(m, l, o) -> out [heads*hd]` tensor."""
+    """The compute legs of one rank. `score(b0, b1) -> [q_heads, b1-b0]` f32 tensor; `topk_pairs(scores, b0, top) ->
+    [q_heads, 64, 2]` f32 tensor of (score, block-id bits) pairs; `merge_pairs(pairs [world, q_heads, 64, 2], top) ->
+    blocks [q_heads, 64]` (int32 bit patterns of the u32 ids); `attend_blocks(blocks, b0, b1, include_recent) ->
+    triples [q_heads * (2 + hd)]` laid out m | l | o; `attend_tokens(t0, t1) -> triples` for the dense cache;
+    `merge(triples [world, q_heads * (2 + hd)]) -> out [heads*hd]` tensor."""
     score: Callable | None
+    topk_pairs: Callable | None
+    merge_pairs: Callable | None
     attend_blocks: Callable | None
     attend_tokens: Callable | None
     merge: Callable
 
 
+def _all_gather(send: torch.Tensor, group=None) -> torch.Tensor:
+    """One fixed-size message per rank, concatenated along a new leading dimension."""
+    _, world = _world(group)
+    recv = torch.empty((world * send.shape[0],) + tuple(send.shape[1:]), dtype=send.dtype, device=send.device)
+    dist.all_gather_into_tensor(recv, send.contiguous(), group=group)
+    return recv.view((world,) + tuple(send.shape))
+
+
 def compressed_split_k(legs: Legs, n_old_blocks: int, top_blocks: int, group=None):
-    """One long sequence over the FP16-K / q4-V cache: score own blocks -> all-gather scores -> global top-k ->
-    attend own selected blocks (the last rank adds the recent ring) -> all-gather triples -> merge. Every rank
-    returns the full attention output and the block list."""
+    """One long sequence over the FP16-K / q4-V cache: score own blocks -> local top-k pairs -> all-gather pairs ->
+    global top-k -> attend own selected blocks (the last rank adds the recent ring) -> all-gather triples -> merge.
+    Every rank returns the full attention output and the block list (both as tensors of the legs' device)."""
     rank, world = _world(group)
-    ranges = block_ranges(n_old_blocks, world)
-    b0, b1 = ranges[rank]
-    scores = gather_scores(legs.score(b0, b1), ranges, group)
-    blocks = select_global_topk(scores.cpu().numpy(), top_blocks)
-    m, l, o = legs.attend_blocks(blocks, b0, b1, rank == world - 1)
-    gm, gl, go = gather_triples(m, l, o, group)
-    return legs.merge(gm, gl, go), blocks
+    b0, b1 = block_ranges(n_old_blocks, world)[rank]
+    pairs = legs.topk_pairs(legs.score(b0, b1), b0, top_blocks)
+    blocks = legs.merge_pairs(_all_gather(pairs, group), top_blocks)
+    triples = legs.attend_blocks(blocks, b0, b1, rank == world - 1)
+    return legs.merge(_all_gather(triples, group)), blocks
 
 
 def dense_split_k(legs: Legs, seq_len: int, group=None):
     """One long sequence over the dense FP16 cache: attend own token range -> all-gather triples -> merge."""
     rank, world = _world(group)
     t0, t1 = token_ranges(seq_len, world)[rank]
-    m, l, o = legs.attend_tokens(t0, t1)
-    gm, gl, go = gather_triples(m, l, o, group)
-    return legs.merge(gm, gl, go)
+    return legs.merge(_all_gather(legs.attend_tokens(t0, t1), group))
+
+
+def host_topk_pairs(scores: np.ndarray, index_base: int, top_blocks: int) -> np.ndarray:
+    """Host statement of m40llm_topk_pairs_async (for plans and CPU tests): [q_heads, 64, 2] float32 whose [..., 1]
+    holds the u32 block ids as raw bits."""
+    scores = np.asarray(scores, np.float32)
+    q_heads = scores.shape[0]
+    sel = select_global_topk(scores, top_blocks) if scores.shape[1] else np.full((q_heads, MAX_TOP_BLOCKS), EMPTY_BLOCK, np.uint32)
+    out = np.empty((q_heads, MAX_TOP_BLOCKS, 2), np.float32)
+    ids = np.full((q_heads, MAX_TOP_BLOCKS), EMPTY_BLOCK, np.uint32)
+    sc = np.full((q_heads, MAX_TOP_BLOCKS), np.float32(SCORE_FLOOR), np.float32)
+    for h in range(q_heads):
+        live = sel[h] != EMPTY_BLOCK
+        ids[h, live] = sel[h, live] + np.uint32(index_base)
+        sc[h, live] = scores[h, sel[h, live]]
+    out[:, :, 0] = sc
+    out[:, :, 1] = ids.view(np.float32)
+    return out
+
+
+def host_merge_pairs(pairs: np.ndarray, top_blocks: int) -> np.ndarray:
+    """Host statement of m40llm_topk_merge_pairs_async: pairs [parts, q_heads, 64, 2] -> blocks [q_heads, 64] u32."""
+    pairs = np.ascontiguousarray(pairs, np.float32)
+    parts, q_heads = pairs.shape[0], pairs.shape[1]
+    sc = pairs[..., 0].transpose(1, 0, 2).reshape(q_heads, parts * MAX_TOP_BLOCKS)
+    ids = np.ascontiguousarray(pairs[..., 1]).view(np.uint32).transpose(1, 0, 2).reshape(q_heads, parts * MAX_TOP_BLOCKS)
+    out = np.full((q_heads, MAX_TOP_BLOCKS), EMPTY_BLOCK, np.uint32)
+    for h in range(q_heads):
+        ok = np.flatnonzero(~np.isnan(sc[h]) & (sc[h] > np.float32(SCORE_FLOOR)) & (ids[h] != EMPTY_BLOCK))
+        # descending score, ties to the lower block id
+        order = ok[np.lexsort((ids[h][ok], -sc[h][ok]))][:top_blocks]
+        out[h, :order.size] = ids[h][order]
+    return out
 
 
 class NativeLegs:
     """The legs over the CUDA library's split-K entry points. `lib` is the loaded C ABI (ctypes), `ctx`/`kv` its
-    handles; `q` is a CUDA f32 tensor [q_heads * head_dim]. Kernels run on the context's decode stream, the
-    collectives on torch's stream: each leg synchronises its stream before handing a tensor to the other side."""
+    handles; `q` is a CUDA f32 tensor [q_heads * head_dim]. Every leg only enqueues: the kernels run on the context's
+    decode stream, and `stream` (a torch view of that same stream, see `DeviceSplitK`) is where the collectives and
+    the buffer allocations are ordered, so nothing here synchronises with the host."""
 
     def __init__(self, lib, ctx, kv, q: torch.Tensor, q_heads: int, head_dim: int, seq_id: int, seq_len: int):
         if not q.is_cuda:
@@ -193,63 +238,88 @@ class NativeLegs:
         self.lib, self.ctx, self.kv, self.q = lib, ctx, kv, q.contiguous()
         self.qh, self.hd, self.seq, self.len = q_heads, head_dim, seq_id, seq_len
         self.dev = q.device
-
-    def _p(self, t: torch.Tensor):
-        return C.c_void_p(t.data_ptr())
-
-    def _sync(self):
-        rc = self.lib.m40llm_stream_synchronize(self.ctx, 1)
-        if rc != 0:
-            raise RuntimeError(f"m40llm_stream_synchronize failed: {rc}")
-
-    def _triples(self):
+        # buffers are made once: a steady-state call allocates nothing
         z = lambda *s: torch.empty(s, dtype=torch.float32, device=self.dev)
-        return z(self.qh), z(self.qh), z(self.qh, self.hd)
+        self._scores = None
+        self._pairs = z(q_heads, MAX_TOP_BLOCKS, 2)
+        self._blocks = torch.empty((q_heads, MAX_TOP_BLOCKS), dtype=torch.int32, device=self.dev)
+        self._triples = z(q_heads * (2 + head_dim))
+        self._out = z(q_heads * head_dim)
+
+    def _p(self, t: torch.Tensor, offset_floats: int = 0):
+        return C.c_void_p(t.data_ptr() + 4 * offset_floats)
+
+    def _check(self, rc: int, what: str):
+        if rc != 0:
+            raise RuntimeError(f"{what} failed: {rc}")
 
     def score(self, b0: int, b1: int) -> torch.Tensor:
-        out = torch.empty((self.qh, b1 - b0), dtype=torch.float32, device=self.dev)
-        torch.cuda.current_stream(self.dev).synchronize()
-        if b1 > b0:
-            rc = self.lib.m40llm_kvcache_score_old_blocks_async(self.ctx, self.kv, self.seq, self._p(self.q), self.qh,
-                                                                self.len, b0, b1, self._p(out))
-            if rc != 0:
-                raise RuntimeError(f"m40llm_kvcache_score_old_blocks_async failed: {rc}")
-            self._sync()
-        return out
+        n = b1 - b0
+        if self._scores is None or self._scores.shape[1] != max(n, 1):
+            self._scores = torch.empty((self.qh, max(n, 1)), dtype=torch.float32, device=self.dev)
+        if n > 0:
+            self._check(self.lib.m40llm_kvcache_score_old_blocks_async(self.ctx, self.kv, self.seq, self._p(self.q), self.qh,
+                                                                       self.len, b0, b1, self._p(self._scores)),
+                        "m40llm_kvcache_score_old_blocks_async")
+        return self._scores[:, :n]
 
-    def attend_blocks(self, blocks: np.ndarray, b0: int, b1: int, include_recent: bool):
-        m, l, o = self._triples()
-        # u32 block ids travel as their int32 bit patterns (torch has no general uint32 arithmetic)
-        packed = torch.from_numpy(np.ascontiguousarray(blocks, dtype=np.uint32).view(np.int32).copy()).to(self.dev)
-        torch.cuda.current_stream(self.dev).synchronize()
-        rc = self.lib.m40llm_attention_compressed_selected_partial_async(
-            self.ctx, self.kv, self.seq, self._p(self.q), self.qh, self.len, self._p(packed), b0, b1,
-            1 if include_recent else 0, self._p(m), self._p(l), self._p(o))
-        if rc != 0:
-            raise RuntimeError(f"m40llm_attention_compressed_selected_partial_async failed: {rc}")
-        self._sync()
-        return m, l, o
+    def topk_pairs(self, scores: torch.Tensor, b0: int, top: int) -> torch.Tensor:
+        n = scores.shape[1]
+        self._check(self.lib.m40llm_topk_pairs_async(self.ctx, self._p(self._scores), self.qh, n, self._scores.shape[1], b0,
+                                                     top, self._p(self._pairs)), "m40llm_topk_pairs_async")
+        return self._pairs
 
-    def attend_tokens(self, t0: int, t1: int):
-        m, l, o = self._triples()
-        torch.cuda.current_stream(self.dev).synchronize()
-        rc = self.lib.m40llm_attention_last_token_f32_gqa_partial_async(
-            self.ctx, self.kv, self.seq, self._p(self.q), self.qh, t0, t1, self._p(m), self._p(l), self._p(o))
-        if rc != 0:
-            raise RuntimeError(f"m40llm_attention_last_token_f32_gqa_partial_async failed: {rc}")
-        self._sync()
-        return m, l, o
+    def merge_pairs(self, pairs: torch.Tensor, top: int) -> torch.Tensor:
+        self._check(self.lib.m40llm_topk_merge_pairs_async(self.ctx, self._p(pairs), pairs.shape[0], self.qh, top,
+                                                           self._p(self._blocks), None), "m40llm_topk_merge_pairs_async")
+        return self._blocks
 
-    def merge(self, m: torch.Tensor, l: torch.Tensor, o: torch.Tensor) -> torch.Tensor:
-        parts = m.shape[0]
-        out = torch.empty(self.qh * self.hd, dtype=torch.float32, device=self.dev)
-        torch.cuda.current_stream(self.dev).synchronize()
-        rc = self.lib.m40llm_attention_merge_partials_async(self.ctx, self._p(m), self._p(l), self._p(o), parts,
-                                                            self.qh, self.hd, self._p(out))
-        if rc != 0:
-            raise RuntimeError(f"m40llm_attention_merge_partials_async failed: {rc}")
-        self._sync()
-        return out
+    def attend_blocks(self, blocks: torch.Tensor, b0: int, b1: int, include_recent: bool) -> torch.Tensor:
+        t = self._triples
+        self._check(self.lib.m40llm_attention_compressed_selected_partial_async(
+            self.ctx, self.kv, self.seq, self._p(self.q), self.qh, self.len, self._p(blocks), b0, b1,
+            1 if include_recent else 0, self._p(t), self._p(t, self.qh), self._p(t, 2 * self.qh)),
+            "m40llm_attention_compressed_selected_partial_async")
+        return t
+
+    def attend_tokens(self, t0: int, t1: int) -> torch.Tensor:
+        t = self._triples
+        self._check(self.lib.m40llm_attention_last_token_f32_gqa_partial_async(
+            self.ctx, self.kv, self.seq, self._p(self.q), self.qh, t0, t1, self._p(t), self._p(t, self.qh),
+            self._p(t, 2 * self.qh)), "m40llm_attention_last_token_f32_gqa_partial_async")
+        return t
+
+    def merge(self, triples: torch.Tensor) -> torch.Tensor:
+        self._check(self.lib.m40llm_attention_merge_gathered_async(self.ctx, self._p(triples), triples.shape[0], self.qh,
+                                                                   self.hd, self._p(self._out)),
+                    "m40llm_attention_merge_gathered_async")
+        return self._out
 
     def legs(self) -> Legs:
-        return Legs(self.score, self.attend_blocks, self.attend_tokens, self.merge)
+        return Legs(self.score, self.topk_pairs, self.merge_pairs, self.attend_blocks, self.attend_tokens, self.merge)
+
+
+class DeviceSplitK:
+    """Split-K attention of one long sequence with everything enqueued on the library's decode stream: the stream is
+    wrapped as a torch stream, made current around each call, and the NCCL all-gathers are ordered on it like the
+    kernels. A call returns once the work is enqueued; synchronise the decode stream (or time with events on it)
+    afterwards."""
+
+    def __init__(self, lib, ctx, kv, q: torch.Tensor, q_heads: int, head_dim: int, seq_id: int, seq_len: int, group=None):
+        handle = C.c_void_p()
+        rc = lib.m40llm_context_stream_handle(ctx, 1, C.byref(handle))
+        if rc != 0 or not handle.value:
+            raise RuntimeError(f"m40llm_context_stream_handle failed: {rc}")
+        self.stream = torch.cuda.ExternalStream(handle.value, device=q.device)
+        self.group = group
+        with torch.cuda.stream(self.stream):
+            self.native = NativeLegs(lib, ctx, kv, q, q_heads, head_dim, seq_id, seq_len)
+        self._legs = self.native.legs()
+
+    def compressed(self, n_old_blocks: int, top_blocks: int):
+        with torch.cuda.stream(self.stream):
+            return compressed_split_k(self._legs, n_old_blocks, top_blocks, self.group)
+
+    def dense(self, seq_len: int):
+        with torch.cuda.stream(self.stream):
+            return dense_split_k(self._legs, seq_len, self.group)

@@ -74,6 +74,24 @@ def test_select_global_topk_rule():
         splitk.select_global_topk(s, 65)
 
 
+def test_pair_exchange_equals_global_selection():
+    """Local top-k pairs per block range, then the merge of the gathered pairs, give the list the global rule gives
+    on the whole score matrix: every world size, ties across ranges, ranges shorter than the top count."""
+    rng = np.random.default_rng(12)
+    E = splitk.EMPTY_BLOCK
+    for nb, top in ((504, 64), (37, 8), (5, 8), (64, 64), (130, 1)):
+        scores = rng.standard_normal((6, nb)).astype(np.float32)
+        scores[0, ::7] = scores[0, 3]            # ties that straddle rank boundaries
+        scores[1, 5:9] = np.nan
+        scores[2, :] = -2e30                     # nothing selectable
+        want = splitk.select_global_topk(scores, top)
+        for world in (1, 2, 3, 8):
+            parts = [splitk.host_topk_pairs(scores[:, b:e], b, top) for b, e in splitk.block_ranges(nb, world)]
+            got = splitk.host_merge_pairs(np.stack(parts), top)
+            assert np.array_equal(got, want), (nb, top, world)
+    assert (splitk.host_merge_pairs(np.stack([splitk.host_topk_pairs(np.zeros((2, 0), np.float32), 0, 4)]), 4) == E).all()
+
+
 def test_select_global_topk_matches_oracle_selection():
     O = __import__("oracle.oracle", fromlist=["oracle"])
     rng = np.random.default_rng(8)
@@ -140,6 +158,15 @@ def _worker(rank, world, store_path, results):
                     for h in range(QH)]
             return torch.from_numpy(np.stack(rows).astype(np.float32))
 
+        def pack(m, l, o):  # one message per rank: m | l | o
+            return torch.from_numpy(np.concatenate([m, l, o.reshape(-1)]).astype(np.float32))
+
+        def topk_pairs(scores, b0, top):
+            return torch.from_numpy(splitk.host_topk_pairs(scores.numpy(), b0, top))
+
+        def merge_pairs(pairs, top):
+            return splitk.host_merge_pairs(pairs.numpy(), top)
+
         def attend_blocks(blocks, b0, b1, include_recent):
             m, l, o = np.empty(QH, np.float32), np.empty(QH, np.float32), np.empty((QH, HD), np.float32)
             for h in range(QH):
@@ -151,19 +178,20 @@ def _worker(rank, world, store_path, results):
                     keys = np.concatenate([keys, rk[slots, h // G].astype(np.float32)])
                     vals = np.concatenate([vals, rv[slots, h // G].astype(np.float32)])
                 m[h], l[h], o[h] = _partial(q[h * HD:(h + 1) * HD], keys, vals)
-            return torch.from_numpy(m), torch.from_numpy(l), torch.from_numpy(o)
+            return pack(m, l, o)
 
         def attend_tokens(t0, t1):
             m, l, o = np.empty(QH, np.float32), np.empty(QH, np.float32), np.empty((QH, HD), np.float32)
             for h in range(QH):
                 m[h], l[h], o[h] = _partial(q[h * HD:(h + 1) * HD], k[t0:t1, h // G].astype(np.float32),
                                             v[t0:t1, h // G].astype(np.float32))
-            return torch.from_numpy(m), torch.from_numpy(l), torch.from_numpy(o)
+            return pack(m, l, o)
 
-        def merge(m, l, o):
-            return torch.from_numpy(splitk.merge_triples(m.numpy(), l.numpy(), o.numpy()))
+        def merge(triples):
+            t = triples.numpy()
+            return torch.from_numpy(splitk.merge_triples(t[:, :QH], t[:, QH:2 * QH], t[:, 2 * QH:].reshape(-1, QH, HD)))
 
-        legs = splitk.Legs(score, attend_blocks, attend_tokens, merge)
+        legs = splitk.Legs(score, topk_pairs, merge_pairs, attend_blocks, attend_tokens, merge)
         out_c, blocks = splitk.compressed_split_k(legs, nb, TOP)
         out_d = splitk.dense_split_k(legs, L)
         results[rank] = (out_c.numpy().copy(), blocks.copy(), out_d.numpy().copy())
