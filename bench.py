@@ -465,6 +465,138 @@ def compressed_case(nat, ev, peak, calls=16, reps=20):
             "config": "16/2/128 heads, context 32768, ring 512, block 64, top 64"}
 
 
+def splitk_case(nat, pkg, O, rank, world, dist, peak, reps=200):
+    """One long sequence, split-K over the ranks (BASELINE configs[3]): Qwen2.5-3B heads (16 / 2 / 128), context 32768
+    in the FP16-K / q4-V cache, 512-token ring, 64-token blocks, top 64. Every rank loads ONLY its own block range of
+    old K / q4 V (the last rank also the ring); per call: local block scores -> local top-k pairs -> NCCL all-gather
+    -> global top-k -> attention over the rank's selected blocks -> NCCL all-gather of the (m, l, o) triples -> merge,
+    all enqueued on the decode stream with no host synchronisation. Also the whole Qwen-shaped layer around it
+    (projections replicated on every rank, f16 weights, QKV bias, NeoX RoPE). Times are CUDA events on the decode
+    stream, max over ranks. Rank 0 checks the attention output and the block lists against the oracle first."""
+    import torch
+    L_, ctx = nat.lib, nat.ctx
+    splitk = pkg.splitk
+    qh, kvh, hd, cL, cR, cbs, ctop, cH, cF = 16, 2, 128, 32768, 512, 64, 64, 2048, 11008
+    rng = np.random.default_rng(7)
+    k = rng.standard_normal((cL, kvh, hd), dtype=np.float32).astype(np.float16)
+    v = rng.standard_normal((cL, kvh, hd), dtype=np.float32).astype(np.float16)
+    q = rng.standard_normal(qh * hd, dtype=np.float32)
+    old_len = cL - cR
+    nb = (old_len + cbs - 1) // cbs
+    b0, b1 = splitk.block_ranges(nb, world)[rank]
+    t0, t1 = b0 * cbs, (cL if rank == world - 1 else min(b1 * cbs, old_len))
+    kvc = nat.kv_compressed(cL + 8, 1, kvh, hd, cR, cbs, ctop)
+    nat.kv_fill(kvc, 0, k[t0:t1], v[t0:t1], final_len=cL, tok_begin=t0)
+    dev = torch.device("cuda", torch.cuda.current_device())
+    dq = torch.from_numpy(q).to(dev)
+    if world > 1:
+        sk = splitk.DeviceSplitK(L_, ctx, kvc, dq, qh, hd, 0, cL)
+        attend = lambda: sk.compressed(nb, ctop)
+    else:
+        dout = torch.empty(qh * hd, dtype=torch.float32, device=dev)
+        torch.cuda.synchronize()
+        f = L_.m40llm_attention_last_token_f32_gqa_block_select_exact_fp16_k_q4_v_old_direct_async
+
+        def attend():
+            rc = f(ctx, kvc, 0, C.c_void_p(dq.data_ptr()), qh, cL, cR, cbs, ctop, C.c_void_p(dout.data_ptr()))
+            assert rc == 0, rc
+            return dout, None
+    torch.cuda.synchronize()
+    out, blocks = attend()
+    nat.sync(1)
+    record = {"config": "16/2/128 heads, context 32768, ring 512, block 64, top 64; each rank holds only its block range",
+              "ranks": world, "blocks_per_rank": [e - b for b, e in splitk.block_ranges(nb, world)]}
+    if rank == 0:  # parity first
+        old_k, q4, sc, rk, rv = O.compressed_state_from_dense(k, v, cL, cR)
+        exp, esel, ecnt, _ = O.attention_compressed(old_k, q4, sc, rk, rv, q, qh, cL, cR, cbs, ctop)
+        got = out.cpu().numpy()
+        err = np.abs(got.astype(np.float64) - exp)
+        if not np.all(err <= ATOL + RTOL * np.abs(exp)):
+            sys.stderr.write(f"PARITY FAILED: split-K attention over {world} rank(s), max err {err.max():.3e}\n")
+            raise SystemExit(3)
+        record["parity"] = {"max_abs_err": float(err.max()), "passed": True}
+        if blocks is not None:
+            got_b = blocks.cpu().numpy().view(np.uint32)
+            same = all(set(int(b) for b in got_b[h, :ctop]) == set(int(b) for b in esel[h, :ecnt[h]]) for h in range(qh))
+            record["parity"]["block_lists_equal_oracle"] = bool(same)
+    ev = Events(nat)
+    for _ in range(5):
+        attend()
+    nat.sync(1)
+    if dist is not None:
+        dist.barrier()
+    ev.start()
+    for _ in range(reps):
+        attend()
+    att_ms = ev.stop_ms() / reps
+
+    # the whole layer around it: weights replicated; the step re-appends the last token (position cL - 1) on every
+    # rank, so the block ranges stay those of the loaded data (the parity check above came first)
+    host = pkg.host
+    wr = np.random.default_rng(8)
+    mk = lambda *sh: nat.buf((wr.standard_normal(sh, dtype=np.float32) * np.float32(0.02)).astype(np.float16))
+    W = {"wq": mk(qh * hd, cH), "wk": mk(kvh * hd, cH), "wv": mk(kvh * hd, cH), "wo": mk(cH, qh * hd), "wg": mk(cF, cH),
+         "wu": mk(cF, cH), "wd": mk(cH, cF)}
+    Bq = nat.buf(wr.standard_normal(qh * hd, dtype=np.float32) * np.float32(0.02))
+    Bk = nat.buf(wr.standard_normal(kvh * hd, dtype=np.float32) * np.float32(0.02))
+    Bv = nat.buf(wr.standard_normal(kvh * hd, dtype=np.float32) * np.float32(0.02))
+    ones = nat.buf(np.ones(cH, np.float32))
+    dx = nat.buf(wr.standard_normal(cH, dtype=np.float32))
+    dqb, datt = torch.empty(qh * hd, dtype=torch.float32, device=dev), torch.empty(qh * hd, dtype=torch.float32, device=dev)
+    dx1, dhid, dlo = nat.buf(cH * 4), nat.buf(cF * 4), nat.buf(cH * 4)
+    dids, dpos = nat.buf(np.array([0], np.uint32)), nat.buf(np.array([cL - 1], np.uint32))
+    torch.cuda.synchronize()
+    if world > 1:
+        skl = splitk.DeviceSplitK(L_, ctx, kvc, dqb, qh, hd, 0, cL)
+
+    def layer():
+        rc = L_.m40llm_qkv_rmsnorm_rope_append_async(ctx, kvc, dx.ptr, ones.ptr, 1, EPS, W["wq"].ptr, W["wk"].ptr, W["wv"].ptr,
+                                                    Bq.ptr, Bk.ptr, Bv.ptr, dids.ptr, dpos.ptr, 1, cH, qh, 1e6, 1.0, 1,
+                                                    C.c_void_p(dqb.data_ptr()))
+        assert rc == 0, rc
+        if world > 1:
+            o, _ = skl.compressed(nb, ctop)
+            src = C.c_void_p(o.data_ptr())
+        else:
+            rc = L_.m40llm_attention_last_token_f32_gqa_block_select_exact_fp16_k_q4_v_old_direct_async(
+                ctx, kvc, 0, C.c_void_p(dqb.data_ptr()), qh, cL, cR, cbs, ctop, C.c_void_p(datt.data_ptr()))
+            assert rc == 0, rc
+            src = C.c_void_p(datt.data_ptr())
+        rc = L_.m40llm_attn_out_ffn_async(ctx, src, W["wo"].ptr, dx.ptr, ones.ptr, 1, EPS, W["wg"].ptr, W["wu"].ptr,
+                                          W["wd"].ptr, 0, dx1.ptr, dhid.ptr, dlo.ptr, 1, cH, qh * hd, cF)
+        assert rc == 0, rc
+
+    for _ in range(5):
+        layer()
+    nat.sync(1)
+    if dist is not None:
+        dist.barrier()
+    ev.start()
+    for _ in range(reps):
+        layer()
+    layer_ms = ev.stop_ms() / reps
+    nat.sync(1)
+    st = np.zeros(1, np.uint32)
+    assert L_.m40llm_context_take_device_status(ctx, st.ctypes.data) == 0 and st[0] == 0, int(st[0])
+    if dist is not None:
+        t = torch.tensor([att_ms, layer_ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        att_ms, layer_ms = float(t[0]), float(t[1])
+    # per rank: its share of the old K (scoring), the selected q4 V + scales, the ring on the last rank
+    cbytes = old_len * kvh * hd * 2 + qh * ctop * cbs * (hd // 2 + 4) + 2 * cR * kvh * hd * 2
+    wbytes = sum(b.nbytes for b in W.values())
+    record.update({"attention_ms": att_ms, "attention_calls_per_s": 1e3 / att_ms, "attention_algorithmic_bytes": cbytes,
+                   "attention_frac_of_hbm_peak": cbytes / (att_ms * 1e-3) / 1e9 / (peak * world),
+                   "layer_ms": layer_ms, "layer_tokens_per_s": 1e3 / layer_ms,
+                   "layer_note": f"Qwen2.5-3B-shaped layer (hidden {cH}, FFN {cF}, f16 weights {wbytes / 1e6:.0f} MB replicated on "
+                                 "every rank, QKV bias, NeoX RoPE theta 1e6), eager launches; only the attention shards",
+                   "exchange": "none (one rank)" if world == 1 else
+                               f"2 NCCL all-gathers per call on the decode stream: {qh * 64 * 8} B of top-k pairs and "
+                               f"{qh * (hd + 2) * 4} B of triples per rank; selection and merge on the device"})
+    L_.m40llm_kvcache_destroy(kvc)
+    return record
+
+
 def run_reference_arm(args, rank, world):
     """`--impl reference`: the reference's CPU path is Rust and cannot be built here (no cargo/rustc, no network),
     so the timed stand-in is the oracle port of that math, on all host threads. Rank 0 only. It is ONE CPU process on
@@ -514,6 +646,9 @@ def main():
                     help="small case for a profiler: the layer chain at ROWS rows, context 7969")
     ap.add_argument("--compressed-only", action="store_true",
                     help="small case for a profiler: the 32K compressed attention call alone")
+    ap.add_argument("--workload", default="layer", choices=["layer", "splitk"],
+                    help="layer: the batched decode layer (the contract's line); splitk: one 32K sequence, split-K over "
+                         "the ranks (its own JSON line)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     rank = int(os.environ.get("RANK", "0"))
@@ -530,6 +665,7 @@ def main():
     dist = None
     if world > 1:
         import torch.distributed as dist
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")  # the split-K exchange is two 8 KB all-gathers: plain rings
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     pkg = load_package()
     nat = pkg.native.Native(pkg.native.lib(), device=local_rank)
@@ -548,6 +684,19 @@ def main():
     if args.compressed_only:
         print(json.dumps({"case": "compressed32k", **compressed_case(nat, Events(nat), peak, calls=4, reps=max(args.steps, 1))}),
               flush=True)
+        return
+
+    if args.workload == "splitk":
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+        rec = splitk_case(nat, pkg, O, rank, world, dist, peak)
+        if rank == 0:
+            print(json.dumps({"metric": "splitk_attention_calls_per_s", "value": rec["attention_calls_per_s"], "unit": "calls/s",
+                              "n_gpus": world, "higher_is_better": True, "scaling": "strong", "dtype": "f32",
+                              "data": "synthetic", "config": {"workload": "qwen2.5-3b heads, one 32K sequence, compressed "
+                                                              "cache, split-K (BASELINE configs[3])"}, **rec}), flush=True)
+        if dist is not None:
+            dist.barrier()
+            dist.destroy_process_group()
         return
 
     # ---------------- the global batch, dealt to the ranks (src/decode_batch.rs:143-286 builds the per-GPU plan)
@@ -777,6 +926,12 @@ def main():
 
     if rank == 0 and not args.no_extras:
         extra["compressed32k"] = compressed_case(nat, ev, peak)
+
+    # ---------------- one long sequence, split-K over the ranks (BASELINE configs[3]); every rank takes part
+    if not args.no_extras:
+        sk_rec = splitk_case(nat, pkg, O, rank, world, dist, peak)
+        if rank == 0:
+            extra["splitk"] = sk_rec
 
     # ---------------- whole-model greedy decode at BASELINE configs[1] (TinyLlama-1.1B shape, batch 1, context 2048):
     # 22 distinct random f16 layers + lm_head, one CUDA graph per token step, ids chosen on the device.

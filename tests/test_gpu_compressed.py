@@ -184,7 +184,58 @@ def test_qwen_long_context_shape(nat, O):
     assert nat.lib.m40llm_attention_merge_partials_async(nat.ctx, dm.ptr, dl.ptr, dop.ptr, P, qh, hd, do.ptr) == 0
     nat.sync(1)
     assert_close(do.download(np.float32, q.shape), exp, what="compressed split-K merge")
+    # the same exchange with the selection on the device: local top-k (score, block) pairs per rank, the "gathered"
+    # pair array, the global list, triples as one message per rank, the gathered merge; no host step in between
+    for P2 in (1, 3, 8):
+        b2 = [r * nb // P2 for r in range(P2 + 1)]
+        dpairs = nat.buf(P2 * qh * 64 * 2 * 4)
+        widest = max(b2[r + 1] - b2[r] for r in range(P2))
+        dsc = nat.buf(qh * widest * 4)
+        for r in range(P2):
+            n = b2[r + 1] - b2[r]
+            assert nat.lib.m40llm_kvcache_score_old_blocks_async(nat.ctx, kv, 0, dq.ptr, qh, L, b2[r], b2[r + 1], dsc.ptr) == 0
+            assert nat.lib.m40llm_topk_pairs_async(nat.ctx, dsc.ptr, qh, n, n, b2[r], top, dpairs.ptr + r * qh * 64 * 8) == 0
+        dglob, dgsc = nat.buf(qh * 64 * 4), nat.buf(qh * 64 * 4)
+        assert nat.lib.m40llm_topk_merge_pairs_async(nat.ctx, dpairs.ptr, P2, qh, top, dglob.ptr, dgsc.ptr) == 0
+        dtr = nat.buf(P2 * qh * (2 + hd) * 4)
+        for r in range(P2):
+            base = dtr.ptr + r * qh * (2 + hd) * 4
+            rc = nat.lib.m40llm_attention_compressed_selected_partial_async(
+                nat.ctx, kv, 0, dq.ptr, qh, L, dglob.ptr, b2[r], b2[r + 1], 1 if r == P2 - 1 else 0,
+                base, base + qh * 4, base + 2 * qh * 4)
+            assert rc == 0, rc
+        assert nat.lib.m40llm_attention_merge_gathered_async(nat.ctx, dtr.ptr, P2, qh, hd, do.ptr) == 0
+        nat.sync(1)
+        dev_glob = dglob.download(np.uint32, (qh, 64))
+        dev_gsc = dgsc.download(np.float32, (qh, 64))
+        for h in range(qh):
+            _, _, _, s64 = O.block_select_head(old_k, q[h * hd:(h + 1) * hd], h // (qh // kvh), L - R, bs, top)
+            assert_selection_matches([int(b) for b in dev_glob[h, :top]], [int(b) for b in esel[h, :ecnt[h]]], s64,
+                                     what=f"device top-k over {P2} ranks, head {h}")
+            assert np.all(np.diff(dev_gsc[h, :top]) <= 0), "scores must be in descending order"
+        assert_close(do.download(np.float32, q.shape), exp, what=f"device-side split-K over {P2} ranks")
     nat.lib.m40llm_kvcache_destroy(kv)
+    nat.free_all()
+
+
+def test_topk_pairs_rules(nat):
+    """Ties go to the lower block, NaN and scores <= -1e30 are never chosen, short candidate lists leave empty slots,
+    and a list shorter than a previous call's leaves nothing stale behind."""
+    E = 0xFFFFFFFF
+    s = np.array([[1.0, 3.0, 3.0, np.nan, -2e30, 2.0, 3.0], [0.5, 0.5, 0.5, 0.5, 0.5, 0.5, 0.5]], np.float32)
+    ds, dp = nat.buf(s), nat.buf(2 * 64 * 2 * 4)
+    for top, want0, want1 in ((64, [101, 102, 106, 105, 100], [100, 101, 102, 103, 104, 105, 106]), (2, [101, 102], [100, 101])):
+        assert nat.lib.m40llm_topk_pairs_async(nat.ctx, ds.ptr, 2, 7, 7, 100, top, dp.ptr) == 0
+        nat.sync(1)
+        pairs = dp.download(np.uint32, (2, 64, 2))
+        ids = pairs[:, :, 1]
+        assert list(ids[0, :len(want0)]) == want0 and (ids[0, len(want0):] == E).all()
+        assert list(ids[1, :len(want1)]) == want1 and (ids[1, len(want1):] == E).all()
+        sc = pairs[:, :, 0].view(np.float32)
+        assert sc[0, 0] == 3.0 and sc[0, 1] == 3.0
+    assert nat.lib.m40llm_topk_pairs_async(nat.ctx, ds.ptr, 2, 7, 7, 0, 65, dp.ptr) == -2
+    assert nat.lib.m40llm_topk_pairs_async(nat.ctx, ds.ptr, 2, 5000, 5000, 0, 8, dp.ptr) == -2
+    assert nat.lib.m40llm_topk_merge_pairs_async(nat.ctx, None, 1, 2, 8, dp.ptr, None) == -1
     nat.free_all()
 
 
