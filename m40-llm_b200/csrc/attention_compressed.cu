@@ -15,8 +15,11 @@
 #include <stdlib.h>
 #include <string.h>
 
+#include <atomic>
+
 #include "attention.cuh"
 #include "common.cuh"
+#include "tc_ptx.cuh"
 
 namespace {
 
@@ -39,6 +42,7 @@ struct SelArgs {
     uint32_t block_begin, block_end;  // blocks this call may read (split-K); [0, nb) otherwise
     uint32_t score_stride, include_recent, splits;
     float inv_sqrt;
+    uint32_t* status_word;  // the context's device status word
 };
 
 // ---- 1. block scores. grid (ceil(blocks/4), kv_heads), 128 threads; a warp per block. ----
@@ -87,6 +91,83 @@ __global__ void __launch_bounds__(128) block_score_kernel(SelArgs a) {
         // reduce over the LPT lanes that hold distinct pieces
 #pragma unroll
         for (int o = LPT / 2; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+        if (lane == 0) a.scores[(size_t)(kvh * G + g) * a.score_stride + (b - a.block_begin)] = (dot * inv_len) * a.inv_sqrt;
+    }
+}
+
+// ---- 1b. block scores with the K rows staged by bulk copies. Same grid and result as block_score_kernel; the CTA's
+// four blocks (contiguous in the head-major cache) arrive as four 1-D bulk async copies on one mbarrier, so all of a
+// launch's bytes are in flight at once and the pass costs one memory round trip plus the transfer instead of a chain
+// of dependent loads per warp. Shared memory: q of the group [G][HD] f32, then 4 x block_size x HD f16.
+template <int HD>
+__global__ void __launch_bounds__(128) block_score_bulk_kernel(SelArgs a) {
+    constexpr int DPL = HD / 32;  // dims per lane
+    extern __shared__ __align__(128) unsigned char bs_smem[];
+    __shared__ uint64_t bar;
+    const uint32_t G = a.q_heads / a.kv_heads;
+    float* sq = reinterpret_cast<float*>(bs_smem);
+    __half* sk = reinterpret_cast<__half*>(bs_smem + (((size_t)G * HD * sizeof(float) + 127u) & ~(size_t)127u));
+    const uint32_t kvh = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+    const uint32_t b_first = a.block_begin + blockIdx.x * 4u;
+    const __half* Kh = a.old_k + kv_row_offset(a.seq_id, kvh, 0, a.kv_heads, a.max_seq_len, HD);
+    // q, and the newest old K row (an append evicts the ring's oldest token into the old region), come from the
+    // kernel before this one
+    pdl_wait();
+    pdl_trigger();
+    if (threadIdx.x == 0) {
+        tc::mbar_init(&bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        uint32_t total = 0;
+        for (uint32_t w = 0; w < 4u; ++w) {
+            const uint32_t b = b_first + w;
+            if (b >= a.block_end) break;
+            const uint32_t t0 = b * a.block_size, t1 = min(t0 + a.block_size, a.old_len);
+            total += (t1 - t0) * HD * 2u;
+        }
+        tc::mbar_expect_tx(&bar, total);
+        for (uint32_t w = 0; w < 4u; ++w) {
+            const uint32_t b = b_first + w;
+            if (b >= a.block_end) break;
+            const uint32_t t0 = b * a.block_size, t1 = min(t0 + a.block_size, a.old_len);
+            const uint32_t bytes = (t1 - t0) * HD * 2u;
+            asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                         ::"r"(tc::smem_u32(sk + (size_t)w * a.block_size * HD)), "l"(Kh + (size_t)t0 * HD), "r"(bytes),
+                           "r"(tc::smem_u32(&bar)) : "memory");
+        }
+    }
+    for (uint32_t i = threadIdx.x; i < G * HD; i += blockDim.x) sq[i] = a.q[(size_t)kvh * G * HD + i];
+    __syncthreads();  // also publishes the barrier's initialisation
+    const bool landed = tc::mbar_wait(&bar, 0u);
+    if (!landed) {  // never seen; the copies may still be in flight, so the CTA may not leave its shared memory yet
+        if (threadIdx.x == 0) atomicOr(a.status_word, 4u);
+        tc::mbar_wait(&bar, 0u);
+        return;
+    }
+    const uint32_t b = b_first + warp;
+    if (b >= a.block_end) return;
+    const uint32_t t0 = b * a.block_size, t1 = min(t0 + a.block_size, a.old_len), n = t1 - t0;
+    const __half* rows = sk + (size_t)warp * a.block_size * HD + lane * DPL;
+    float acc[DPL];
+#pragma unroll
+    for (int j = 0; j < DPL; ++j) acc[j] = 0.0f;
+#pragma unroll 8
+    for (uint32_t t = 0; t < n; ++t) {
+        if (DPL == 4) {
+            const uint2 w = *reinterpret_cast<const uint2*>(rows + (size_t)t * HD);
+            const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&w.x));
+            const float2 f1 = __half22float2(*reinterpret_cast<const __half2*>(&w.y));
+            acc[0] += f0.x, acc[1] += f0.y, acc[DPL - 2] += f1.x, acc[DPL - 1] += f1.y;
+        } else {
+            const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(rows + (size_t)t * HD));
+            acc[0] += f0.x, acc[1] += f0.y;
+        }
+    }
+    const float inv_len = 1.0f / (float)n;
+    for (uint32_t g = 0; g < G; ++g) {
+        float dot = 0.0f;
+#pragma unroll
+        for (int j = 0; j < DPL; ++j) dot = fmaf(sq[g * HD + lane * DPL + j], acc[j], dot);
+        dot = warp_sum(dot);
         if (lane == 0) a.scores[(size_t)(kvh * G + g) * a.score_stride + (b - a.block_begin)] = (dot * inv_len) * a.inv_sqrt;
     }
 }
@@ -394,6 +475,196 @@ __global__ void __launch_bounds__(128) selected_attend_kernel(SelArgs a) {
     }
 }
 
+// ---- 3b. attention over the selected tokens with K and V staged by bulk copies (compressed cache only).
+// Work items per q head: the 64 list entries (one selected block each: K f16 rows and q4 V rows are contiguous in the
+// head-major cache) followed by pieces of the recent ring (`ring_piece` slots each: K and V f16). A warp takes one
+// item: two bulk async copies into its own slice of shared memory on its own mbarrier, then the dot products, the
+// online softmax and the V accumulation run from shared memory. All of a launch's bytes are in flight at once, where
+// the gather form issues them as dependent rounds of loads. grid (ceil(items / 4), q_heads), 128 threads; one
+// (m, l, o) partial per CTA, merged by the same kernel as before.
+template <int HD>
+__global__ void __launch_bounds__(128) selected_attend_staged_kernel(SelArgs a, uint32_t slice_bytes, uint32_t ring_piece,
+                                                                     uint32_t ring_items) {
+    constexpr int DPL = HD / 32;  // dims per lane, contiguous
+    extern __shared__ __align__(128) unsigned char st_smem[];
+    __shared__ uint64_t bars[4];
+    __shared__ float sm_m[4], sm_l[4], sm_o[4][HD];
+    const uint32_t h = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+    const uint32_t G = a.q_heads / a.kv_heads, kvh = h / G;
+    const uint32_t item = blockIdx.x * 4u + warp;
+    unsigned char* slice = st_smem + (size_t)warp * slice_bytes;
+    pdl_wait();
+    pdl_trigger();
+    // ---- what this warp's item is
+    uint32_t n = 0, tok0 = 0;
+    bool ring = false;
+    if (item < 64u) {
+        const uint32_t b = a.sel_blocks[h * 64u + item];
+        if (b != 0xffffffffu && b >= a.block_begin && b < a.block_end) {
+            tok0 = b * a.block_size;
+            if (tok0 < a.old_len) n = min(a.block_size, a.old_len - tok0);
+        }
+    } else if (a.include_recent && item - 64u < ring_items) {
+        ring = true;
+        const uint32_t recent_n = a.seq_len - a.old_len;  // the ring's live slots are [0, recent_n)
+        tok0 = (item - 64u) * ring_piece;
+        if (tok0 < recent_n) n = min(ring_piece, recent_n - tok0);
+    }
+    const size_t vec_base = ((size_t)a.seq_id * a.kv_heads + kvh) * (size_t)a.max_seq_len;
+    const uint32_t k_bytes = n * HD * 2u, v_bytes = ring ? k_bytes : n * (HD / 2u);
+    if (lane == 0 && n) {
+        tc::mbar_init(&bars[warp], 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        tc::mbar_expect_tx(&bars[warp], k_bytes + v_bytes);
+        const void *ksrc, *vsrc;
+        if (ring) {
+            const size_t off = kv_row_offset(a.seq_id, kvh, tok0, a.kv_heads, a.ring_size, HD);
+            ksrc = a.ring_k + off;
+            vsrc = a.ring_v + off;
+        } else {
+            ksrc = a.old_k + kv_row_offset(a.seq_id, kvh, tok0, a.kv_heads, a.max_seq_len, HD);
+            vsrc = a.q4_v + (vec_base + tok0) * (HD / 2u);
+        }
+        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                     ::"r"(tc::smem_u32(slice)), "l"(ksrc), "r"(k_bytes), "r"(tc::smem_u32(&bars[warp])) : "memory");
+        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                     ::"r"(tc::smem_u32(slice + k_bytes)), "l"(vsrc), "r"(v_bytes), "r"(tc::smem_u32(&bars[warp])) : "memory");
+    }
+    float qr[DPL], acc[DPL];
+#pragma unroll
+    for (int j = 0; j < DPL; ++j) {
+        qr[j] = a.q[(size_t)h * HD + lane * DPL + j];
+        acc[j] = 0.0f;
+    }
+    // q4 scales of this item's tokens: lane l holds tokens l and l + 32 (blocks of at most 64 tokens)
+    float sc_lo = 0.0f, sc_hi = 0.0f;
+    if (!ring && n) {
+        if (lane < n) sc_lo = a.q4_scale[vec_base + tok0 + lane];
+        if (lane + 32u < n) sc_hi = a.q4_scale[vec_base + tok0 + lane + 32u];
+    }
+    float m = -INFINITY, l = 0.0f;
+    __syncwarp();
+    if (n) {
+        if (!tc::mbar_wait(&bars[warp], 0u)) {  // never seen; wait on, the copies target this CTA's shared memory
+            if (lane == 0) atomicOr(a.status_word, 4u);
+            tc::mbar_wait(&bars[warp], 0u);
+            n = 0;
+        }
+    }
+    const __half* sK = reinterpret_cast<const __half*>(slice) + lane * DPL;
+    const unsigned char* sV = slice + k_bytes;
+    constexpr int U = 8;
+    for (uint32_t t0 = 0; t0 < n; t0 += U) {
+        float sc[U];
+#pragma unroll
+        for (int i = 0; i < U; ++i) {
+            const uint32_t t = min(t0 + i, n - 1u);
+            float dot;
+            if (DPL == 4) {
+                const uint2 w = *reinterpret_cast<const uint2*>(sK + (size_t)t * HD);
+                const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&w.x));
+                const float2 f1 = __half22float2(*reinterpret_cast<const __half2*>(&w.y));
+                dot = fmaf(qr[0], f0.x, 0.0f);
+                dot = fmaf(qr[1], f0.y, dot);
+                dot = fmaf(qr[DPL - 2], f1.x, dot);
+                dot = fmaf(qr[DPL - 1], f1.y, dot);
+            } else {
+                const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(sK + (size_t)t * HD));
+                dot = fmaf(qr[0], f0.x, 0.0f);
+                dot = fmaf(qr[1], f0.y, dot);
+            }
+            sc[i] = dot;
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+            for (int i = 0; i < U; ++i) sc[i] += __shfl_xor_sync(0xffffffffu, sc[i], o);
+#pragma unroll
+        for (int i = 0; i < U; ++i) {
+            const uint32_t t = t0 + i;
+            if (t >= n) break;  // warp-uniform
+            const float s = sc[i] * a.inv_sqrt;
+            float vx[DPL];
+            if (!ring) {
+                const float scale = __shfl_sync(0xffffffffu, t < 32u ? sc_lo : sc_hi, t & 31u);
+                uint32_t bits;
+                if (DPL == 4) bits = *reinterpret_cast<const uint16_t*>(sV + (size_t)t * (HD / 2) + lane * 2);
+                else bits = sV[(size_t)t * (HD / 2) + lane];
+#pragma unroll
+                for (int j = 0; j < DPL; ++j) {
+                    // signed nibble as an exact float without a conversion instruction: 2^23 + (nib ^ 8) - (2^23 + 8)
+                    const uint32_t nib = (bits >> (4 * j)) & 0xfu;
+                    const float sv = __uint_as_float(0x4B000000u | (nib ^ 8u)) - 8388616.0f;
+                    vx[j] = __half2float(__float2half_rn(sv * scale));
+                }
+            } else {
+                const __half* vp = reinterpret_cast<const __half*>(sV) + (size_t)t * HD + lane * DPL;
+                const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(vp));
+                vx[0] = f0.x, vx[1] = f0.y;
+                if (DPL == 4) {
+                    const float2 f1 = __half22float2(*reinterpret_cast<const __half2*>(vp + 2));
+                    vx[DPL - 2] = f1.x, vx[DPL - 1] = f1.y;
+                }
+            }
+            const float mn = fmaxf(m, s);
+            const float corr = expf(m - mn);
+            const float pw = expf(s - mn);
+            l = l * corr + pw;
+#pragma unroll
+            for (int j = 0; j < DPL; ++j) acc[j] = fmaf(pw, vx[j], acc[j] * corr);
+            m = mn;
+        }
+    }
+    if (lane == 0) {
+        sm_m[warp] = m;
+        sm_l[warp] = l;
+    }
+#pragma unroll
+    for (int j = 0; j < DPL; ++j) sm_o[warp][lane * DPL + j] = acc[j];
+    __syncthreads();
+    for (uint32_t d = threadIdx.x; d < HD; d += blockDim.x) {
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) M = fmaxf(M, sm_m[w]);
+        float L = 0.0f, O = 0.0f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const float e = sm_m[w] == -INFINITY ? 0.0f : expf(sm_m[w] - M);
+            L += sm_l[w] * e;
+            O += sm_o[w][d] * e;
+        }
+        const size_t pi = (size_t)h * a.splits + blockIdx.x;
+        if (d == 0) {
+            a.part_m[pi] = M;
+            a.part_l[pi] = L;
+        }
+        a.part_o[pi * HD + d] = O;
+    }
+}
+
+// Shape of the staged attend launch for this call, or splits == 0 when the gather form has to be used.
+struct StagedPlan {
+    uint32_t slice_bytes, ring_piece, ring_items, splits;
+};
+
+StagedPlan plan_staged(const SelArgs& a, bool dense) {
+    StagedPlan p = {};
+    if (dense || a.block_size > 64u || a.block_size == 0u) return p;
+    uint32_t slice = a.block_size * (a.hd * 2u + a.hd / 2u);
+    slice = (slice + 127u) & ~127u;
+    if (slice > 24u * 1024u) return p;
+    uint32_t piece = slice / (a.hd * 4u);  // ring slots whose K and V rows (f16) fit one slice
+    piece &= ~7u;
+    if (piece == 0u) return p;
+    const uint32_t recent_n = a.seq_len - a.old_len;
+    p.slice_bytes = slice;
+    p.ring_piece = piece;
+    p.ring_items = (recent_n + piece - 1u) / piece;
+    p.splits = (64u + p.ring_items + 3u) / 4u;
+    if (p.splits > 256u) p.splits = 0;  // the merge kernel's limit
+    return p;
+}
+
 struct SelPlan {
     uint32_t old_len, nb, top_n, recent_count;
 };
@@ -435,15 +706,32 @@ int fill_common(const M40llmKVCache* kv, SelArgs* a, uint32_t seq_id, const void
     return 0;
 }
 
-int launch_scores(M40llmCudaContext* ctx, const SelArgs& a) {
-    const uint32_t blocks = a.block_end - a.block_begin;
+int launch_scores(M40llmCudaContext* ctx, const SelArgs& a0) {
+    const uint32_t blocks = a0.block_end - a0.block_begin;
     if (blocks == 0) return 0;
+    SelArgs a = a0;
+    a.status_word = ctx->d_status;
     const uint32_t G = a.q_heads / a.kv_heads;
     dim3 grid((blocks + 3u) / 4u, a.kv_heads);
-    const size_t smem = (size_t)G * a.hd * sizeof(float);
+    const size_t qbytes = ((size_t)G * a.hd * sizeof(float) + 127u) & ~(size_t)127u;
+    const size_t bulk_smem = qbytes + (size_t)4 * a.block_size * a.hd * sizeof(__half);
     cudaError_t e;
-    if (a.hd == 128) e = m40_launch_dependent(block_score_kernel<128>, grid, dim3(128), smem, ctx->decode_stream, a);
-    else e = m40_launch_dependent(block_score_kernel<64>, grid, dim3(128), smem, ctx->decode_stream, a);
+    // staged form: whole 16-byte pieces per block and at most 96 KB per CTA (two or three CTAs per SM)
+    if ((a.block_size * a.hd * 2u) % 16u == 0u && bulk_smem <= 96u * 1024u) {
+        auto kern = a.hd == 128 ? block_score_bulk_kernel<128> : block_score_bulk_kernel<64>;
+        static std::atomic<unsigned long long> configured[2];
+        const unsigned long long bit = 1ull << (ctx->device_id & 63);
+        std::atomic<unsigned long long>& cfgd = configured[a.hd == 128 ? 1 : 0];
+        if (!(cfgd.load(std::memory_order_acquire) & bit)) {
+            if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024) != cudaSuccess) return -8;
+            cfgd.fetch_or(bit, std::memory_order_release);
+        }
+        e = m40_launch_dependent(kern, grid, dim3(128), bulk_smem, ctx->decode_stream, a);
+    } else {
+        const size_t smem = (size_t)G * a.hd * sizeof(float);
+        if (a.hd == 128) e = m40_launch_dependent(block_score_kernel<128>, grid, dim3(128), smem, ctx->decode_stream, a);
+        else e = m40_launch_dependent(block_score_kernel<64>, grid, dim3(128), smem, ctx->decode_stream, a);
+    }
     M40_COUNT_LAUNCH(ctx);
     return e == cudaSuccess && cudaGetLastError() == cudaSuccess ? 0 : -8;
 }
@@ -487,10 +775,28 @@ int launch_topk(M40llmCudaContext* ctx, const SelArgs& a) {
     return cudaGetLastError() == cudaSuccess ? 0 : -8;
 }
 
-int launch_attend(M40llmCudaContext* ctx, const SelArgs& a, bool dense) {
-    dim3 grid(a.splits, a.q_heads);
+int launch_attend(M40llmCudaContext* ctx, const SelArgs& a0, bool dense) {
+    SelArgs a = a0;
+    a.status_word = ctx->d_status;
     cudaStream_t s = ctx->decode_stream;
     cudaError_t e;
+    const StagedPlan sp = plan_staged(a, dense);
+    if (sp.splits != 0 && sp.splits == a.splits) {  // the caller sized its partials with attend_splits(): same plan
+        auto kern = a.hd == 128 ? selected_attend_staged_kernel<128> : selected_attend_staged_kernel<64>;
+        const size_t smem = (size_t)4 * sp.slice_bytes;
+        static std::atomic<unsigned long long> configured[2];
+        const unsigned long long bit = 1ull << (ctx->device_id & 63);
+        std::atomic<unsigned long long>& cfgd = configured[a.hd == 128 ? 1 : 0];
+        if (!(cfgd.load(std::memory_order_acquire) & bit)) {
+            if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024) != cudaSuccess) return -8;
+            cfgd.fetch_or(bit, std::memory_order_release);
+        }
+        e = m40_launch_dependent(kern, dim3(sp.splits, a.q_heads), dim3(128), smem, s, a, sp.slice_bytes, sp.ring_piece,
+                                 sp.ring_items);
+        M40_COUNT_LAUNCH(ctx);
+        return e == cudaSuccess && cudaGetLastError() == cudaSuccess ? 0 : -8;
+    }
+    dim3 grid(a.splits, a.q_heads);
     if (a.hd == 128) {
         if (dense) e = m40_launch_dependent(selected_attend_kernel<128, true>, grid, dim3(128), 0, s, a);
         else e = m40_launch_dependent(selected_attend_kernel<128, false>, grid, dim3(128), 0, s, a);
@@ -502,7 +808,9 @@ int launch_attend(M40llmCudaContext* ctx, const SelArgs& a, bool dense) {
     return e == cudaSuccess && cudaGetLastError() == cudaSuccess ? 0 : -8;
 }
 
-uint32_t attend_splits(const M40llmCudaContext* ctx, const SelArgs& a) {
+uint32_t attend_splits(const M40llmCudaContext* ctx, const SelArgs& a, bool dense = false) {
+    const StagedPlan sp = plan_staged(a, dense);
+    if (sp.splits != 0 && getenv("M40LLM_ATTEND_GATHER") == nullptr) return sp.splits;  // one partial per staged CTA
     const uint32_t total = 64u * a.block_size + (a.seq_len - a.old_len);
     // ~8 CTAs per SM, never fewer than 64 slots per CTA: the kernel is latency-bound, so parallelism is what counts
     uint32_t splits = ((uint32_t)ctx->sm_count * 8u + a.q_heads - 1u) / a.q_heads;
@@ -520,7 +828,7 @@ int block_select_attention(M40llmCudaContext* ctx, const M40llmKVCache* kv, uint
     if (q_heads > ctx->selected_capacity_heads) return -7;
     SelArgs a = {};
     fill_common(kv, &a, seq_id, q, q_heads, seq_len, recent_window, block_size, top_blocks, dense);
-    a.splits = attend_splits(ctx, a);
+    a.splits = attend_splits(ctx, a, dense);
     const size_t n_scores = (size_t)q_heads * a.score_stride;
     const size_t n_part = (size_t)q_heads * a.splits;
     float* scratch = (float*)m40_ensure_scratch(ctx, 1, (n_scores + n_part * (2 + (size_t)a.hd)) * sizeof(float));

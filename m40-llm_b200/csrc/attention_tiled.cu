@@ -363,6 +363,7 @@ struct FusedRowArgs {
     const uint32_t* positions;
     const uint32_t* seq_lens;
     uint32_t* status;
+    const float* inv_freq;  // [hd / 2] host-made table, or null: evaluate the power on the device
     uint32_t max_seq_len, max_batch, kv_heads, q_heads, layout;
     float freq_base, freq_scale, inv_sqrt;
 };
@@ -413,7 +414,13 @@ __global__ void __launch_bounds__(128 * FUSED_WG, 1) attn_decode_fused_row_kerne
     // ---- rotation table, rotated q, and (last CTA) the new token
     if (tid < HALF) {
         float c, sn;
-        rope_cs(pos, tid, HD, a.freq_base, a.freq_scale, &c, &sn);
+        if (a.inv_freq) {  // the same angle as rope_cs, its power taken from the table
+            const float theta = (static_cast<float>(pos) * a.freq_scale) * a.inv_freq[tid];
+            c = cosf(theta);
+            sn = sinf(theta);
+        } else {
+            rope_cs(pos, tid, HD, a.freq_base, a.freq_scale, &c, &sn);
+        }
         s_cs[tid] = make_float2(c, sn);
     }
     for (uint32_t i = tid; i < 16 * HD; i += blockDim.x) (&s_q[0][0])[i] = 0.0f;
@@ -618,6 +625,7 @@ int m40_attention_fused_row(M40llmCudaContext* ctx, M40llmKVCache* kv, const flo
     a.positions = positions;
     a.seq_lens = seq_lens;
     a.status = ctx->d_status;
+    a.inv_freq = m40_rope_inv_freq(ctx, freq_base, kv->head_dim);
     a.max_seq_len = kv->max_seq_len;
     a.max_batch = kv->max_batch_size;
     a.kv_heads = kv->num_heads;

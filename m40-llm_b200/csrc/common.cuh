@@ -46,6 +46,11 @@ struct M40llmCudaContext {
     // Device status word (bit 0: a batched-attention row was out of range and skipped).
     uint32_t* d_status;
     unsigned long long launches;
+    // Inverse RoPE frequencies per (base, head_dim), made on the host (see m40_rope_inv_freq) and kept on the device.
+    float* d_rope_inv_freq[4];
+    float rope_table_base[4];
+    uint32_t rope_table_hd[4];
+    uint32_t rope_tables;
     // Prefetch hint for the next streaming launch on the decode stream: up to two ranges it pulls into L2 while it
     // drains (the head of the weights that the launch after it will stream). Consumed and cleared by that launch.
     const void* pf_hint_ptr[2];
@@ -189,6 +194,13 @@ __device__ __forceinline__ void rope_cs(uint32_t pos, uint32_t pair, uint32_t he
     *c = cosf(theta);
     *s = sinf(theta);
 }
+
+// Device table of the head_dim / 2 inverse frequencies that rope_cs() evaluates per call: the same float-rounded
+// values (the exponent in float, the power in double, rounded once), computed on the host where double precision is
+// cheap. On this GPU a double-precision pow per rotation pair costs microseconds. Returns null when no table can be
+// made right now (the stream is being captured and this pair of parameters was never seen eagerly; four pairs are
+// kept per context): kernels then fall back to rope_cs().
+const float* m40_rope_inv_freq(M40llmCudaContext* ctx, float freq_base, uint32_t head_dim);
 
 // softmax scale as the reference kernels spell it (kernels.cu:2869) for 64/128, 1/sqrt otherwise (kernels.cu:1384)
 __host__ __device__ __forceinline__ float attn_inv_sqrt(uint32_t head_dim) {

@@ -1,6 +1,7 @@
 // Context, streams, events, graphs and raw memory entry points of the C ABI.
 // These are thin CUDA-runtime wrappers; their argument checks and return codes follow
 // cuda/kernels.cu:302-680, 1245-1292, 8027-8042 of the reference.
+#include <math.h>
 #include <stdlib.h>
 #include <string.h>
 
@@ -38,6 +39,37 @@ void* m40_ensure_scratch(M40llmCudaContext* ctx, uint32_t kind, size_t bytes, ui
     ctx->scratch_bytes[kind][level] = want;
     ctx->scratch_generation++;
     return p;
+}
+
+const float* m40_rope_inv_freq(M40llmCudaContext* ctx, float freq_base, uint32_t head_dim) {
+    if (!ctx || head_dim < 2 || head_dim > 512) return nullptr;
+    for (uint32_t i = 0; i < ctx->rope_tables; ++i)
+        if (ctx->rope_table_base[i] == freq_base && ctx->rope_table_hd[i] == head_dim) return ctx->d_rope_inv_freq[i];
+    if (ctx->rope_tables >= 4) return nullptr;
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(ctx->decode_stream, &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone) return nullptr;
+    float host[256];
+    const uint32_t half = head_dim / 2u;
+    for (uint32_t i = 0; i < half; ++i) {
+        const float e = -2.0f * static_cast<float>(i) / static_cast<float>(head_dim);
+        host[i] = static_cast<float>(pow(static_cast<double>(freq_base), static_cast<double>(e)));
+    }
+    float* d = nullptr;
+    if (cudaMalloc(&d, half * sizeof(float)) != cudaSuccess) {
+        cudaGetLastError();
+        return nullptr;
+    }
+    if (cudaMemcpy(d, host, half * sizeof(float), cudaMemcpyHostToDevice) != cudaSuccess ||
+        cudaStreamSynchronize(cudaStreamLegacy) != cudaSuccess) {
+        cudaGetLastError();
+        cudaFree(d);
+        return nullptr;
+    }
+    const uint32_t slot = ctx->rope_tables++;
+    ctx->d_rope_inv_freq[slot] = d;
+    ctx->rope_table_base[slot] = freq_base;
+    ctx->rope_table_hd[slot] = head_dim;
+    return d;
 }
 
 extern "C" {
@@ -109,6 +141,7 @@ void m40llm_destroy_context(M40llmCudaContext* ctx) {
     for (int k = 0; k < 2; ++k)
         for (int l = 0; l < 2; ++l)
             if (ctx->scratch[k][l]) cudaFree(ctx->scratch[k][l]);
+    for (uint32_t i = 0; i < ctx->rope_tables; ++i) cudaFree(ctx->d_rope_inv_freq[i]);
     while (ctx->retired) {
         M40RetiredArena* r = ctx->retired;
         ctx->retired = r->next;
