@@ -191,9 +191,10 @@ struct RankArgs {
 };
 
 __global__ void __launch_bounds__(256) rank_topk_kernel(RankArgs a) {
-    extern __shared__ float rk_smem[];
-    float* sc = rk_smem;                                    // n scores, unselectable ones replaced by -inf
-    uint32_t* id = reinterpret_cast<uint32_t*>(sc + a.n);   // n block indices
+    extern __shared__ __align__(16) float rk_smem[];
+    const uint32_t n4 = (a.n + 3u) / 4u;                      // candidates padded to whole groups of four
+    float* sc = rk_smem;                                      // 4 n4 scores, unselectable ones replaced by -inf
+    uint32_t* id = reinterpret_cast<uint32_t*>(sc + 4u * n4); // 4 n4 block indices
     __shared__ uint32_t s_selectable;
     pdl_wait();
     pdl_trigger();
@@ -201,11 +202,15 @@ __global__ void __launch_bounds__(256) rank_topk_kernel(RankArgs a) {
     if (tid == 0) s_selectable = 0;
     __syncthreads();
     uint32_t mine = 0;
-    for (uint32_t c = tid; c < a.n; c += blockDim.x) {
-        const size_t off = (size_t)h * a.head_stride + (size_t)(c / a.per_part) * a.part_stride +
-                           (size_t)(c % a.per_part) * a.elem_stride;
-        const float s = a.scores[off];
-        const uint32_t b = a.ids ? a.ids[off] : a.index_base + c;
+    for (uint32_t c = tid; c < 4u * n4; c += blockDim.x) {
+        float s = -INFINITY;
+        uint32_t b = 0xffffffffu;
+        if (c < a.n) {
+            const size_t off = (size_t)h * a.head_stride + (size_t)(c / a.per_part) * a.part_stride +
+                               (size_t)(c % a.per_part) * a.elem_stride;
+            s = a.scores[off];
+            b = a.ids ? a.ids[off] : a.index_base + c;
+        }
         const bool ok = s > -1e30f && b != 0xffffffffu;  // false for NaN too
         sc[c] = ok ? s : -INFINITY;
         id[c] = b;
@@ -220,22 +225,31 @@ __global__ void __launch_bounds__(256) rank_topk_kernel(RankArgs a) {
         a.out_ids[((size_t)h * 64u + r) * a.out_stride] = 0xffffffffu;
         a.out_scores[((size_t)h * 64u + r) * a.out_stride] = -1e30f;
     }
-    // four adjacent lanes share one candidate of this slice and scan a quarter of all candidates each
+    // four adjacent lanes share one candidate of this slice; lane `part` scans the groups of four part, part + 4, ...
+    // (16-byte shared-memory reads, four independent counters)
     const uint32_t per_slice = (a.n + slices - 1u) / slices;
     const uint32_t c0 = slice * per_slice, c1 = min(c0 + per_slice, a.n);
-    const uint32_t part = tid & 3u, q0 = (a.n * part) / 4u, q1 = (a.n * (part + 1u)) / 4u;
+    const uint32_t part = tid & 3u;
+    const float4* sc4 = reinterpret_cast<const float4*>(sc);
+    const uint4* id4 = reinterpret_cast<const uint4*>(id);
     for (uint32_t i0 = c0; i0 < c1; i0 += blockDim.x / 4u) {
         const uint32_t i = i0 + tid / 4u;
         const float s = i < c1 ? sc[i] : -INFINITY;
         const uint32_t bi = i < c1 ? id[i] : 0u;
-        uint32_t rank = 0;
+        uint32_t r0 = 0, r1 = 0, r2 = 0, r3 = 0;
         if (s != -INFINITY) {
 #pragma unroll 4
-            for (uint32_t j = q0; j < q1; ++j) {
-                const float o = sc[j];
-                rank += (o > s || (o == s && id[j] < bi)) ? 1u : 0u;  // equal score, lower block index: ahead
+            for (uint32_t j = part; j < n4; j += 4u) {
+                const float4 o = sc4[j];
+                const uint4 b = id4[j];
+                // equal score, lower block index: ahead
+                r0 += (o.x > s || (o.x == s && b.x < bi)) ? 1u : 0u;
+                r1 += (o.y > s || (o.y == s && b.y < bi)) ? 1u : 0u;
+                r2 += (o.z > s || (o.z == s && b.z < bi)) ? 1u : 0u;
+                r3 += (o.w > s || (o.w == s && b.w < bi)) ? 1u : 0u;
             }
         }
+        uint32_t rank = (r0 + r1) + (r2 + r3);
         rank += __shfl_xor_sync(0xffffffffu, rank, 1);
         rank += __shfl_xor_sync(0xffffffffu, rank, 2);
         if (part == 0 && s != -INFINITY && rank < a.top_n && rank < 64u) {
@@ -478,20 +492,41 @@ __global__ void __launch_bounds__(128) selected_attend_kernel(SelArgs a) {
 // ---- 3b. attention over the selected tokens with K and V staged by bulk copies (compressed cache only).
 // Work items per q head: the 64 list entries (one selected block each: K f16 rows and q4 V rows are contiguous in the
 // head-major cache) followed by pieces of the recent ring (`ring_piece` slots each: K and V f16). A warp takes one
-// item: two bulk async copies into its own slice of shared memory on its own mbarrier, then the dot products, the
-// online softmax and the V accumulation run from shared memory. All of a launch's bytes are in flight at once, where
-// the gather form issues them as dependent rounds of loads. grid (ceil(items / 4), q_heads), 128 threads; one
-// (m, l, o) partial per CTA, merged by the same kernel as before.
+// item: two bulk async copies into its own slice of shared memory on its own mbarrier, so all of a launch's bytes are
+// in flight at once, where the gather form issues them as dependent rounds of loads. The item is then consumed 32
+// tokens at a time: the 32 dot products are reduced across the warp by a halving exchange (31 shuffles for 32 sums,
+// lane t ends up with token t's score), the softmax runs one token per lane, and only the V accumulation walks the
+// tokens one by one. grid (ceil(items / warps), q_heads), `warps` x 32 threads; one (m, l, o) partial per CTA, merged
+// by the same kernel as before.
+constexpr uint32_t STAGED_MAX_WARPS = 8;
+
+// v[i] (i < 32) is this lane's partial sum for token i. Returns the complete sum of token `lane`.
+__device__ __forceinline__ float transpose_reduce32(float (&v)[32], uint32_t lane) {
+#pragma unroll
+    for (int o = 16; o >= 1; o >>= 1) {
+        const bool upper = (lane & o) != 0u;
+#pragma unroll
+        for (int i = 0; i < o; ++i) {
+            // keep the half of the values that matches this lane's bit, hand the other half to the partner
+            const float keep = upper ? v[i + o] : v[i];
+            const float give = upper ? v[i] : v[i + o];
+            v[i] = keep + __shfl_xor_sync(0xffffffffu, give, o);
+        }
+    }
+    return v[0];
+}
+
 template <int HD>
-__global__ void __launch_bounds__(128) selected_attend_staged_kernel(SelArgs a, uint32_t slice_bytes, uint32_t ring_piece,
-                                                                     uint32_t ring_items) {
+__global__ void __launch_bounds__(32 * STAGED_MAX_WARPS) selected_attend_staged_kernel(SelArgs a, uint32_t slice_bytes,
+                                                                                       uint32_t ring_piece,
+                                                                                       uint32_t ring_items) {
     constexpr int DPL = HD / 32;  // dims per lane, contiguous
     extern __shared__ __align__(128) unsigned char st_smem[];
-    __shared__ uint64_t bars[4];
-    __shared__ float sm_m[4], sm_l[4], sm_o[4][HD];
-    const uint32_t h = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+    __shared__ uint64_t bars[STAGED_MAX_WARPS];
+    __shared__ float sm_m[STAGED_MAX_WARPS], sm_l[STAGED_MAX_WARPS], sm_o[STAGED_MAX_WARPS][HD];
+    const uint32_t h = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31u, warps = blockDim.x >> 5;
     const uint32_t G = a.q_heads / a.kv_heads, kvh = h / G;
-    const uint32_t item = blockIdx.x * 4u + warp;
+    const uint32_t item = blockIdx.x * warps + warp;
     unsigned char* slice = st_smem + (size_t)warp * slice_bytes;
     pdl_wait();
     pdl_trigger();
@@ -533,14 +568,14 @@ __global__ void __launch_bounds__(128) selected_attend_staged_kernel(SelArgs a, 
     float qr[DPL], acc[DPL];
 #pragma unroll
     for (int j = 0; j < DPL; ++j) {
-        qr[j] = a.q[(size_t)h * HD + lane * DPL + j];
+        qr[j] = a.q[(size_t)h * HD + lane * DPL + j] * a.inv_sqrt;
         acc[j] = 0.0f;
     }
-    // q4 scales of this item's tokens: lane l holds tokens l and l + 32 (blocks of at most 64 tokens)
-    float sc_lo = 0.0f, sc_hi = 0.0f;
+    // q4 scales of this item's tokens (old blocks only): lane l holds tokens l and l + 32; requested before the wait
+    float scale_lo = 0.0f, scale_hi = 0.0f;
     if (!ring && n) {
-        if (lane < n) sc_lo = a.q4_scale[vec_base + tok0 + lane];
-        if (lane + 32u < n) sc_hi = a.q4_scale[vec_base + tok0 + lane + 32u];
+        if (lane < n) scale_lo = a.q4_scale[vec_base + tok0 + lane];
+        if (lane + 32u < n) scale_hi = a.q4_scale[vec_base + tok0 + lane + 32u];
     }
     float m = -INFINITY, l = 0.0f;
     __syncwarp();
@@ -553,40 +588,41 @@ __global__ void __launch_bounds__(128) selected_attend_staged_kernel(SelArgs a, 
     }
     const __half* sK = reinterpret_cast<const __half*>(slice) + lane * DPL;
     const unsigned char* sV = slice + k_bytes;
-    constexpr int U = 8;
-    for (uint32_t t0 = 0; t0 < n; t0 += U) {
-        float sc[U];
+    for (uint32_t g0 = 0; g0 < n; g0 += 32u) {
+        const uint32_t cnt = min(32u, n - g0);  // warp-uniform
+        const float scale = g0 == 0u ? scale_lo : scale_hi;
+        // ---- 32 dot products, dims split over the lanes, then the halving exchange
+        float part[32];
 #pragma unroll
-        for (int i = 0; i < U; ++i) {
-            const uint32_t t = min(t0 + i, n - 1u);
-            float dot;
+        for (int i = 0; i < 32; ++i) {
+            const uint32_t t = g0 + min((uint32_t)i, cnt - 1u);
             if (DPL == 4) {
                 const uint2 w = *reinterpret_cast<const uint2*>(sK + (size_t)t * HD);
                 const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&w.x));
                 const float2 f1 = __half22float2(*reinterpret_cast<const __half2*>(&w.y));
-                dot = fmaf(qr[0], f0.x, 0.0f);
-                dot = fmaf(qr[1], f0.y, dot);
-                dot = fmaf(qr[DPL - 2], f1.x, dot);
-                dot = fmaf(qr[DPL - 1], f1.y, dot);
+                part[i] = fmaf(qr[DPL - 1], f1.y, fmaf(qr[DPL - 2], f1.x, fmaf(qr[1], f0.y, qr[0] * f0.x)));
             } else {
                 const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(sK + (size_t)t * HD));
-                dot = fmaf(qr[0], f0.x, 0.0f);
-                dot = fmaf(qr[1], f0.y, dot);
+                part[i] = fmaf(qr[1], f0.y, qr[0] * f0.x);
             }
-            sc[i] = dot;
         }
+        float s = transpose_reduce32(part, lane);  // token g0 + lane (already scaled by 1/sqrt(hd) through q)
+        if (lane >= cnt) s = -INFINITY;
+        // ---- softmax, one token per lane
+        const float mn = fmaxf(m, warp_max(s));
+        const float corr = expf(m - mn);            // 0 on the first group (m = -inf, mn finite)
+        const float p = lane < cnt ? expf(s - mn) : 0.0f;
+        l = l * corr + warp_sum(p);
+        m = mn;
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1)
-#pragma unroll
-            for (int i = 0; i < U; ++i) sc[i] += __shfl_xor_sync(0xffffffffu, sc[i], o);
-#pragma unroll
-        for (int i = 0; i < U; ++i) {
-            const uint32_t t = t0 + i;
-            if (t >= n) break;  // warp-uniform
-            const float s = sc[i] * a.inv_sqrt;
+        for (int j = 0; j < DPL; ++j) acc[j] *= corr;
+        // ---- O += P V, token by token
+        for (uint32_t i = 0; i < cnt; ++i) {
+            const float pw = __shfl_sync(0xffffffffu, p, i);
+            const uint32_t t = g0 + i;
             float vx[DPL];
             if (!ring) {
-                const float scale = __shfl_sync(0xffffffffu, t < 32u ? sc_lo : sc_hi, t & 31u);
+                const float sc = __shfl_sync(0xffffffffu, scale, i);
                 uint32_t bits;
                 if (DPL == 4) bits = *reinterpret_cast<const uint16_t*>(sV + (size_t)t * (HD / 2) + lane * 2);
                 else bits = sV[(size_t)t * (HD / 2) + lane];
@@ -595,7 +631,7 @@ __global__ void __launch_bounds__(128) selected_attend_staged_kernel(SelArgs a, 
                     // signed nibble as an exact float without a conversion instruction: 2^23 + (nib ^ 8) - (2^23 + 8)
                     const uint32_t nib = (bits >> (4 * j)) & 0xfu;
                     const float sv = __uint_as_float(0x4B000000u | (nib ^ 8u)) - 8388616.0f;
-                    vx[j] = __half2float(__float2half_rn(sv * scale));
+                    vx[j] = __half2float(__float2half_rn(sv * sc));
                 }
             } else {
                 const __half* vp = reinterpret_cast<const __half*>(sV) + (size_t)t * HD + lane * DPL;
@@ -606,13 +642,8 @@ __global__ void __launch_bounds__(128) selected_attend_staged_kernel(SelArgs a, 
                     vx[DPL - 2] = f1.x, vx[DPL - 1] = f1.y;
                 }
             }
-            const float mn = fmaxf(m, s);
-            const float corr = expf(m - mn);
-            const float pw = expf(s - mn);
-            l = l * corr + pw;
 #pragma unroll
-            for (int j = 0; j < DPL; ++j) acc[j] = fmaf(pw, vx[j], acc[j] * corr);
-            m = mn;
+            for (int j = 0; j < DPL; ++j) acc[j] = fmaf(pw, vx[j], acc[j]);
         }
     }
     if (lane == 0) {
@@ -624,11 +655,9 @@ __global__ void __launch_bounds__(128) selected_attend_staged_kernel(SelArgs a, 
     __syncthreads();
     for (uint32_t d = threadIdx.x; d < HD; d += blockDim.x) {
         float M = -INFINITY;
-#pragma unroll
-        for (int w = 0; w < 4; ++w) M = fmaxf(M, sm_m[w]);
+        for (uint32_t w = 0; w < warps; ++w) M = fmaxf(M, sm_m[w]);
         float L = 0.0f, O = 0.0f;
-#pragma unroll
-        for (int w = 0; w < 4; ++w) {
+        for (uint32_t w = 0; w < warps; ++w) {
             const float e = sm_m[w] == -INFINITY ? 0.0f : expf(sm_m[w] - M);
             L += sm_l[w] * e;
             O += sm_o[w][d] * e;
@@ -644,10 +673,10 @@ __global__ void __launch_bounds__(128) selected_attend_staged_kernel(SelArgs a, 
 
 // Shape of the staged attend launch for this call, or splits == 0 when the gather form has to be used.
 struct StagedPlan {
-    uint32_t slice_bytes, ring_piece, ring_items, splits;
+    uint32_t slice_bytes, ring_piece, ring_items, warps, splits;
 };
 
-StagedPlan plan_staged(const SelArgs& a, bool dense) {
+StagedPlan plan_staged(const SelArgs& a, bool dense, int sm_count) {
     StagedPlan p = {};
     if (dense || a.block_size > 64u || a.block_size == 0u) return p;
     uint32_t slice = a.block_size * (a.hd * 2u + a.hd / 2u);
@@ -660,7 +689,20 @@ StagedPlan plan_staged(const SelArgs& a, bool dense) {
     p.slice_bytes = slice;
     p.ring_piece = piece;
     p.ring_items = (recent_n + piece - 1u) / piece;
-    p.splits = (64u + p.ring_items + 3u) / 4u;
+    const uint32_t items = 64u + p.ring_items;
+    // warps (= items) per CTA: the fewest for which the whole launch is resident at once; a second wave that holds
+    // a handful of CTAs would double the time of this latency-bound kernel
+    const uint32_t sms = sm_count > 0 ? (uint32_t)sm_count : 1u;
+    p.warps = STAGED_MAX_WARPS;
+    for (uint32_t w = 4u; w <= STAGED_MAX_WARPS; ++w) {
+        const uint32_t per_sm = (220u * 1024u) / (w * slice + 4096u);
+        const uint32_t ctas = a.q_heads * ((items + w - 1u) / w);
+        if (per_sm >= 1u && ctas <= per_sm * sms) {
+            p.warps = w;
+            break;
+        }
+    }
+    p.splits = (items + p.warps - 1u) / p.warps;
     if (p.splits > 256u) p.splits = 0;  // the merge kernel's limit
     return p;
 }
@@ -743,7 +785,7 @@ int launch_rank(M40llmCudaContext* ctx, const RankArgs& r, uint32_t q_heads) {
     const uint32_t max_slices = (r.n + 63u) / 64u;
     if (slices > max_slices) slices = max_slices;
     if (slices < 1u) slices = 1u;
-    const size_t smem = (size_t)(r.n ? r.n : 1u) * 8u;
+    const size_t smem = (size_t)((r.n + 3u) / 4u * 4u + 4u) * 8u;
     const cudaError_t e = m40_launch_dependent(rank_topk_kernel, dim3(q_heads, slices), dim3(256), smem, ctx->decode_stream, r);
     M40_COUNT_LAUNCH(ctx);
     return e == cudaSuccess && cudaGetLastError() == cudaSuccess ? 0 : -8;
@@ -780,18 +822,18 @@ int launch_attend(M40llmCudaContext* ctx, const SelArgs& a0, bool dense) {
     a.status_word = ctx->d_status;
     cudaStream_t s = ctx->decode_stream;
     cudaError_t e;
-    const StagedPlan sp = plan_staged(a, dense);
+    const StagedPlan sp = plan_staged(a, dense, ctx->sm_count);
     if (sp.splits != 0 && sp.splits == a.splits) {  // the caller sized its partials with attend_splits(): same plan
         auto kern = a.hd == 128 ? selected_attend_staged_kernel<128> : selected_attend_staged_kernel<64>;
-        const size_t smem = (size_t)4 * sp.slice_bytes;
+        const size_t smem = (size_t)sp.warps * sp.slice_bytes;
         static std::atomic<unsigned long long> configured[2];
         const unsigned long long bit = 1ull << (ctx->device_id & 63);
         std::atomic<unsigned long long>& cfgd = configured[a.hd == 128 ? 1 : 0];
         if (!(cfgd.load(std::memory_order_acquire) & bit)) {
-            if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024) != cudaSuccess) return -8;
+            if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess) return -8;
             cfgd.fetch_or(bit, std::memory_order_release);
         }
-        e = m40_launch_dependent(kern, dim3(sp.splits, a.q_heads), dim3(128), smem, s, a, sp.slice_bytes, sp.ring_piece,
+        e = m40_launch_dependent(kern, dim3(sp.splits, a.q_heads), dim3(32u * sp.warps), smem, s, a, sp.slice_bytes, sp.ring_piece,
                                  sp.ring_items);
         M40_COUNT_LAUNCH(ctx);
         return e == cudaSuccess && cudaGetLastError() == cudaSuccess ? 0 : -8;
@@ -809,7 +851,7 @@ int launch_attend(M40llmCudaContext* ctx, const SelArgs& a0, bool dense) {
 }
 
 uint32_t attend_splits(const M40llmCudaContext* ctx, const SelArgs& a, bool dense = false) {
-    const StagedPlan sp = plan_staged(a, dense);
+    const StagedPlan sp = plan_staged(a, dense, ctx->sm_count);
     if (sp.splits != 0 && getenv("M40LLM_ATTEND_GATHER") == nullptr) return sp.splits;  // one partial per staged CTA
     const uint32_t total = 64u * a.block_size + (a.seq_len - a.old_len);
     // ~8 CTAs per SM, never fewer than 64 slots per CTA: the kernel is latency-bound, so parallelism is what counts
