@@ -151,11 +151,14 @@ __global__ void __launch_bounds__(128) attn_merge_kernel(const float* __restrict
 // The same merge with the work spread over the CTA: split s's weight exp(m_s - M) is computed once by thread s,
 // the output accumulation runs as 8 split groups x (hd/4) float4 lanes with independent loads, and the groups
 // meet in shared memory in a fixed order. Takes hd % 4 == 0, hd <= 128, splits <= 256 and 16-byte aligned partials.
+// With fold_m / fold_l given the result is left unnormalised and its (max, sum) are written too: the fold of one
+// rank's splits into ONE triple per head for the split-K exchange.
 __global__ void __launch_bounds__(256) attn_merge_wide_kernel(const float* __restrict__ pm, const float* __restrict__ pl,
                                                               const float* __restrict__ po, float* __restrict__ out,
                                                               uint32_t q_heads, uint32_t hd, uint32_t splits,
                                                               size_t part_stride_m, size_t part_stride_o,
-                                                              uint32_t strided) {
+                                                              uint32_t strided, float* __restrict__ fold_m = nullptr,
+                                                              float* __restrict__ fold_l = nullptr) {
     __shared__ float sw[256];
     __shared__ float sred[8];
     __shared__ float4 sacc[8][32];
@@ -187,7 +190,11 @@ __global__ void __launch_bounds__(256) attn_merge_wide_kernel(const float* __res
     L = 0.0f;
 #pragma unroll
     for (int i = 0; i < 8; ++i) L += sred[i];
-    const float inv = 1.0f / (L > 0.0f ? L : 1.0f);
+    const float inv = fold_m ? 1.0f : 1.0f / (L > 0.0f ? L : 1.0f);
+    if (fold_m && tid == 0) {
+        fold_m[(size_t)row * q_heads + h] = M;
+        fold_l[(size_t)row * q_heads + h] = L;
+    }
     const uint32_t vl = hd / 4u;            // float4 lanes per split (<= 32)
     const uint32_t g = tid / 32u, v = lane;  // split group, float4 lane
     float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
@@ -350,7 +357,7 @@ int m40_attention_merge_rows(M40llmCudaContext* ctx, const float* m, const float
     dim3 grid(q_heads, rows);
     if (merge_wide_ok(o, out, hd, splits, 0))
         m40_launch_dependent(attn_merge_wide_kernel, grid, dim3(256), 0, ctx->decode_stream, m, l, o, out, q_heads, hd,
-                             splits, (size_t)0, (size_t)0, 0u);
+                             splits, (size_t)0, (size_t)0, 0u, (float*)nullptr, (float*)nullptr);
     else
         attn_merge_kernel<<<grid, 128, 0, ctx->decode_stream>>>(m, l, o, out, q_heads, hd, splits, 0, 0, 0u);
     M40_COUNT_LAUNCH(ctx);
@@ -360,7 +367,11 @@ int m40_attention_merge_rows(M40llmCudaContext* ctx, const float* m, const float
 int m40_attention_fold_partials(M40llmCudaContext* ctx, const float* m, const float* l, const float* o,
                                 uint32_t splits, uint32_t q_heads, uint32_t hd, float* out_m, float* out_l,
                                 float* out_o) {
-    attn_fold_kernel<<<q_heads, 128, 0, ctx->decode_stream>>>(m, l, o, hd, splits, out_m, out_l, out_o);
+    if (merge_wide_ok(o, out_o, hd, splits, 0))
+        m40_launch_dependent(attn_merge_wide_kernel, dim3(q_heads, 1), dim3(256), 0, ctx->decode_stream, m, l, o, out_o, q_heads,
+                             hd, splits, (size_t)0, (size_t)0, 0u, out_m, out_l);
+    else
+        attn_fold_kernel<<<q_heads, 128, 0, ctx->decode_stream>>>(m, l, o, hd, splits, out_m, out_l, out_o);
     M40_COUNT_LAUNCH(ctx);
     return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }

@@ -490,15 +490,15 @@ __global__ void __launch_bounds__(128) selected_attend_kernel(SelArgs a) {
 }
 
 // ---- 3b. attention over the selected tokens with K and V staged by bulk copies (compressed cache only).
-// Work items per q head: the 64 list entries (one selected block each: K f16 rows and q4 V rows are contiguous in the
-// head-major cache) followed by pieces of the recent ring (`ring_piece` slots each: K and V f16). A warp takes one
-// item: two bulk async copies into its own slice of shared memory on its own mbarrier, so all of a launch's bytes are
-// in flight at once, where the gather form issues them as dependent rounds of loads. The item is then consumed 32
-// tokens at a time: the 32 dot products are reduced across the warp by a halving exchange (31 shuffles for 32 sums,
-// lane t ends up with token t's score), the softmax runs one token per lane, and only the V accumulation walks the
-// tokens one by one. grid (ceil(items / warps), q_heads), `warps` x 32 threads; one (m, l, o) partial per CTA, merged
+// Work items per q head: runs of up to 32 tokens of the 64 selected blocks (K f16 rows and q4 V rows of a block are
+// contiguous in the head-major cache) followed by pieces of the recent ring (`ring_piece` slots each: K and V f16).
+// A warp takes one item: two bulk async copies into its own slice of shared memory on its own mbarrier, so all of a
+// launch's bytes are in flight at once, where the gather form issues them as dependent rounds of loads. The item's
+// dot products are reduced across the warp by a halving exchange (31 shuffles for 32 sums, lane t ends up with token
+// t's score), the softmax runs one token per lane, and only the V accumulation walks the tokens one by one. grid (ceil(items / warps), q_heads), `warps` x 32 threads; one (m, l, o) partial per CTA, merged
 // by the same kernel as before.
-constexpr uint32_t STAGED_MAX_WARPS = 8;
+constexpr uint32_t STAGED_MAX_WARPS = 16;
+constexpr uint32_t STAGED_ITEM_TOKENS = 32;  // tokens per work item (one per lane in the softmax)
 
 // v[i] (i < 32) is this lane's partial sum for token i. Returns the complete sum of token `lane`.
 __device__ __forceinline__ float transpose_reduce32(float (&v)[32], uint32_t lane) {
@@ -533,16 +533,17 @@ __global__ void __launch_bounds__(32 * STAGED_MAX_WARPS) selected_attend_staged_
     // ---- what this warp's item is
     uint32_t n = 0, tok0 = 0;
     bool ring = false;
-    if (item < 64u) {
-        const uint32_t b = a.sel_blocks[h * 64u + item];
+    const uint32_t subs = (a.block_size + STAGED_ITEM_TOKENS - 1u) / STAGED_ITEM_TOKENS;  // items per selected block
+    if (item < 64u * subs) {
+        const uint32_t b = a.sel_blocks[h * 64u + item / subs], off = (item % subs) * STAGED_ITEM_TOKENS;
         if (b != 0xffffffffu && b >= a.block_begin && b < a.block_end) {
-            tok0 = b * a.block_size;
-            if (tok0 < a.old_len) n = min(a.block_size, a.old_len - tok0);
+            tok0 = b * a.block_size + off;
+            if (tok0 < a.old_len) n = min(min(STAGED_ITEM_TOKENS, a.block_size - off), a.old_len - tok0);
         }
-    } else if (a.include_recent && item - 64u < ring_items) {
+    } else if (a.include_recent && item - 64u * subs < ring_items) {
         ring = true;
         const uint32_t recent_n = a.seq_len - a.old_len;  // the ring's live slots are [0, recent_n)
-        tok0 = (item - 64u) * ring_piece;
+        tok0 = (item - 64u * subs) * ring_piece;
         if (tok0 < recent_n) n = min(ring_piece, recent_n - tok0);
     }
     const size_t vec_base = ((size_t)a.seq_id * a.kv_heads + kvh) * (size_t)a.max_seq_len;
@@ -571,12 +572,9 @@ __global__ void __launch_bounds__(32 * STAGED_MAX_WARPS) selected_attend_staged_
         qr[j] = a.q[(size_t)h * HD + lane * DPL + j] * a.inv_sqrt;
         acc[j] = 0.0f;
     }
-    // q4 scales of this item's tokens (old blocks only): lane l holds tokens l and l + 32; requested before the wait
-    float scale_lo = 0.0f, scale_hi = 0.0f;
-    if (!ring && n) {
-        if (lane < n) scale_lo = a.q4_scale[vec_base + tok0 + lane];
-        if (lane + 32u < n) scale_hi = a.q4_scale[vec_base + tok0 + lane + 32u];
-    }
+    // the q4 scale of this lane's token (old blocks only), requested before the wait
+    float scale = 0.0f;
+    if (!ring && lane < n) scale = a.q4_scale[vec_base + tok0 + lane];
     float m = -INFINITY, l = 0.0f;
     __syncwarp();
     if (n) {
@@ -588,9 +586,8 @@ __global__ void __launch_bounds__(32 * STAGED_MAX_WARPS) selected_attend_staged_
     }
     const __half* sK = reinterpret_cast<const __half*>(slice) + lane * DPL;
     const unsigned char* sV = slice + k_bytes;
-    for (uint32_t g0 = 0; g0 < n; g0 += 32u) {
-        const uint32_t cnt = min(32u, n - g0);  // warp-uniform
-        const float scale = g0 == 0u ? scale_lo : scale_hi;
+    if (n) {
+        const uint32_t g0 = 0, cnt = n;  // warp-uniform, at most 32
         // ---- 32 dot products, dims split over the lanes, then the halving exchange
         float part[32];
 #pragma unroll
@@ -617,6 +614,7 @@ __global__ void __launch_bounds__(32 * STAGED_MAX_WARPS) selected_attend_staged_
 #pragma unroll
         for (int j = 0; j < DPL; ++j) acc[j] *= corr;
         // ---- O += P V, token by token
+#pragma unroll 4
         for (uint32_t i = 0; i < cnt; ++i) {
             const float pw = __shfl_sync(0xffffffffu, p, i);
             const uint32_t t = g0 + i;
@@ -678,24 +676,27 @@ struct StagedPlan {
 
 StagedPlan plan_staged(const SelArgs& a, bool dense, int sm_count) {
     StagedPlan p = {};
-    if (dense || a.block_size > 64u || a.block_size == 0u) return p;
-    uint32_t slice = a.block_size * (a.hd * 2u + a.hd / 2u);
+    if (dense || a.block_size == 0u) return p;
+    const uint32_t item_tokens = a.block_size < STAGED_ITEM_TOKENS ? a.block_size : STAGED_ITEM_TOKENS;
+    uint32_t slice = item_tokens * (a.hd * 2u + a.hd / 2u);
     slice = (slice + 127u) & ~127u;
-    if (slice > 24u * 1024u) return p;
     uint32_t piece = slice / (a.hd * 4u);  // ring slots whose K and V rows (f16) fit one slice
-    piece &= ~7u;
+    if (piece > 8u) piece &= ~7u;
     if (piece == 0u) return p;
     const uint32_t recent_n = a.seq_len - a.old_len;
     p.slice_bytes = slice;
     p.ring_piece = piece;
     p.ring_items = (recent_n + piece - 1u) / piece;
-    const uint32_t items = 64u + p.ring_items;
+    const uint32_t subs = (a.block_size + STAGED_ITEM_TOKENS - 1u) / STAGED_ITEM_TOKENS;
+    if (subs > 64u) return p;
+    const uint32_t items = 64u * subs + p.ring_items;
     // warps (= items) per CTA: the fewest for which the whole launch is resident at once; a second wave that holds
     // a handful of CTAs would double the time of this latency-bound kernel
     const uint32_t sms = sm_count > 0 ? (uint32_t)sm_count : 1u;
     p.warps = STAGED_MAX_WARPS;
     for (uint32_t w = 4u; w <= STAGED_MAX_WARPS; ++w) {
-        const uint32_t per_sm = (220u * 1024u) / (w * slice + 4096u);
+        uint32_t per_sm = (220u * 1024u) / (w * slice + 10u * 1024u);  // dynamic slices + the static merge arrays
+        if (per_sm > 2048u / (32u * w)) per_sm = 2048u / (32u * w);
         const uint32_t ctas = a.q_heads * ((items + w - 1u) / w);
         if (per_sm >= 1u && ctas <= per_sm * sms) {
             p.warps = w;
