@@ -244,7 +244,11 @@ int m40llm_kvcache_debug_attention_telemetry(M40llmCudaContext* ctx, const M40ll
                                              uint32_t seq_id, const void* d_q_f32, uint32_t q_heads, uint32_t seq_len,
                                              uint32_t recent_window, uint32_t block_size, uint32_t top_blocks,
                                              uint32_t needle_block, M40llmAttentionTelemetry* out);
-/* cuda/kernels.cu:7173-7231 — prefill-side helper: M40LLM_ERR_UNSUPPORTED */
+/* cuda/kernels.cu:7173-7231 (src/cuda.rs:462-471) — builds the compressed state of every sequence slot from a dense
+ * cache that holds seq_len tokens per slot: the last min(seq_len, recent_window) tokens in the ring (slot t % R), the
+ * older ones in the FP16-K / q4-V old region (the state token-by-token appends would have left), every sequence length
+ * = seq_len. Return codes as the reference: -2 wrong cache kinds, -3 shapes differ, -4 seq_len beyond a cache;
+ * M40LLM_ERR_UNSUPPORTED for a compressed cache without the FP16-K / q4-V backing. Synchronous, decode stream. */
 int m40llm_kvcache_build_compressed_from_dense(M40llmCudaContext* ctx, M40llmKVCache* compressed,
                                                const M40llmKVCache* dense, uint32_t seq_len);
 /* cuda/kernels.cu:4089-4122 — q8 KV backing: M40LLM_ERR_UNSUPPORTED */
@@ -320,7 +324,11 @@ int m40llm_attention_last_token_f32_gqa_compressed_recent_only_async(M40llmCudaC
                                                                      uint32_t seq_id, const void* d_q_f32,
                                                                      uint32_t q_heads, uint32_t seq_len,
                                                                      void* d_out_f32);
-/* cuda/kernels.cu:4834-4977 — packed prefill attention: M40LLM_ERR_UNSUPPORTED */
+/* cuda/kernels.cu:3749-3835, 4834-4977 (src/cuda.rs:619-668) — packed variable-length causal prefill attention over f32
+ * Q [total_q][q_heads][hd], K / V [total_kv][kv_heads][hd]: sequence b owns q rows [q_offsets[b], +q_lens[b]) and kv rows
+ * [kv_offsets[b], +kv_lens[b]); q row i attends kv rows 0 .. kv_len - q_len + i. head_dim 64 or 128 (-9 otherwise, and
+ * for pointers that are not 16-byte aligned); the lengths are validated on the host as in the reference (-8 for a zero
+ * length, q_len > kv_len or kv_len > 8192). Prefill stream; the plain form synchronises it. */
 int m40llm_attention_prefill_f32_gqa_varlen(M40llmCudaContext* ctx, const void* d_q_f32, const void* d_k_f32,
                                             const void* d_v_f32, const uint32_t* d_q_offsets,
                                             const uint32_t* d_kv_offsets, const uint32_t* d_q_lens,

@@ -556,28 +556,4 @@ int m40llm_attention_last_token_f32_gqa_dense_recent_async(M40llmCudaContext* ct
     return M40LLM_ERR_UNSUPPORTED;
 }
 
-int m40llm_attention_prefill_f32_gqa_varlen_async(M40llmCudaContext* ctx, const void* d_q_f32, const void* d_k_f32,
-                                                  const void* d_v_f32, const uint32_t* d_q_offsets,
-                                                  const uint32_t* d_kv_offsets, const uint32_t* d_q_lens,
-                                                  const uint32_t* d_kv_lens, uint32_t batch_size, uint32_t q_heads,
-                                                  uint32_t kv_heads, uint32_t head_dim, void* d_out_f32) {
-    (void)head_dim;
-    if (!ctx || !d_q_f32 || !d_k_f32 || !d_v_f32 || !d_q_offsets || !d_kv_offsets || !d_q_lens || !d_kv_lens ||
-        !d_out_f32)
-        return -1;
-    if (batch_size == 0) return -2;
-    if (q_heads == 0 || kv_heads == 0 || q_heads % kv_heads != 0) return -3;
-    return M40LLM_ERR_UNSUPPORTED;
-}
-
-int m40llm_attention_prefill_f32_gqa_varlen(M40llmCudaContext* ctx, const void* d_q_f32, const void* d_k_f32,
-                                            const void* d_v_f32, const uint32_t* d_q_offsets,
-                                            const uint32_t* d_kv_offsets, const uint32_t* d_q_lens,
-                                            const uint32_t* d_kv_lens, uint32_t batch_size, uint32_t q_heads,
-                                            uint32_t kv_heads, uint32_t head_dim, void* d_out_f32) {
-    return m40llm_attention_prefill_f32_gqa_varlen_async(ctx, d_q_f32, d_k_f32, d_v_f32, d_q_offsets, d_kv_offsets,
-                                                         d_q_lens, d_kv_lens, batch_size, q_heads, kv_heads, head_dim,
-                                                         d_out_f32);
-}
-
 }  // extern "C"

@@ -101,6 +101,31 @@ __global__ void __launch_bounds__(64) place_tokens_kernel(const __half* __restri
     }
 }
 
+// One (token, kv head, slot) of a dense cache into the compressed cache. grid (seq_len, heads, slots), block 64.
+__global__ void __launch_bounds__(64) compress_from_dense_kernel(M40llmKVCache dense, M40llmKVCache kv, uint32_t seq_len) {
+    __shared__ float red[32];
+    const uint32_t t = blockIdx.x, head = blockIdx.y, slot = blockIdx.z, hd = kv.head_dim;
+    const size_t src = kv_row_offset(slot, head, t, dense.num_heads, dense.max_seq_len, hd);
+    const uint32_t old_len = seq_len > kv.recent_window ? seq_len - kv.recent_window : 0u;
+    if (t < old_len) {
+        const size_t row = kv_row_offset(slot, head, t, kv.num_heads, kv.max_seq_len, hd);
+        for (uint32_t i = threadIdx.x; i < hd; i += blockDim.x) kv.d_old_k[row + i] = dense.d_k[src + i];
+        const size_t vec = ((size_t)slot * kv.num_heads + head) * (size_t)kv.max_seq_len + t;
+        quantize_v_row_q4(dense.d_v + src, kv.d_q4_v + vec * (hd / 2u), kv.d_q4_scale + vec, hd, red);
+    } else {
+        const size_t row = kv_row_offset(slot, head, t % kv.recent_window, kv.num_heads, kv.recent_window, hd);
+        for (uint32_t i = threadIdx.x; i < hd; i += blockDim.x) {
+            kv.d_recent_k[row + i] = dense.d_k[src + i];
+            kv.d_recent_v[row + i] = dense.d_v[src + i];
+        }
+    }
+}
+
+__global__ void fill_u32_kernel(uint32_t* p, uint32_t v, uint32_t n) {
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) p[i] = v;
+}
+
 template <typename T>
 bool dev_alloc_zero(T** p, size_t count) {
     if (cudaMalloc((void**)p, count * sizeof(T)) != cudaSuccess) {
@@ -514,12 +539,36 @@ int m40llm_kvcache_debug_write_range(M40llmCudaContext* ctx, M40llmKVCache* kv, 
     return rc;
 }
 
-// ---- modes outside the decode hot path ----
+// Builds the compressed state of EVERY sequence slot from a dense cache holding `seq_len` tokens per slot
+// (cuda/kernels.cu:7173-7231; the reference fills its recent ring and lossy summaries there). Here the state is what
+// token-by-token appends would have left in the FP16-K / q4-V cache: tokens [0, seq_len - R) in the old region (K
+// copied, V quantised to q4), the last min(seq_len, R) tokens in ring slot t % R, every sequence length = seq_len.
+// Decode stream, synchronous like the reference.
 int m40llm_kvcache_build_compressed_from_dense(M40llmCudaContext* ctx, M40llmKVCache* compressed,
                                                const M40llmKVCache* dense, uint32_t seq_len) {
-    (void)seq_len;
     if (!ctx || !compressed || !dense) return -1;
-    return M40LLM_ERR_UNSUPPORTED;
+    if (!compressed->compressed || dense->compressed) return -2;
+    if (compressed->max_batch_size != dense->max_batch_size || compressed->num_heads != dense->num_heads ||
+        compressed->head_dim != dense->head_dim)
+        return -3;
+    if (seq_len > compressed->max_seq_len || seq_len > dense->max_seq_len) return -4;
+    if (!compressed->d_old_k || !compressed->d_q4_v || !compressed->d_q4_scale || !dense->d_k || !dense->d_v)
+        return M40LLM_ERR_UNSUPPORTED;  // only the FP16-K / q4-V backing is built
+    if (m40_ensure_device(ctx) != 0) return -1;
+    cudaStream_t s = ctx->decode_stream;
+    const size_t ring_elems = (size_t)compressed->max_batch_size * compressed->num_heads * compressed->recent_window * compressed->head_dim;
+    if (cudaMemsetAsync(compressed->d_recent_k, 0, ring_elems * sizeof(__half), s) != cudaSuccess ||
+        cudaMemsetAsync(compressed->d_recent_v, 0, ring_elems * sizeof(__half), s) != cudaSuccess)
+        return -5;
+    if (seq_len > 0) {
+        dim3 grid(seq_len, compressed->num_heads, compressed->max_batch_size);
+        compress_from_dense_kernel<<<grid, 64, 0, s>>>(*dense, *compressed, seq_len);
+        M40_COUNT_LAUNCH(ctx);
+    }
+    fill_u32_kernel<<<(compressed->max_batch_size + 127) / 128, 128, 0, s>>>(compressed->d_seq_map, seq_len, compressed->max_batch_size);
+    M40_COUNT_LAUNCH(ctx);
+    if (cudaGetLastError() != cudaSuccess) return -5;
+    return cudaStreamSynchronize(s) == cudaSuccess ? 0 : -6;
 }
 
 int m40llm_kvcache_build_q8_old_from_dense(M40llmCudaContext* ctx, M40llmKVCache* kv, uint32_t seq_id,

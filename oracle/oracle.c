@@ -8,7 +8,7 @@
  *
  * Pinning: every function below is checked (tests/test_oracle_*.py) against
  * golden outputs produced by the reference project's own CUDA translation unit
- * (cuda/kernels.cu compiled unmodified, see oracle/build_ref.sh) on a B200,
+ * (cuda/kernels.cu compiled unmodified by `make -C oracle ref`) on a B200,
  * committed under tests/golden/, and against an independent numpy restatement
  * of the reference tests' closed-form cases.
  *
@@ -695,3 +695,48 @@ ORC_API void orc_set_num_threads(int n) {
     (void)n;
 #endif
 }
+
+/* Packed variable-length causal prefill attention, f32 throughout: cuda/kernels.cu:3749-3835 (three passes: scores of
+ * kv rows 0 .. kv_len - q_len + i, their maximum, exp / sum, then the weighted V sum with p = exp(s - max) / denom). */
+ORC_API int orc_attention_prefill_varlen(const float* q, const float* k, const float* v, const uint32_t* q_off,
+                                 const uint32_t* kv_off, const uint32_t* q_lens, const uint32_t* kv_lens, uint32_t batch,
+                                 uint32_t q_heads, uint32_t kv_heads, uint32_t hd, float* out) {
+    if (!q || !k || !v || !out || kv_heads == 0 || q_heads % kv_heads != 0) return -1;
+    const uint32_t group = q_heads / kv_heads;
+    const float inv_sqrt = hd == 64u ? 0.125f : (hd == 128u ? 0.08838834764831845f : 1.0f / sqrtf((float)hd));
+    for (uint32_t b = 0; b < batch; ++b) {
+        const uint32_t ql = q_lens[b], kl = kv_lens[b];
+        if (ql == 0 || kl == 0 || ql > kl) return -8;
+#pragma omp parallel for collapse(2) schedule(dynamic)
+        for (uint32_t i = 0; i < ql; ++i) {
+            for (uint32_t h = 0; h < q_heads; ++h) {
+                const uint32_t end = kl - ql + i, kvh = h / group;
+                const float* qh = q + ((size_t)(q_off[b] + i) * q_heads + h) * hd;
+                float* scores = (float*)malloc((size_t)(end + 1) * sizeof(float));
+                float mx = -1e30f;
+                for (uint32_t t = 0; t <= end; ++t) {
+                    const float* kh = k + ((size_t)(kv_off[b] + t) * kv_heads + kvh) * hd;
+                    float dot = 0.0f;
+                    for (uint32_t d = 0; d < hd; ++d) dot += qh[d] * kh[d];
+                    scores[t] = dot * inv_sqrt;
+                    if (scores[t] > mx) mx = scores[t];
+                }
+                float denom = 0.0f;
+                for (uint32_t t = 0; t <= end; ++t) denom += expf(scores[t] - mx);
+                if (!(denom > 0.0f)) denom = 1.0f;
+                float* oh = out + ((size_t)(q_off[b] + i) * q_heads + h) * hd;
+                for (uint32_t d = 0; d < hd; ++d) {
+                    float acc = 0.0f;
+                    for (uint32_t t = 0; t <= end; ++t) {
+                        const float* vh = v + ((size_t)(kv_off[b] + t) * kv_heads + kvh) * hd;
+                        acc += (expf(scores[t] - mx) / denom) * vh[d];
+                    }
+                    oh[d] = acc;
+                }
+                free(scores);
+            }
+        }
+    }
+    return 0;
+}
+

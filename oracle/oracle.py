@@ -352,3 +352,17 @@ def decode_layer(cfg: LayerCfg, x, w, K, V, pos: int):
                                 C.c_uint32(pos), _p(dbg_q), _p(dbg_att))
     assert rc == 0, rc
     return out, dbg_q, dbg_att
+
+
+def attention_prefill_varlen(q, k, v, q_offsets, kv_offsets, q_lens, kv_lens, q_heads: int, kv_heads: int, hd: int) -> np.ndarray:
+    """Packed causal prefill attention (cuda/kernels.cu:3749-3835): q [total_q, q_heads, hd], k / v [total_kv, kv_heads,
+    hd] f32; q row i of a sequence attends its kv rows 0 .. kv_len - q_len + i."""
+    q, k, v = _f32(q), _f32(k), _f32(v)
+    qo, ko = np.ascontiguousarray(q_offsets, np.uint32), np.ascontiguousarray(kv_offsets, np.uint32)
+    ql, kl = np.ascontiguousarray(q_lens, np.uint32), np.ascontiguousarray(kv_lens, np.uint32)
+    out = np.zeros_like(q)
+    rc = lib().orc_attention_prefill_varlen(_p(q), _p(k), _p(v), _p(qo), _p(ko), _p(ql), _p(kl), C.c_uint32(len(ql)),
+                                            C.c_uint32(q_heads), C.c_uint32(kv_heads), C.c_uint32(hd), _p(out))
+    assert rc == 0, rc
+    return out
+

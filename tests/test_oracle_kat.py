@@ -347,3 +347,34 @@ def test_decode_layer_composition(O):
     g, u = f(w["wg"]) @ x1n, f(w["wu"]) @ x1n
     ref = x1 + f(w["wd"]) @ (g / (1 + np.exp(-g)) * u)
     np.testing.assert_allclose(out, ref, atol=2e-5)
+
+
+def test_prefill_varlen_closed_form(O):
+    """Packed causal prefill (tests/attention_prefill_varlen.rs:19-140: 4 / 2 heads, (q_len, kv_len) = (3, 3), (2, 5),
+    (1, 4), head_dim 64 and 128, tolerance 1e-6 in the reference) against a float64 restatement; the last q row of a
+    sequence equals last-token attention over the same f16-exact keys and values."""
+    rng = np.random.default_rng(0)
+    for hd in (64, 128):
+        qh, kvh = 4, 2
+        pairs = [(3, 3), (2, 5), (1, 4)]
+        ql = np.array([p[0] for p in pairs], np.uint32)
+        kl = np.array([p[1] for p in pairs], np.uint32)
+        qo = np.concatenate([[0], np.cumsum(ql)[:-1]]).astype(np.uint32)
+        ko = np.concatenate([[0], np.cumsum(kl)[:-1]]).astype(np.uint32)
+        q = rng.standard_normal((int(ql.sum()), qh, hd)).astype(np.float32)
+        k = rng.standard_normal((int(kl.sum()), kvh, hd)).astype(np.float16).astype(np.float32)
+        v = rng.standard_normal((int(kl.sum()), kvh, hd)).astype(np.float16).astype(np.float32)
+        out = O.attention_prefill_varlen(q, k, v, qo, ko, ql, kl, qh, kvh, hd)
+        for b in range(len(pairs)):
+            for i in range(ql[b]):
+                for h in range(qh):
+                    end = kl[b] - ql[b] + i
+                    kk = k[ko[b]:ko[b] + end + 1, h // 2].astype(np.float64)
+                    vv = v[ko[b]:ko[b] + end + 1, h // 2].astype(np.float64)
+                    s = kk @ q[qo[b] + i, h].astype(np.float64) / np.sqrt(hd)
+                    p = np.exp(s - s.max())
+                    assert np.abs(out[qo[b] + i, h] - (p / p.sum()) @ vv).max() < 2e-6
+            last = O.attention_gqa(k[ko[b]:ko[b] + kl[b]].astype(np.float16), v[ko[b]:ko[b] + kl[b]].astype(np.float16),
+                                   q[qo[b] + ql[b] - 1].reshape(-1), qh, int(kl[b]))
+            assert np.abs(out[qo[b] + ql[b] - 1].reshape(-1) - last).max() < 2e-6
+
