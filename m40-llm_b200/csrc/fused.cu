@@ -158,8 +158,18 @@ extern "C" int m40llm_qkv_rope_append_attention_async(
     if (norm_w_dtype > 1) return -4;
     if (m40_ensure_device(ctx) != 0) return -1;
     const uint32_t hd = kv->head_dim, QD = q_heads * hd, KD = kv->num_heads * hd;
+    // The cluster kernel saves two launches per layer, which is what counts while a sequence's K / V is a few MB
+    // (1198 against 1087 tokens/s on a 22-layer stack at context 2048); with tens of MB to stream its 16 CTAs per kv
+    // head fall behind the separate split + merge launches (87 against 82 us per layer step at context 8K). The
+    // lengths live on the device, so the cache's capacity stands in for them.
+    static long fused_row_max_bytes = -1;
+    if (fused_row_max_bytes < 0) {
+        const char* e = getenv("M40LLM_FUSED_ROW_MAX_KV_MB");
+        fused_row_max_bytes = (e ? atol(e) : 8L) << 20;
+    }
+    const size_t kv_bytes = (size_t)kv->num_heads * kv->max_seq_len * hd * 4u;  // K and V rows of one sequence, f16
     const bool one_launch_attention = rows == 1 && !kv->compressed && kv->d_k && kv->d_v && (hd == 64 || hd == 128) &&
-                                      q_heads / kv->num_heads <= 16 && getenv("M40LLM_NO_FUSED_ROW") == nullptr;
+                                      q_heads / kv->num_heads <= 16 && kv_bytes <= (size_t)fused_row_max_bytes;
     if (one_launch_attention) {
         const size_t need = (size_t)rows * ((size_t)QD + 2 * (size_t)KD) * sizeof(float);
         float* scratch = (float*)m40_ensure_scratch(ctx, 1, need, 1);

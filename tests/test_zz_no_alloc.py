@@ -48,12 +48,14 @@ def test_static_matches_regular_twice_in_a_row(nat, O, qh, kvh, hd, max_seq):
 
 
 def test_static_rejects_what_it_cannot_hold(nat):
-    # 64 q heads x 128 splits x (2 + 128) floats = 1 064 960 > 2^20: refused before any launch
-    kv = nat.kv_dense(16384, 1, 4, 128)
+    # 64 q heads x 128 splits x (2 + 128) floats = 1 064 960 > 2^20: refused before any launch (a 131072-token sequence
+    # is cut into the maximum of 128 splits of 1024 tokens)
+    kv = nat.kv_dense(131072, 1, 4, 128)
     q = np.zeros(64 * 128, np.float32)
     dq, do = nat.buf(q), nat.buf(q.nbytes)
     L = nat.lib
-    assert L.m40llm_attention_last_token_f32_gqa_static_async(nat.ctx, kv, 0, dq.ptr, 64, 16384, do.ptr) == ERR_LIMIT
+    assert L.m40llm_attention_last_token_f32_gqa_static_async(nat.ctx, kv, 0, dq.ptr, 64, 131072, do.ptr) == ERR_LIMIT
+    assert L.m40llm_attention_last_token_f32_gqa_static_async(nat.ctx, kv, 0, dq.ptr, 64, 16384, do.ptr) == 0   # fits
     # argument checks are the regular entry point's
     assert L.m40llm_attention_last_token_f32_gqa_static_async(nat.ctx, kv, 1, dq.ptr, 64, 16, do.ptr) == -2
     assert L.m40llm_attention_last_token_f32_gqa_static_async(nat.ctx, kv, 0, dq.ptr, 64, 0, do.ptr) == -3
