@@ -80,6 +80,36 @@ def q4_inputs(name):
     q = r.standard_normal(qh * hd).astype(np.float32)
     return k, v, q
 
+PREFILL_CASES = {  # name: (q_heads, kv_heads, hd, [(q_len, kv_len), ...])
+    "prefill_ref_hd64": (4, 2, 64, [(3, 3), (2, 5), (1, 4)]), "prefill_ref_hd128": (4, 2, 128, [(3, 3), (2, 5), (1, 4)]),
+    "prefill_tiles_hd64": (8, 2, 64, [(65, 65), (17, 200)]), "prefill_tiles_hd128": (8, 4, 128, [(130, 130), (1, 70)]),
+}
+
+
+def prefill_inputs(name):
+    """(q, k, v, q_offsets, kv_offsets, q_lens, kv_lens): packed f32 rows [tokens][heads][hd]."""
+    qh, kvh, hd, pairs = PREFILL_CASES[name]
+    rng = rng_for(name)
+    ql = np.array([p[0] for p in pairs], np.uint32)
+    kl = np.array([p[1] for p in pairs], np.uint32)
+    qo = np.concatenate([[0], np.cumsum(ql)[:-1]]).astype(np.uint32)
+    ko = np.concatenate([[0], np.cumsum(kl)[:-1]]).astype(np.uint32)
+    q = rng.standard_normal((int(ql.sum()), qh, hd)).astype(np.float32)
+    k = rng.standard_normal((int(kl.sum()), kvh, hd)).astype(np.float32)
+    v = rng.standard_normal((int(kl.sum()), kvh, hd)).astype(np.float32)
+    return q, k, v, qo, ko, ql, kl
+
+
+def prefill_sample_rows(name):
+    """Packed q rows whose outputs are stored in the fixture: per sequence the first two, the middle and the last row and
+    the rows around the 64-row tile boundary."""
+    _, _, _, pairs = PREFILL_CASES[name]
+    rows, off = [], 0
+    for ql, _ in pairs:
+        rows += [off + r for r in sorted({0, 1, ql // 2, ql - 1, 63, 64, 65} & set(range(ql)))]
+        off += ql
+    return np.array(rows, np.int64)
+
 
 def cache_sample_tokens(L):
     """Token positions whose cache rows are stored in the fixture (the whole cache would be megabytes)."""

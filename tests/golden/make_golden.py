@@ -30,7 +30,11 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--lib", choices=["ref", "mine"], required=True)
     ap.add_argument("--out", required=True)
+    ap.add_argument("--only", default="", help="comma-separated case-name prefixes to generate (default: everything)")
+    ap.add_argument("--merge-into", default="", help="existing .npz whose arrays are kept and extended by this run")
     args = ap.parse_args()
+    only = [x for x in args.only.split(",") if x]
+    want = lambda name: not only or any(name.startswith(x) for x in only)
     pkg = helpers.load_package()
     if args.lib == "ref":
         dll = helpers.load_reference_lib(pkg)
@@ -43,6 +47,8 @@ def main():
     p = lambda a: a.ctypes.data_as(C.c_void_p)
 
     for name, (rows, dim) in cases.NORM_CASES.items():
+        if not want(name):
+            continue
         x, w = cases.norm_inputs(name)
         dx, dw, dy = nat.buf(x), nat.buf(w), nat.buf(x.nbytes)
         assert L.m40llm_rms_norm_f32_async(ctx, dx.ptr, dy.ptr, rows, dim, 1e-5) == 0
@@ -54,6 +60,8 @@ def main():
         nat.free_all()
 
     for name, (rows, heads, hd, past, base, layout) in cases.ROPE_CASES.items():
+        if not want(name):
+            continue
         x = cases.rope_inputs(name)
         dx = nat.buf(x)
         assert L.m40llm_rope_f32_inplace_layout_async(ctx, dx.ptr, rows, heads, hd, past, base, 1.0, layout) == 0
@@ -62,6 +70,8 @@ def main():
         nat.free_all()
 
     for name, (M, N, K) in cases.GEMM_CASES.items():
+        if not want(name):
+            continue
         a, w = cases.gemm_inputs(name)
         b = np.ascontiguousarray(w.T)
         da, da16, dw, db, dc = nat.buf(a), nat.buf(a.astype(np.float16)), nat.buf(w), nat.buf(b), nat.buf(M * N * 4)
@@ -89,6 +99,8 @@ def main():
     nat.free_all()
 
     for name, (qh, kvh, hd, Ln) in cases.ATTN_CASES.items():
+        if not want(name):
+            continue
         k, v, q = cases.attn_inputs(name)
         kv = nat.kv_dense(Ln, 1, kvh, hd)
         # K through the fused RoPE append (theta 1e4, adjacent) so the cache content itself is a golden
@@ -112,6 +124,8 @@ def main():
         nat.free_all()
 
     for name, (qh, kvh, hd, lens) in cases.BATCH_CASES.items():
+        if not want(name):
+            continue
         ks, vs, q = cases.batch_inputs(name)
         kv = nat.kv_dense(max(lens), len(lens), kvh, hd)
         for b in range(len(lens)):
@@ -124,6 +138,8 @@ def main():
         nat.free_all()
 
     for name, (qh, kvh, hd, Ln, R, bs, top) in cases.Q4_CASES.items():
+        if not want(name):
+            continue
         k, v, q = cases.q4_inputs(name)
         kv = nat.kv_compressed(Ln, 1, kvh, hd, R, bs, top)
         nat.kv_append_tokens(kv, 0, k, v, scale=0.0)
@@ -144,6 +160,23 @@ def main():
         L.m40llm_kvcache_destroy(kv)
         nat.free_all()
 
+    for name, (qh, kvh, hd, pairs) in cases.PREFILL_CASES.items():
+        if not want(name):
+            continue
+        q, k, v, qo, ko, ql, kl = cases.prefill_inputs(name)
+        dq, dk, dv, do = nat.buf(q), nat.buf(k), nat.buf(v), nat.buf(q.nbytes)
+        dqo, dko, dql, dkl = nat.buf(qo), nat.buf(ko), nat.buf(ql), nat.buf(kl)
+        rc = L.m40llm_attention_prefill_f32_gqa_varlen(ctx, dq.ptr, dk.ptr, dv.ptr, dqo.ptr, dko.ptr, dql.ptr, dkl.ptr,
+                                                       len(pairs), qh, kvh, hd, do.ptr)
+        assert rc == 0, rc
+        nat.sync(0)
+        out[name + "/out"] = do.download(np.float32, q.shape)[cases.prefill_sample_rows(name)]
+        nat.free_all()
+
+    if args.merge_into and os.path.exists(args.merge_into):
+        merged = dict(np.load(args.merge_into))
+        merged.update(out)
+        out = merged
     os.makedirs(os.path.dirname(os.path.abspath(args.out)), exist_ok=True)
     np.savez_compressed(args.out, **out)
     print(f"wrote {args.out}: {len(out)} arrays, {os.path.getsize(args.out)} bytes")

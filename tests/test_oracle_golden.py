@@ -92,3 +92,15 @@ def test_q4_direct_and_selection(O, gold):
         assert int(gold[name + "/total_blocks"][0]) == len(s64)
         assert_selection_matches(gold[name + "/head0_blocks"], blocks, s64, what=name)
         np.testing.assert_allclose(gold[name + "/head0_scores"], [s64[int(b)] for b in gold[name + "/head0_blocks"]], atol=2e-5)
+
+
+def test_prefill_varlen(O, gold):
+    """Packed causal prefill attention: the oracle's restatement against the reference kernel's own outputs (f32 end to
+    end on both sides; the reference test allows 1e-6 against its CPU formula)."""
+    for name, (qh, kvh, hd, pairs) in cases.PREFILL_CASES.items():
+        if name + "/out" not in gold:
+            pytest.skip("fixture predates the prefill cases")
+        q, k, v, qo, ko, ql, kl = cases.prefill_inputs(name)
+        rows = cases.prefill_sample_rows(name)
+        assert_close(O.attention_prefill_varlen(q, k, v, qo, ko, ql, kl, qh, kvh, hd)[rows], gold[name + "/out"], atol=2e-5,
+                     rtol=1e-5, what=name)
