@@ -57,14 +57,9 @@ struct M40llmCudaContext {
     size_t pf_hint_bytes[2];
 };
 
-// Leaves a prefetch hint (see M40llmCudaContext::pf_hint_ptr); each range is capped at `cap` bytes.
-static inline void m40_set_prefetch_hint(M40llmCudaContext* ctx, const void* p0, size_t b0, const void* p1, size_t b1) {
-    const size_t cap = (size_t)12u << 20;
-    ctx->pf_hint_ptr[0] = p0;
-    ctx->pf_hint_bytes[0] = p0 ? (b0 < cap ? b0 : cap) : 0;
-    ctx->pf_hint_ptr[1] = p1;
-    ctx->pf_hint_bytes[1] = p1 ? (b1 < cap ? b1 : cap) : 0;
-}
+// Leaves a prefetch hint (see M40llmCudaContext::pf_hint_ptr); each range is capped at 12 MiB. M40LLM_PREFETCH_HINTS=0
+// turns the hints off.
+void m40_set_prefetch_hint(M40llmCudaContext* ctx, const void* p0, size_t b0, const void* p1, size_t b1);
 
 struct M40llmCudaGraphExec {
     cudaGraph_t graph;
@@ -186,10 +181,15 @@ __device__ __forceinline__ float warp_max(float v) {
 // is only good to a few ulp, so the inverse frequency is evaluated in double and rounded once: this makes the
 // device angle equal to the host reference's angle instead of merely close to it.
 __device__ __forceinline__ void rope_cs(uint32_t pos, uint32_t pair, uint32_t head_dim, float freq_base,
-                                        float freq_scale, float* c, float* s) {
+                                        float freq_scale, float* c, float* s, const float* inv_freq_table = nullptr) {
     const float p = static_cast<float>(pos) * freq_scale;
-    const float e = -2.0f * static_cast<float>(pair) / static_cast<float>(head_dim);
-    const float inv_freq = static_cast<float>(pow(static_cast<double>(freq_base), static_cast<double>(e)));
+    float inv_freq;
+    if (inv_freq_table) {  // the same value, made on the host (see m40_rope_inv_freq below)
+        inv_freq = inv_freq_table[pair];
+    } else {
+        const float e = -2.0f * static_cast<float>(pair) / static_cast<float>(head_dim);
+        inv_freq = static_cast<float>(pow(static_cast<double>(freq_base), static_cast<double>(e)));
+    }
     const float theta = p * inv_freq;
     *c = cosf(theta);
     *s = sinf(theta);

@@ -23,7 +23,8 @@ __global__ void __launch_bounds__(64) rope_q_append_kv_rows_kernel(float* __rest
                                                                    const uint32_t* __restrict__ seq_ids,
                                                                    const uint32_t* __restrict__ positions,
                                                                    uint32_t q_heads, float freq_base, float freq_scale,
-                                                                   uint32_t layout, uint32_t* status) {
+                                                                   uint32_t layout, uint32_t* status,
+                                                                   const float* __restrict__ inv_freq) {
     __shared__ float red[32];
     pdl_wait();
     pdl_trigger();
@@ -40,7 +41,7 @@ __global__ void __launch_bounds__(64) rope_q_append_kv_rows_kernel(float* __rest
             const uint32_t i0 = layout == 1u ? i : 2u * i;
             const uint32_t i1 = layout == 1u ? i + half : 2u * i + 1u;
             float c, s;
-            rope_cs(pos, i, hd, freq_base, freq_scale, &c, &s);
+            rope_cs(pos, i, hd, freq_base, freq_scale, &c, &s, inv_freq);
             const float a = qh[i0], b = qh[i1];
             qh[i0] = a * c - b * s;
             qh[i1] = a * s + b * c;
@@ -50,8 +51,8 @@ __global__ void __launch_bounds__(64) rope_q_append_kv_rows_kernel(float* __rest
     const uint32_t kvh = hsel - q_heads;
     const float* kh = k + ((size_t)row * kv.num_heads + kvh) * hd;
     const float* vh = v + ((size_t)row * kv.num_heads + kvh) * hd;
-    if (kv.compressed) kv_append_compressed_head(kv, seq, kvh, pos, kh, vh, freq_base, freq_scale, layout, red);
-    else kv_append_dense_head(kv, seq, kvh, pos, kh, vh, freq_base, freq_scale, layout);
+    if (kv.compressed) kv_append_compressed_head(kv, seq, kvh, pos, kh, vh, freq_base, freq_scale, layout, red, inv_freq);
+    else kv_append_dense_head(kv, seq, kvh, pos, kh, vh, freq_base, freq_scale, layout, inv_freq);
 }
 
 }  // namespace
@@ -110,7 +111,7 @@ extern "C" int m40llm_qkv_rmsnorm_rope_append_async(M40llmCudaContext* ctx, M40l
         const bool tail_in_epilogue = !kv->compressed && rope_layout == 0u && QD % 128u == 0u && KD % 128u == 0u;
         const M40TcRopeAppend ra = {d_seq_ids, d_positions, (__half*)kv->d_k, (__half*)kv->d_v, kv->d_seq_map,
                                     ctx->d_status, hd, kv->num_heads, kv->max_seq_len, kv->max_batch_size,
-                                    freq_base, freq_scale};
+                                    freq_base, freq_scale, m40_rope_inv_freq(ctx, freq_base, hd)};
         rc = m40_gemm_tc_f16(ctx, s, 1u, (const float*)d_x_f32, (int)rows, (int)hidden, 3, w, n, o, b, nullptr, 0, &norm,
                              tail_in_epilogue ? &ra : nullptr);
         if (rc != 0) return rc;
@@ -131,7 +132,8 @@ extern "C" int m40llm_qkv_rmsnorm_rope_append_async(M40llmCudaContext* ctx, M40l
     dim3 grid(q_heads + kv->num_heads, rows);
     const cudaError_t e = m40_launch_dependent(rope_q_append_kv_rows_kernel, grid, dim3(64), 0, s, (float*)d_q_out_f32,
                                                (const float*)kbuf, (const float*)vbuf, *kv, d_seq_ids, d_positions,
-                                               q_heads, freq_base, freq_scale, rope_layout, ctx->d_status);
+                                               q_heads, freq_base, freq_scale, rope_layout, ctx->d_status,
+                                               m40_rope_inv_freq(ctx, freq_base, hd));
     M40_COUNT_LAUNCH(ctx);
     return e == cudaSuccess && cudaGetLastError() == cudaSuccess ? 0 : -6;
 }
@@ -194,7 +196,8 @@ extern "C" int m40llm_qkv_rope_append_attention_async(
             if (ce != cudaSuccess) return -6;
             rope_q_append_kv_rows_kernel<<<grid, 64, 0, ctx->decode_stream>>>((float*)d_q_out_f32, kbuf, vbuf, *kv, d_seq_ids,
                                                                               d_positions, q_heads, freq_base, freq_scale,
-                                                                              rope_layout, ctx->d_status);
+                                                                              rope_layout, ctx->d_status,
+                                                                              m40_rope_inv_freq(ctx, freq_base, hd));
             M40_COUNT_LAUNCH(ctx);
             if (cudaGetLastError() != cudaSuccess) return -6;
             return m40llm_attention_last_token_f32_gqa_batched_async(ctx, kv, d_seq_ids, d_seq_lens, rows, d_q_out_f32,

@@ -341,7 +341,7 @@ __global__ void __launch_bounds__(256) gemm_tc_epilogue_kernel(EpiArgs e) {
         }
         if (p < 2) {
             float c, sn;
-            rope_cs(pos, d >> 1, ra.head_dim, ra.freq_base, ra.freq_scale, &c, &sn);
+            rope_cs(pos, d >> 1, ra.head_dim, ra.freq_base, ra.freq_scale, &c, &sn, ra.inv_freq);
             r = (d & 1u) ? other * sn + r * c : r * c - other * sn;
         }
         if (p == 0) {

@@ -15,6 +15,7 @@ struct M40TcRopeAppend {
     uint32_t* status;
     uint32_t head_dim, kv_heads, max_seq_len, max_batch;
     float freq_base, freq_scale;
+    const float* inv_freq;  // host-made inverse-frequency table [head_dim / 2] or null (see m40_rope_inv_freq)
 };
 
 // True when the tcgen05 path can take this problem set (2 <= M <= 256, K % 8 == 0, 16-byte aligned weights).

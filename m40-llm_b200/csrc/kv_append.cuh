@@ -41,7 +41,8 @@ __device__ __forceinline__ void quantize_v_row_q4(const __half* __restrict__ v, 
 __device__ __forceinline__ void kv_append_compressed_head(const M40llmKVCache& kv, uint32_t seq_id, uint32_t head,
                                                           uint32_t position, const float* __restrict__ k_in,
                                                           const float* __restrict__ v_in, float freq_base,
-                                                          float freq_scale, uint32_t layout, float* red) {
+                                                          float freq_scale, uint32_t layout, float* red,
+                                                          const float* inv_freq = nullptr) {
     const uint32_t hd = kv.head_dim, half = hd / 2u, R = kv.recent_window, heads = kv.num_heads;
     const uint32_t tid = threadIdx.x;
     const size_t ring_row = kv_row_offset(seq_id, head, position % R, heads, R, hd);
@@ -58,7 +59,7 @@ __device__ __forceinline__ void kv_append_compressed_head(const M40llmKVCache& k
         const uint32_t i0 = layout == 1u ? tid : 2u * tid;
         const uint32_t i1 = layout == 1u ? tid + half : 2u * tid + 1u;
         float c, s;
-        rope_cs(position, tid, hd, freq_base, freq_scale, &c, &s);
+        rope_cs(position, tid, hd, freq_base, freq_scale, &c, &s, inv_freq);
         const float a = k_in[i0], b = k_in[i1];
         kv.d_recent_k[ring_row + i0] = __float2half_rn(a * c - b * s);
         kv.d_recent_k[ring_row + i1] = __float2half_rn(a * s + b * c);
@@ -72,14 +73,15 @@ __device__ __forceinline__ void kv_append_compressed_head(const M40llmKVCache& k
 __device__ __forceinline__ void kv_append_dense_head(const M40llmKVCache& kv, uint32_t seq_id, uint32_t head,
                                                      uint32_t position, const float* __restrict__ k_in,
                                                      const float* __restrict__ v_in, float freq_base,
-                                                     float freq_scale, uint32_t layout) {
+                                                     float freq_scale, uint32_t layout,
+                                                     const float* inv_freq = nullptr) {
     const uint32_t hd = kv.head_dim, half = hd / 2u;
     const size_t row = kv_row_offset(seq_id, head, position, kv.num_heads, kv.max_seq_len, hd);
     for (uint32_t i = threadIdx.x; i < half; i += blockDim.x) {
         const uint32_t i0 = layout == 1u ? i : 2u * i;
         const uint32_t i1 = layout == 1u ? i + half : 2u * i + 1u;
         float c, s;
-        rope_cs(position, i, hd, freq_base, freq_scale, &c, &s);
+        rope_cs(position, i, hd, freq_base, freq_scale, &c, &s, inv_freq);
         const float a = k_in[i0], b = k_in[i1];
         kv.d_k[row + i0] = __float2half_rn(a * c - b * s);
         kv.d_k[row + i1] = __float2half_rn(a * s + b * c);
