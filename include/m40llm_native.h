@@ -514,11 +514,6 @@ int m40llm_context_launch_count(M40llmCudaContext* ctx, uint64_t* out_count);
  * earlier keeps working on the memory it was captured with. A harness can watch this counter to see that a call
  * allocated. */
 int m40llm_context_scratch_generation(M40llmCudaContext* ctx, uint64_t* out_generation);
-/* Performance hint, never required: the weights that the call AFTER the next one will stream first (the next layer's
- * Wq while this layer's FFN runs). The last one-row streaming launch of the next m40llm_attn_out_ffn_async call pulls
- * the first bytes of that range (at most 12 MiB) into L2 while it drains, so that the following projection's first
- * loads hit L2 instead of an idle HBM. Consumed by that call; NULL or 0 clears it. Host-side only, no launch. */
-int m40llm_prefetch_hint(M40llmCudaContext* ctx, const void* d_next_weights, size_t bytes);
 /* The raw CUDA stream handle of a stream kind, for harnesses that time with their own events. */
 int m40llm_context_stream_handle(M40llmCudaContext* ctx, uint32_t stream_kind, void** out_stream);
 

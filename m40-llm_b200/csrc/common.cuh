@@ -51,15 +51,8 @@ struct M40llmCudaContext {
     float rope_table_base[4];
     uint32_t rope_table_hd[4];
     uint32_t rope_tables;
-    // Prefetch hint for the next streaming launch on the decode stream: up to two ranges it pulls into L2 while it
-    // drains (the head of the weights that the launch after it will stream). Consumed and cleared by that launch.
-    const void* pf_hint_ptr[2];
-    size_t pf_hint_bytes[2];
 };
 
-// Leaves a prefetch hint (see M40llmCudaContext::pf_hint_ptr); each range is capped at 12 MiB. M40LLM_PREFETCH_HINTS=0
-// turns the hints off.
-void m40_set_prefetch_hint(M40llmCudaContext* ctx, const void* p0, size_t b0, const void* p1, size_t b1);
 
 struct M40llmCudaGraphExec {
     cudaGraph_t graph;

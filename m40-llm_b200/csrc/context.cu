@@ -41,19 +41,6 @@ void* m40_ensure_scratch(M40llmCudaContext* ctx, uint32_t kind, size_t bytes, ui
     return p;
 }
 
-void m40_set_prefetch_hint(M40llmCudaContext* ctx, const void* p0, size_t b0, const void* p1, size_t b1) {
-    static int enabled = -1;
-    if (enabled < 0) {
-        const char* e = getenv("M40LLM_PREFETCH_HINTS");
-        enabled = (e && e[0] == '0') ? 0 : 1;
-    }
-    const size_t cap = (size_t)12u << 20;
-    ctx->pf_hint_ptr[0] = enabled ? p0 : nullptr;
-    ctx->pf_hint_bytes[0] = (enabled && p0) ? (b0 < cap ? b0 : cap) : 0;
-    ctx->pf_hint_ptr[1] = enabled ? p1 : nullptr;
-    ctx->pf_hint_bytes[1] = (enabled && p1) ? (b1 < cap ? b1 : cap) : 0;
-}
-
 const float* m40_rope_inv_freq(M40llmCudaContext* ctx, float freq_base, uint32_t head_dim) {
     if (!ctx || head_dim < 2 || head_dim > 512) return nullptr;
     for (uint32_t i = 0; i < ctx->rope_tables; ++i)
@@ -447,12 +434,6 @@ int m40llm_context_launch_count(M40llmCudaContext* ctx, uint64_t* out_count) {
 int m40llm_context_scratch_generation(M40llmCudaContext* ctx, uint64_t* out_generation) {
     if (!ctx || !out_generation) return -1;
     *out_generation = (uint64_t)ctx->scratch_generation;
-    return 0;
-}
-
-int m40llm_prefetch_hint(M40llmCudaContext* ctx, const void* d_next_weights, size_t bytes) {
-    if (!ctx) return -1;
-    m40_set_prefetch_hint(ctx, d_next_weights, bytes, nullptr, 0);
     return 0;
 }
 

@@ -230,13 +230,6 @@ extern "C" int m40llm_attn_out_ffn_async(M40llmCudaContext* ctx, const void* d_a
     if (ffn_q80 ? (hidden % 128 != 0 || ffn % 128 != 0) : (hidden % 8 != 0 || ffn % 8 != 0)) return -2;
     if (m40_ensure_device(ctx) != 0) return -1;
     cudaStream_t s = ctx->decode_stream;
-    const size_t ffn_row_bytes = ffn_q80 ? (size_t)(hidden / 32u) * 34u : (size_t)hidden * 2u;
-    const size_t down_bytes = ffn_q80 ? (size_t)hidden * (ffn / 32u) * 34u : (size_t)hidden * ffn * 2u;
-    // at one row each streaming launch pulls the head of its successor's weights into L2 while it drains; a hint
-    // the caller left for the end of this call (the next layer's first weights) moves to the last launch
-    const void* after_ptr = ctx->pf_hint_ptr[0];
-    const size_t after_bytes = ctx->pf_hint_bytes[0];
-    if (rows == 1) m40_set_prefetch_hint(ctx, d_wg, ffn_row_bytes * ffn, d_wu, ffn_row_bytes * ffn);
     // x1 = x + att.Wo (residual folded into the projection's store on every path)
     int rc = m40_gemm_dispatch_f16(ctx, s, 1u, (const float*)d_att_f32, (const __half*)d_wo_f16, (float*)d_x1_f32,
                                    (int)rows, (int)hidden, (int)q_dim, nullptr, (const float*)d_x_f32);
@@ -245,11 +238,9 @@ extern "C" int m40llm_attn_out_ffn_async(M40llmCudaContext* ctx, const void* d_a
         const int fmt = ffn_q80 ? M40_GEMV_Q80 : M40_GEMV_F16;
         const M40GemvSeg gu = {d_wg, d_wu, (float*)d_hid_f32, nullptr, nullptr, (int)ffn};
         const M40GemvNorm norm = {d_ffn_norm_w, norm_w_dtype == 1u ? 1 : 0, eps, nullptr};
-        m40_set_prefetch_hint(ctx, d_wd, down_bytes / 2, (const char*)d_wd + ((down_bytes / 2) & ~(size_t)15u), down_bytes / 2);
         rc = m40_gemv_stream(ctx, s, (const float*)d_x1_f32, (int)hidden, fmt, 1, 1, &gu, &norm);
         if (rc < 0) return rc;
         if (rc == 0) {
-            m40_set_prefetch_hint(ctx, after_ptr, after_bytes, nullptr, 0);
             const M40GemvSeg dn = {d_wd, nullptr, (float*)d_out_f32, nullptr, (const float*)d_x1_f32, (int)hidden};
             rc = m40_gemv_stream(ctx, s, (const float*)d_hid_f32, (int)ffn, fmt, 0, 1, &dn, nullptr);
             if (rc < 0) return rc;

@@ -66,15 +66,7 @@ struct GemvArgs {
     int nseg, K, pieces, cw, R, nstages, total_groups;
     uint32_t row_bytes, stage_bytes, xq_off;
     int first_late;  // ring slots from this one on share their bytes with the activation digits
-    // Up to two ranges (the head of the weights the NEXT kernel will stream) pulled into L2 while this kernel drains.
-    const uint8_t* pf_ptr[2];
-    uint32_t pf_bytes[2];
 };
-
-// L2 prefetch of [p, p + bytes): bytes a multiple of 16, p 16-byte aligned.
-__device__ __forceinline__ void bulk_prefetch_l2(const void* p, uint32_t bytes) {
-    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
-}
 
 __device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
@@ -250,17 +242,6 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_stream_kernel(const __grid_co
             issued = i + PWARPS;
             s += PWARPS;
             if (s >= a.nstages) s -= a.nstages, ++use;
-        }
-        if (!abort_flag && a.pf_bytes[pw]) {
-            // Every load of this launch has been issued; what follows is the drain of the ring, the dependent launch
-            // and the successor's first memory round trip, during which HBM would idle. This CTA's share of the
-            // successor's first weights goes to L2 meanwhile (64 KB requests), so that its ramp hits L2.
-            const uint32_t per = ((a.pf_bytes[pw] / gridDim.x) + 15u) & ~15u;
-            const uint32_t off = blockIdx.x * per;
-            if (off < a.pf_bytes[pw]) {
-                const uint32_t n = min(per, a.pf_bytes[pw] - off) & ~15u;
-                for (uint32_t o = 0; o < n; o += 65536u) bulk_prefetch_l2(a.pf_ptr[pw] + off + o, min(65536u, n - o));
-            }
         }
         if (abort_flag) {
             // the consumers have stopped: wait (bounded) for this thread's copies still in flight before the CTA
@@ -666,14 +647,6 @@ int m40_gemv_stream(M40llmCudaContext* ctx, cudaStream_t s, const float* x, int 
         a.norm_f32 = norm->w_is_f32;
         a.eps = norm->eps;
         a.xn_out = norm->xn_out;
-    }
-    for (int i = 0; i < 2; ++i) {  // a hint left for the next streaming launch is consumed here
-        if (ctx->pf_hint_ptr[i] && (((uintptr_t)ctx->pf_hint_ptr[i]) & 15u) == 0u) {
-            a.pf_ptr[i] = (const uint8_t*)ctx->pf_hint_ptr[i];
-            a.pf_bytes[i] = (uint32_t)(ctx->pf_hint_bytes[i] & ~(size_t)15u);
-        }
-        ctx->pf_hint_ptr[i] = nullptr;
-        ctx->pf_hint_bytes[i] = 0;
     }
     const int grid = g < grid_max ? g : grid_max;
     const size_t smem = smem_bytes;

@@ -68,10 +68,6 @@ int DecodeModel::enqueue_step() {
                                                     cfg_.q_heads, cfg_.rope_base, cfg_.rope_scale, cfg_.rope_layout, d_q_,
                                                     d_att_);
         if (rc != 0) return fail(rc, "qkv_rope_append_attention");
-        // what the launch after this layer's FFN streams first: the next layer's Wq, or the lm_head after the last
-        const bool last = l + 1 == layers_.size();
-        m40llm_prefetch_hint(ctx_, last ? head_.lm_head : layers_[l + 1].wq,
-                             last ? (size_t)head_.vocab * H * 2 : (size_t)QD * H * 2);
         rc = m40llm_attn_out_ffn_async(ctx_, d_att_, w.wo, x, w.ffn_norm, 1u, cfg_.rms_eps, w.wg, w.wu, w.wd,
                                        w.ffn_q80 ? 1u : 0u, d_x1_, d_hid_, y, r, H, QD, cfg_.ffn);
         if (rc != 0) return fail(rc, "attn_out_ffn");
