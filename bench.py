@@ -597,6 +597,51 @@ def splitk_case(nat, pkg, O, rank, world, dist, peak, reps=200):
     return record
 
 
+def prefill_case(nat, ev, reps=10):
+    """Packed varlen prefill attention (the tensor-bound sibling of the decode path): Llama-3-8B heads, four sequences
+    of 2048, 1536, 1024 and 512 prompt tokens, causal, f32 in and out as the reference passes them. FLOPs counted
+    algorithmically: 4 * head_dim per (q row, visible kv row, q head)."""
+    L, ctx = nat.lib, nat.ctx
+    qh, kvh, hd = QH, KVH, HD
+    lens = np.array([2048, 1536, 1024, 512], np.uint32)
+    off = np.concatenate([[0], np.cumsum(lens)[:-1]]).astype(np.uint32)
+    rng = np.random.default_rng(17)
+    total = int(lens.sum())
+    dq = nat.buf(rng.standard_normal((total, qh, hd), dtype=np.float32))
+    dk = nat.buf(rng.standard_normal((total, kvh, hd), dtype=np.float32))
+    dv = nat.buf(rng.standard_normal((total, kvh, hd), dtype=np.float32))
+    do = nat.buf(total * qh * hd * 4)
+    dlen, doff = nat.buf(lens), nat.buf(off)
+    call = lambda: L.m40llm_attention_prefill_f32_gqa_varlen_async(ctx, dq.ptr, dk.ptr, dv.ptr, doff.ptr, doff.ptr, dlen.ptr,
+                                                                 dlen.ptr, len(lens), qh, kvh, hd, do.ptr)
+    for _ in range(2):
+        assert call() == 0
+    nat.sync(0)
+    e0, e1 = C.c_void_p(), C.c_void_p()
+    assert L.m40llm_cuda_event_create(ctx, C.byref(e0)) == 0 and L.m40llm_cuda_event_create(ctx, C.byref(e1)) == 0
+    assert L.m40llm_cuda_event_record(ctx, e0, 0) == 0
+    for _ in range(reps):
+        assert call() == 0
+    assert L.m40llm_cuda_event_record(ctx, e1, 0) == 0
+    ms = C.c_float()
+    assert L.m40llm_cuda_event_elapsed_sync(ctx, e0, e1, C.byref(ms)) == 0
+    ms = ms.value / reps
+    pairs = float(sum(int(n) * (int(n) + 1) // 2 for n in lens))
+    flops = 4.0 * hd * qh * pairs
+    tf = flops / (ms * 1e-3) / 1e12
+    peak_tf = 1636.2
+    try:
+        peak_tf = float(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["bf16_tflops"])
+    except Exception:
+        pass
+    for b in (dq, dk, dv, do, dlen, doff):
+        b.free()
+    return {"prompt_tokens": total, "sequences": [int(n) for n in lens], "ms_per_call": ms, "prompt_tokens_per_s": total / (ms * 1e-3),
+            "algorithmic_tflops": tf, "frac_of_bf16_tensor_peak": tf / peak_tf,
+            "note": "mma.sync (legacy tensor path) flash-attention kernel, f32 inputs rounded to f16 tiles in shared memory; "
+                    "the call also reads the lengths back to the host as the reference does"}
+
+
 def run_reference_arm(args, rank, world):
     """`--impl reference`: the reference's CPU path is Rust and cannot be built here (no cargo/rustc, no network),
     so the timed stand-in is the oracle port of that math, on all host threads. Rank 0 only. It is ONE CPU process on
@@ -926,6 +971,7 @@ def main():
 
     if rank == 0 and not args.no_extras:
         extra["compressed32k"] = compressed_case(nat, ev, peak)
+        extra["prefill_varlen"] = prefill_case(nat, ev)
 
     # ---------------- one long sequence, split-K over the ranks (BASELINE configs[3]); every rank takes part
     if not args.no_extras:

@@ -124,6 +124,16 @@ __device__ __forceinline__ void q80_worker(const Q80Args& a, const Q80Smem& sm, 
                 const uint4 t = chunk[i];
                 L[4 * i] = t.x, L[4 * i + 1] = t.y, L[4 * i + 2] = t.z, L[4 * i + 3] = t.w;
             }
+            // The raw bytes of this stage are in registers now: the slot goes back to the weight producer at once, not
+            // after the (long) wait for a free operand stage below, so that the next raw stage is requested a whole
+            // conversion earlier. The arrive carries a value computed from every loaded chunk, which makes it wait
+            // for the loads themselves (a warp's shared-memory load completes for all its lanes together).
+            {
+                const uint32_t seen = L[0] ^ L[4] ^ L[8] ^ L[12] ^ L[16] ^ L[3] ^ L[7] ^ L[11] ^ L[15] ^ L[19];
+                __syncwarp();
+                if (lane == 0)
+                    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0]; // %1" ::"r"(smem_u32(&sm.raw_empty[rs])), "r"(seen) : "memory");
+            }
             // the stage is free once every MMA of the sub-block that used it last (u - AST) has completed
             if (u >= AST && !wwait(&sm.done[(u - AST) % BS], ((u - AST) / BS) & 1u)) { ok = false; break; }
             tc_fence_after();
@@ -156,10 +166,7 @@ __device__ __forceinline__ void q80_worker(const Q80Args& a, const Q80Smem& sm, 
             tmem_st_wait();
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) {
-                mbar_arrive(&sm.a_full[as]);
-                mbar_arrive(&sm.raw_empty[rs]);  // the raw bytes of this stage are in registers / converted
-            }
+            if (lane == 0) mbar_arrive(&sm.a_full[as]);
         }
         if (!ok) break;
         // ---- end of the tile segment: read this row's accumulator columns and store the partial
