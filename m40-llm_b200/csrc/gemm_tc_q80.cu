@@ -201,6 +201,55 @@ __device__ __forceinline__ void q80_worker(const Q80Args& a, const Q80Smem& sm, 
     if (!ok) *sm.abort_flag = 1;
 }
 
+// One MMA-issuing thread. ROLE 0: both products of a sub-block (single issuer); 1: hi.[Xh | Xl]; 2: lo.Xh into its
+// own accumulator columns. The loop is this kernel's critical path: stage index and phase are carried, not
+// recomputed, and every instantiation holds only the instructions of its own role.
+template <int M_PAD, int ROLE>
+__device__ __forceinline__ void q80_issuer(const Q80Args& a, const Q80Smem& sm, uint32_t tmem_base, uint32_t b_smem0,
+                                        uint32_t u0, uint32_t u1) {
+    constexpr uint32_t B_BYTES = M_PAD * BLOCK_K * 2;
+    constexpr uint32_t BS = b_slots(M_PAD), AST = a_stages(M_PAD);
+    constexpr uint32_t A_COL0 = TB * acc_cols(M_PAD);
+    const uint32_t idesc2 = make_idesc(2 * M_PAD), idesc1 = make_idesc(M_PAD);
+    bool ok = true;
+    uint32_t pos = u0, seg = 0, as = 0, ph = 0, bs = 0;
+    const uint32_t a_tmem0 = tmem_base + A_COL0;
+    while (pos < u1 && ok) {
+        const uint32_t kb_begin = pos % a.units_per_tile;
+        uint32_t kb_end = kb_begin + (u1 - pos);
+        if (kb_end > a.units_per_tile) kb_end = a.units_per_tile;
+        const uint32_t tb = seg % TB;
+        if (seg >= TB && !mbar_wait(&sm.t_empty[tb], ((seg / TB) - 1) & 1u)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + (ROLE == 2 ? acc_lo_col(M_PAD, tb) : acc_hi_col(M_PAD, tb));
+        const uint32_t n_sub = (kb_end - kb_begin) * 4;
+        for (uint32_t j = 0; j < n_sub && ok; ++j) {
+            if (!mbar_wait(&sm.a_full[as], ph)) { ok = false; break; }
+            tc_fence_after();
+            const uint32_t ta = a_tmem0 + as * A_COLS;  // hi columns [0,32), lo columns [32,64)
+            const uint32_t sb = b_smem0 + bs * 2 * B_BYTES;
+#pragma unroll
+            for (uint32_t kk = 0; kk < BLOCK_K / UMMA_K; ++kk) {
+                const uint64_t b_x = make_desc_sw128(sb + kk * UMMA_K * 2);  // rows [0, M_PAD) = Xh, [M_PAD, 2 M_PAD) = Xl
+                const uint32_t a_hi = ta + kk * (UMMA_K / 2), a_lo = a_hi + 32;
+                if (ROLE == 2) {
+                    umma_f16_ts(d_tmem, a_lo, b_x, idesc1, (j | kk) != 0u);
+                } else {
+                    umma_f16_ts(d_tmem, a_hi, b_x, idesc2, (j | kk) != 0u);
+                    if (ROLE == 0) umma_f16_ts(d_tmem, a_lo, b_x, idesc1, 1u);
+                }
+            }
+            umma_commit(&sm.done[bs]);  // this thread's share of sub-block done: operand stage and activation slot
+            if (++as == AST) as = 0, ph ^= 1u;
+            if (++bs == BS) bs = 0;
+        }
+        if (ok) umma_commit(&sm.t_full[tb]);
+        pos += kb_end - kb_begin;
+        ++seg;
+    }
+    if (!ok) *sm.abort_flag = 1;
+}
+
 template <int M_PAD>
 __global__ void __launch_bounds__(CTA_THREADS, 1) gemm_tc_q80_kernel(const __grid_constant__ CUtensorMap tmW0,
                                                                      const __grid_constant__ CUtensorMap tmW1,
@@ -295,49 +344,17 @@ __global__ void __launch_bounds__(CTA_THREADS, 1) gemm_tc_q80_kernel(const __gri
         // ---------------- MMA issuers: one accumulator per tile segment, TMEM buffer = segment % TB. Warp 1 issues
         // hi against [Xh | Xl] (the two activation tiles are contiguous rows of one operand); the lo.Xh products go
         // to warp 3 and their own accumulator columns (dual issue) or follow from warp 1 into the first half.
-        constexpr bool DUAL = dual_issue(M_PAD);
-        const bool lo_thread = warp == 3;
-        if (lane == 0 && (DUAL || !lo_thread)) {
-            const uint32_t idesc2 = make_idesc(2 * M_PAD), idesc1 = make_idesc(M_PAD);
-            bool ok = true;
-            // the loop below is this kernel's critical path: stage index and phase are carried, not recomputed
-            uint32_t pos = u0, seg = 0, as = 0, ph = 0, bs = 0;
-            const uint32_t a_tmem0 = tmem_base + A_COL0, b_smem0 = smem_u32(s_b);
-            while (pos < u1 && ok) {
-                const uint32_t kb_begin = pos % a.units_per_tile;
-                uint32_t kb_end = kb_begin + (u1 - pos);
-                if (kb_end > a.units_per_tile) kb_end = a.units_per_tile;
-                const uint32_t tb = seg % TB;
-                if (seg >= TB && !mbar_wait(&t_empty[tb], ((seg / TB) - 1) & 1u)) { ok = false; break; }
-                tc_fence_after();
-                const uint32_t d_tmem = tmem_base + (DUAL && lo_thread ? acc_lo_col(M_PAD, tb) : acc_hi_col(M_PAD, tb));
-                const uint32_t n_sub = (kb_end - kb_begin) * 4;
-                for (uint32_t j = 0; j < n_sub && ok; ++j) {
-                    if (!mbar_wait(&a_full[as], ph)) { ok = false; break; }
-                    tc_fence_after();
-                    const uint32_t ta = a_tmem0 + as * A_COLS;  // hi columns [0,32), lo columns [32,64)
-                    const uint32_t sb = b_smem0 + bs * 2 * B_BYTES;
-#pragma unroll
-                    for (uint32_t kk = 0; kk < BLOCK_K / UMMA_K; ++kk) {
-                        const uint64_t b_x = make_desc_sw128(sb + kk * UMMA_K * 2);  // rows [0, M_PAD) = Xh, [M_PAD, 2 M_PAD) = Xl
-                        const uint32_t a_hi = ta + kk * (UMMA_K / 2), a_lo = a_hi + 32;
-                        if (DUAL) {
-                            if (lo_thread) umma_f16_ts(d_tmem, a_lo, b_x, idesc1, (j | kk) != 0u);
-                            else umma_f16_ts(d_tmem, a_hi, b_x, idesc2, (j | kk) != 0u);
-                        } else {
-                            umma_f16_ts(d_tmem, a_hi, b_x, idesc2, (j | kk) != 0u);
-                            umma_f16_ts(d_tmem, a_lo, b_x, idesc1, 1u);
-                        }
-                    }
-                    umma_commit(&done[bs]);  // this thread's share of sub-block done: operand stage and activation slot
-                    if (++as == AST) as = 0, ph ^= 1u;
-                    if (++bs == BS) bs = 0;
-                }
-                if (ok) umma_commit(&t_full[tb]);
-                pos += kb_end - kb_begin;
-                ++seg;
+        // The two roles are separate instantiations: with both products under a run-time condition in one loop the
+        // compiler predicated them, and a predicated-off tcgen05.mma still costs its ~70-90 cycles in the issue slot.
+        if (lane == 0) {
+            Q80Smem sm = {s_raw, raw_full, raw_empty, a_full, done, t_full, t_empty, abort_flag};
+            if (!dual_issue(M_PAD)) {
+                if (warp == 1) q80_issuer<M_PAD, 0>(a, sm, tmem_base, smem_u32(s_b), u0, u1);
+            } else if (warp == 1) {
+                q80_issuer<M_PAD, 1>(a, sm, tmem_base, smem_u32(s_b), u0, u1);
+            } else {
+                q80_issuer<M_PAD, 2>(a, sm, tmem_base, smem_u32(s_b), u0, u1);
             }
-            if (!ok) *abort_flag = 1;
         }
     } else {
         // ---------------- workers: warps 4..19; TMEM lane group = warp % 4, k quarter of a raw stage = (warp - 4) / 4
