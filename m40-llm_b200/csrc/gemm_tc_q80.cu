@@ -214,6 +214,25 @@ __device__ __forceinline__ void q80_issuer(const Q80Args& a, const Q80Smem& sm, 
     bool ok = true;
     uint32_t pos = u0, seg = 0, as = 0, ph = 0, bs = 0;
     const uint32_t a_tmem0 = tmem_base + A_COL0;
+    // Everything the loop needs per sub-block is carried as a running value (barrier addresses, the operand's
+    // tensor-memory column, the activation descriptor, whose address field counts 16-byte units): the thread's few
+    // dozen dependent instructions per sub-block are what this kernel waits for.
+    const uint64_t b_desc0 = make_desc_sw128(b_smem0);
+    const uint32_t a_full0 = smem_u32(sm.a_full), done0 = smem_u32(sm.done);
+    uint32_t a_bar = a_full0, d_bar = done0, ta = a_tmem0 + (ROLE == 2 ? 32u : 0u);
+    uint64_t b_x = b_desc0;
+    auto wait_bar = [](uint32_t addr, uint32_t parity) {
+        for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+            uint32_t done;
+            asm volatile(
+                "{\n\t.reg .pred p;\n\t"
+                "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+                "selp.u32 %0, 1, 0, p;\n\t}"
+                : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+            if (done) return true;
+        }
+        return false;
+    };
     while (pos < u1 && ok) {
         const uint32_t kb_begin = pos % a.units_per_tile;
         uint32_t kb_end = kb_begin + (u1 - pos);
@@ -223,25 +242,29 @@ __device__ __forceinline__ void q80_issuer(const Q80Args& a, const Q80Smem& sm, 
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + (ROLE == 2 ? acc_lo_col(M_PAD, tb) : acc_hi_col(M_PAD, tb));
         const uint32_t n_sub = (kb_end - kb_begin) * 4;
-        for (uint32_t j = 0; j < n_sub && ok; ++j) {
-            if (!mbar_wait(&sm.a_full[as], ph)) { ok = false; break; }
+        uint32_t acc = 0u;  // 0 only for the first MMA of the segment
+        for (uint32_t j = 0; j < n_sub; ++j) {
+            if (!wait_bar(a_bar, ph)) { ok = false; break; }
             tc_fence_after();
-            const uint32_t ta = a_tmem0 + as * A_COLS;  // hi columns [0,32), lo columns [32,64)
-            const uint32_t sb = b_smem0 + bs * 2 * B_BYTES;
 #pragma unroll
             for (uint32_t kk = 0; kk < BLOCK_K / UMMA_K; ++kk) {
-                const uint64_t b_x = make_desc_sw128(sb + kk * UMMA_K * 2);  // rows [0, M_PAD) = Xh, [M_PAD, 2 M_PAD) = Xl
-                const uint32_t a_hi = ta + kk * (UMMA_K / 2), a_lo = a_hi + 32;
+                // rows [0, M_PAD) of the activation tile = Xh, [M_PAD, 2 M_PAD) = Xl
+                const uint64_t b_k = b_x + (uint64_t)((kk * UMMA_K * 2) >> 4);
+                const uint32_t a_k = ta + kk * (UMMA_K / 2);  // hi columns [0,32), lo columns [32,64) of the stage
                 if (ROLE == 2) {
-                    umma_f16_ts(d_tmem, a_lo, b_x, idesc1, (j | kk) != 0u);
+                    umma_f16_ts(d_tmem, a_k, b_k, idesc1, acc | kk);
                 } else {
-                    umma_f16_ts(d_tmem, a_hi, b_x, idesc2, (j | kk) != 0u);
-                    if (ROLE == 0) umma_f16_ts(d_tmem, a_lo, b_x, idesc1, 1u);
+                    umma_f16_ts(d_tmem, a_k, b_k, idesc2, acc | kk);
+                    if (ROLE == 0) umma_f16_ts(d_tmem, a_k + 32, b_k, idesc1, 1u);
                 }
             }
-            umma_commit(&sm.done[bs]);  // this thread's share of sub-block done: operand stage and activation slot
-            if (++as == AST) as = 0, ph ^= 1u;
-            if (++bs == BS) bs = 0;
+            acc = 1u;
+            asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(d_bar) : "memory");
+            // this thread's share of sub-block done: operand stage and activation slot
+            ++as, a_bar += 8u, ta += A_COLS;
+            if (as == AST) as = 0, ph ^= 1u, a_bar = a_full0, ta -= AST * A_COLS;
+            ++bs, d_bar += 8u, b_x += (uint64_t)((2 * B_BYTES) >> 4);
+            if (bs == BS) bs = 0, d_bar = done0, b_x = b_desc0;
         }
         if (ok) umma_commit(&sm.t_full[tb]);
         pos += kb_end - kb_begin;
