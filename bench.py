@@ -9,7 +9,8 @@ output projection + residual, norm, Q8_0 SwiGLU FFN + residual): 32 tokens advan
 
 `value`   tokens/s with inputs resident in HBM, the layer replayed as one CUDA graph on the decode stream.
 `e2e`     the same metric through the C ABI with HOST buffers: per step the activations and the batch plan are
-          copied from pinned host memory, the layer runs, the result is copied back.
+          copied from pinned host memory, the layer runs, the result is copied back; two steps in flight (the next
+          step's upload and the previous step's download overlap the compute), the one-call-at-a-time figure beside it.
 `roofline` the dominant kernel (batched decode attention): algorithmic bytes / CUDA-event duration vs the
           measured HBM copy bandwidth.
 `cpu_baseline` the oracle (CPU restatement of the reference math) timed on this box's host cores on a bounded
@@ -872,18 +873,52 @@ def main():
     for i in range(args.steps * e2e_blocks):
         e2e_step(i)
     nat.sync()
+    e2e_sync_s = (time.perf_counter() - t0) / (args.steps * e2e_blocks)
+    # The same call in its two halves with TWO steps in flight (the host layer driver's begin / end): step i + 1's
+    # upload and step i's download ride the prefill stream while the decode stream computes; every step still copies
+    # its inputs in and its result out inside the timed region.
+    hout2 = [torch.empty((B, H), dtype=torch.float32).pin_memory() for _ in range(2)]
+
+    def e2e_begin(i):
+        rc = hl.forward_host_begin_raw(i % 2, kv, hw[i % N_WEIGHT_SETS], kvcfg, B, vp(rid), vp(sid), vp(kvl), vp(act),
+                                       C.c_void_p(hx.data_ptr()), True)
+        assert rc == 0, (rc, host.last_error())
+
+    def e2e_end(i):
+        rc = hl.forward_host_end_raw(i % 2, C.c_void_p(hout2[i % 2].data_ptr()))
+        assert rc == 0, (rc, host.last_error())
+
+    def e2e_pipelined(n):
+        e2e_begin(0)
+        for i in range(n):
+            if i + 1 < n:
+                e2e_begin(i + 1)
+            e2e_end(i)
+
+    e2e_pipelined(max(args.warmup, 2 * N_WEIGHT_SETS) + 2)
+    barrier()
+    t0 = time.perf_counter()
+    e2e_pipelined(args.steps * e2e_blocks)
+    nat.sync()
     e2e_s = (time.perf_counter() - t0) / (args.steps * e2e_blocks)
     e2e_replays = hl.graph_replays()
     # the end-to-end call's result is the layer's: one more (untimed) call on weight set 0, the set whose eager step
     # the launch count above left in the device-resident output buffer
     e2e_step(0)
     e2e_err = float(np.max(np.abs(hout.numpy() - layer.dout.download(np.float32, (B, H)))))
+    # and the two-in-flight form returns the same bytes as the one-call form (weight set 0 in both slots)
+    for slot in range(2):
+        assert hl.forward_host_begin_raw(slot, kv, hw[0], kvcfg, B, vp(rid), vp(sid), vp(kvl), vp(act),
+                                         C.c_void_p(hx.data_ptr()), True) == 0
+    for slot in range(2):
+        assert hl.forward_host_end_raw(slot, C.c_void_p(hout2[slot].data_ptr())) == 0
+        e2e_err = max(e2e_err, float(np.max(np.abs(hout2[slot].numpy() - hout.numpy()))))
 
     per_rank = None
     if dist is not None:
-        t = torch.tensor([ms_step, e2e_s], device="cuda", dtype=torch.float64)
+        t = torch.tensor([ms_step, e2e_s, e2e_sync_s], device="cuda", dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms_step, e2e_s = float(t[0]), float(t[1])
+        ms_step, e2e_s, e2e_sync_s = float(t[0]), float(t[1]), float(t[2])
         mine_t = torch.tensor([ms_step_local, float(att_lens.sum()), attn_ms], device="cuda", dtype=torch.float64)
         allr = [torch.zeros_like(mine_t) for _ in range(world)]
         dist.all_gather(allr, mine_t)
@@ -1068,6 +1103,7 @@ def main():
                          "launches_timed": reps,
                          "traffic": None if NCU_TRAFFIC_RATIO is None else NCU_TRAFFIC_RATIO * attn_bytes},
             "e2e": {"value": world * B / e2e_s, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "in_flight": 2, "one_call_at_a_time": world * B / e2e_sync_s,
                     "graph_replays": e2e_replays, "timed_steps": args.steps * e2e_blocks,
                     "max_abs_diff_vs_device_resident_step": e2e_err},
             "gpu_launches": per_step_launches * args.steps * blocks,

@@ -88,6 +88,12 @@ int m40llm_cuda_event_record(M40llmCudaContext* ctx, M40llmCudaEvent* event, uin
 int m40llm_cuda_event_elapsed_sync(M40llmCudaContext* ctx, M40llmCudaEvent* start, M40llmCudaEvent* stop,
                                    float* elapsed_ms);
 void m40llm_cuda_event_destroy(M40llmCudaEvent* event);
+/* Additive (no counterpart in cuda/kernels.cu): make a stream wait for a recorded event, and block the host on one.
+ * With them a caller can keep two steps in flight: the next step's host-to-device copies on the prefill stream while
+ * the decode stream computes, and a step's result copied back while the next one runs. 0, or -1 null argument,
+ * -2 device, -3 / -4 the CUDA call failed. */
+int m40llm_stream_wait_event(M40llmCudaContext* ctx, uint32_t waiting_stream_kind, M40llmCudaEvent* event);
+int m40llm_cuda_event_synchronize(M40llmCudaContext* ctx, M40llmCudaEvent* event);
 
 /* ---------------------------------------------------- elementwise (decode stream) */
 /* cuda/kernels.cu:1049-1068 (kernel 736-768); sync form 1035-1047 */

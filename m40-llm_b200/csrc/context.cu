@@ -398,6 +398,20 @@ int m40llm_cuda_event_record(M40llmCudaContext* ctx, M40llmCudaEvent* event, uin
     return cudaEventRecord(event->event, s) == cudaSuccess ? 0 : -4;
 }
 
+int m40llm_stream_wait_event(M40llmCudaContext* ctx, uint32_t waiting_stream_kind, M40llmCudaEvent* event) {
+    if (!ctx || !event || !event->event) return -1;
+    if (m40_ensure_device(ctx) != 0) return -2;
+    cudaStream_t s = m40_stream(ctx, waiting_stream_kind);
+    if (!s) return -3;
+    return cudaStreamWaitEvent(s, event->event, 0) == cudaSuccess ? 0 : -4;
+}
+
+int m40llm_cuda_event_synchronize(M40llmCudaContext* ctx, M40llmCudaEvent* event) {
+    if (!ctx || !event || !event->event) return -1;
+    if (m40_ensure_device(ctx) != 0) return -2;
+    return cudaEventSynchronize(event->event) == cudaSuccess ? 0 : -3;
+}
+
 int m40llm_cuda_event_elapsed_sync(M40llmCudaContext* ctx, M40llmCudaEvent* start, M40llmCudaEvent* stop,
                                    float* elapsed_ms) {
     if (!ctx || !start || !stop || !start->event || !stop->event || !elapsed_ms) return -1;

@@ -51,6 +51,9 @@ def lib() -> C.CDLL:
         L.m40host_layer_destroy.argtypes = [C.c_void_p]
         L.m40host_layer_forward_host.argtypes = [C.c_void_p, C.c_void_p, C.POINTER(Weights), C.POINTER(KvCfg), C.c_uint32] + \
             [C.c_void_p] * 6 + [C.c_uint32]
+        L.m40host_layer_forward_host_begin.argtypes = [C.c_void_p, C.c_uint32, C.c_void_p, C.POINTER(Weights),
+                                                       C.POINTER(KvCfg), C.c_uint32] + [C.c_void_p] * 5 + [C.c_uint32]
+        L.m40host_layer_forward_host_end.argtypes = [C.c_void_p, C.c_uint32, C.c_void_p]
         L.m40host_layer_graph_replays.restype = C.c_uint64
         L.m40host_layer_graph_replays.argtypes = [C.c_void_p]
         L.m40host_plan_from_requests.argtypes = [C.c_uint32] + [C.c_void_p] * 8
@@ -134,6 +137,16 @@ class DecodeLayer:
     def forward_host_raw(self, kv, weights, kvcfg, n, rid_p, sid_p, kvl_p, act_p, x_p, out_p, use_graph=True) -> int:
         return lib().m40host_layer_forward_host(self.handle, kv, C.byref(weights), C.byref(kvcfg), n, rid_p, sid_p, kvl_p,
                                                 act_p, x_p, out_p, 1 if use_graph else 0)
+
+    def forward_host_begin_raw(self, slot, kv, weights, kvcfg, n, rid_p, sid_p, kvl_p, act_p, x_p, use_graph=True) -> int:
+        """First half of forward_host for slot 0 or 1: uploads on the prefill stream, enqueues the layer on the decode
+        stream. Two slots may be in flight; end a slot before beginning it again."""
+        return lib().m40host_layer_forward_host_begin(self.handle, slot, kv, C.byref(weights), C.byref(kvcfg), n, rid_p, sid_p,
+                                                      kvl_p, act_p, x_p, 1 if use_graph else 0)
+
+    def forward_host_end_raw(self, slot, out_p) -> int:
+        """Second half: copies the slot's result to `out_p` (host) and returns when it has arrived."""
+        return lib().m40host_layer_forward_host_end(self.handle, slot, out_p)
 
     def graph_replays(self) -> int:
         return int(lib().m40host_layer_graph_replays(self.handle))

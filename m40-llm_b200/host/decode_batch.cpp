@@ -46,7 +46,7 @@ CudaDecodeBatchPlan::~CudaDecodeBatchPlan() {
 
 // One stream-ordered copy of [ids | lens | positions] onto the decode stream: the kernels that read the plan are
 // enqueued behind it on the same stream, so no host synchronisation is needed here.
-int CudaDecodeBatchPlan::upload(M40llmCudaContext* ctx, const DecodeBatchPlan& plan) {
+int CudaDecodeBatchPlan::upload(M40llmCudaContext* ctx, const DecodeBatchPlan& plan, uint32_t stream_kind, bool sync_first) {
     const uint32_t n = plan.batch_size();
     if (n > capacity_ || ctx != ctx_) {
         if (ctx_) {
@@ -63,7 +63,7 @@ int CudaDecodeBatchPlan::upload(M40llmCudaContext* ctx, const DecodeBatchPlan& p
     d_lens_ = d_ids_ + capacity_;
     d_pos_ = d_ids_ + 2 * (size_t)capacity_;
     // the previous copy out of the staging vector must have left it before it is overwritten
-    int rc = m40llm_stream_synchronize(ctx, 1u);
+    int rc = sync_first ? m40llm_stream_synchronize(ctx, stream_kind) : 0;
     if (rc != 0) return rc;
     staging_.assign((size_t)3 * capacity_, 0u);
     const std::vector<uint32_t> ids = plan.sequence_ids(), lens = plan.sequence_lens();
@@ -72,7 +72,7 @@ int CudaDecodeBatchPlan::upload(M40llmCudaContext* ctx, const DecodeBatchPlan& p
         staging_[capacity_ + i] = lens[i];
         staging_[2 * (size_t)capacity_ + i] = lens[i] - 1;
     }
-    if ((rc = m40llm_memcpy_h2d_async(ctx, d_ids_, staging_.data(), staging_.size() * 4, 1u)) != 0) return rc;
+    if ((rc = m40llm_memcpy_h2d_async(ctx, d_ids_, staging_.data(), staging_.size() * 4, stream_kind)) != 0) return rc;
     batch_ = n;
     return 0;
 }

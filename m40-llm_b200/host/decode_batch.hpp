@@ -48,7 +48,10 @@ public:
     ~CudaDecodeBatchPlan();
     CudaDecodeBatchPlan(const CudaDecodeBatchPlan&) = delete;
     CudaDecodeBatchPlan& operator=(const CudaDecodeBatchPlan&) = delete;
-    int upload(M40llmCudaContext* ctx, const DecodeBatchPlan& plan);  // 0 or the failing ABI return code
+    // 0 or the failing ABI return code. The copy rides `stream_kind` (1 = decode, 0 = prefill). The staging vector is
+    // pageable, so the copy has left it when the call returns; `sync_first` additionally drains that stream before the
+    // device block is rewritten (needed when kernels of an earlier step may still read it).
+    int upload(M40llmCudaContext* ctx, const DecodeBatchPlan& plan, uint32_t stream_kind = 1u, bool sync_first = true);
     const uint32_t* d_sequence_ids() const { return d_ids_; }
     const uint32_t* d_sequence_lens() const { return d_lens_; }
     const uint32_t* d_positions() const { return d_pos_; }

@@ -20,8 +20,15 @@ DecodeLayer::~DecodeLayer() {
     if (!ctx_) return;
     m40llm_stream_synchronize(ctx_, 1);
     for (auto& g : graphs_) m40llm_cuda_graph_destroy(g.exec);
-    void* bufs[] = {d_q_, d_att_, d_x1_, d_x1n_, d_hid_, d_xin_, d_xout_};
-    for (void* b : bufs) m40llm_device_free(ctx_, b);
+    m40llm_stream_synchronize(ctx_, 0);
+    void* bufs[] = {d_q_, d_att_, d_x1_, d_x1n_, d_hid_, d_xin_, d_xout_, slots_[0].d_xin, slots_[0].d_xout,
+                    slots_[1].d_xin, slots_[1].d_xout};
+    for (void* b : bufs)
+        if (b) m40llm_device_free(ctx_, b);
+    for (Slot& sl : slots_) {
+        if (sl.computed) m40llm_cuda_event_destroy(sl.computed);
+        if (sl.arrived) m40llm_cuda_event_destroy(sl.arrived);
+    }
 }
 
 int DecodeLayer::fail(int rc, const char* step) {
@@ -122,6 +129,61 @@ int DecodeLayer::forward_host(M40llmKVCache* kv, const LayerWeights& w, const Kv
     if ((rc = forward_device(kv, w, kvcfg, plan, host_plan_dev_, d_xin_, d_xout_, use_graph)) != 0) return rc;
     if ((rc = m40llm_memcpy_d2h_async(ctx_, out_host, d_xout_, bytes, 1u)) != 0) return fail(rc, "memcpy_d2h");
     if ((rc = m40llm_stream_synchronize(ctx_, 1u)) != 0) return fail(rc, "stream_synchronize");
+    return 0;
+}
+
+// staging buffers and events of a slot, made at its first use
+int DecodeLayer::slot_ready(uint32_t slot) {
+    Slot& sl = slots_[slot];
+    if (sl.d_xin) return 0;
+    const size_t bytes = (size_t)max_rows_ * cfg_.hidden * 4;
+    int rc;
+    if ((rc = m40llm_device_malloc(ctx_, bytes, &sl.d_xin)) != 0) return rc;
+    if ((rc = m40llm_device_malloc(ctx_, bytes, &sl.d_xout)) != 0) return rc;
+    if ((rc = m40llm_cuda_event_create(ctx_, &sl.computed)) != 0) return rc;
+    return m40llm_cuda_event_create(ctx_, &sl.arrived);
+}
+
+int DecodeLayer::forward_host_begin(uint32_t slot, M40llmKVCache* kv, const LayerWeights& w,
+                                    const KvCompressionConfig& kvcfg, const std::vector<DecodeRequestState>& requests,
+                                    const float* x_host, bool use_graph) {
+    if (!ok_) return fail(-1, "workspace");
+    if (slot > 1) return fail(-2, "slot");
+    Slot& sl = slots_[slot];
+    if (sl.busy) return fail(-2, "slot_busy");
+    DecodeBatchPlan plan;
+    const std::string err = DecodeBatchPlan::from_requests(requests, &plan);
+    if (!err.empty()) {
+        failed_step_ = err;
+        return -4;
+    }
+    const uint32_t rows = plan.batch_size();
+    if (rows > max_rows_) return fail(-2, "rows");
+    int rc = slot_ready(slot);
+    if (rc != 0) return fail(rc, "slot_alloc");
+    // the slot's previous step has been ended (its result arrived), so nothing reads its plan or staging any more
+    if ((rc = sl.plan.upload(ctx_, plan, 0u, false)) != 0) return fail(rc, "plan_upload");
+    const size_t bytes = (size_t)rows * cfg_.hidden * 4;
+    if ((rc = m40llm_memcpy_h2d_async(ctx_, sl.d_xin, x_host, bytes, 0u)) != 0) return fail(rc, "memcpy_h2d");
+    if ((rc = m40llm_stream_wait_for_stream(ctx_, 1u, 0u)) != 0) return fail(rc, "stream_wait_for_stream");
+    if ((rc = forward_device(kv, w, kvcfg, plan, sl.plan, sl.d_xin, sl.d_xout, use_graph)) != 0) return rc;
+    if ((rc = m40llm_cuda_event_record(ctx_, sl.computed, 1u)) != 0) return fail(rc, "event_record");
+    sl.rows = rows;
+    sl.busy = true;
+    return 0;
+}
+
+int DecodeLayer::forward_host_end(uint32_t slot, float* out_host) {
+    if (!ok_) return fail(-1, "workspace");
+    if (slot > 1 || !slots_[slot].busy) return fail(-2, "slot");
+    Slot& sl = slots_[slot];
+    sl.busy = false;
+    int rc;
+    if ((rc = m40llm_stream_wait_event(ctx_, 0u, sl.computed)) != 0) return fail(rc, "stream_wait_event");
+    if ((rc = m40llm_memcpy_d2h_async(ctx_, out_host, sl.d_xout, (size_t)sl.rows * cfg_.hidden * 4, 0u)) != 0)
+        return fail(rc, "memcpy_d2h");
+    if ((rc = m40llm_cuda_event_record(ctx_, sl.arrived, 0u)) != 0) return fail(rc, "event_record");
+    if ((rc = m40llm_cuda_event_synchronize(ctx_, sl.arrived)) != 0) return fail(rc, "event_synchronize");
     return 0;
 }
 

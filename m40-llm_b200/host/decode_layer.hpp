@@ -55,6 +55,15 @@ public:
     int forward_host(M40llmKVCache* kv, const LayerWeights& w, const KvCompressionConfig& kvcfg,
                      const std::vector<DecodeRequestState>& requests, const float* x_host, float* out_host,
                      bool use_graph);
+    // The same call in two halves, for two steps in flight (slot 0 or 1, each with its own staging buffers and plan):
+    // `begin` copies the plan and x on the PREFILL stream, makes the decode stream wait for them and enqueues the layer;
+    // `end` copies the slot's result back on the prefill stream behind the layer and blocks until it has arrived. A
+    // caller that begins step i + 1 before it ends step i overlaps i + 1's upload and i's download with the compute
+    // of the other step; the layer kernels themselves stay in order on the decode stream. A slot must be ended before
+    // it is begun again.
+    int forward_host_begin(uint32_t slot, M40llmKVCache* kv, const LayerWeights& w, const KvCompressionConfig& kvcfg,
+                           const std::vector<DecodeRequestState>& requests, const float* x_host, bool use_graph);
+    int forward_host_end(uint32_t slot, float* out_host);
     const std::string& failed_step() const { return failed_step_; }
     uint64_t graph_replays() const { return graph_replays_; }
 
@@ -78,6 +87,14 @@ private:
     void *d_q_ = nullptr, *d_att_ = nullptr, *d_x1_ = nullptr, *d_x1n_ = nullptr, *d_hid_ = nullptr;
     void *d_xin_ = nullptr, *d_xout_ = nullptr;  // staging for forward_host
     CudaDecodeBatchPlan host_plan_dev_;
+    struct Slot {
+        void *d_xin = nullptr, *d_xout = nullptr;
+        CudaDecodeBatchPlan plan;
+        M40llmCudaEvent *computed = nullptr, *arrived = nullptr;
+        uint32_t rows = 0;
+        bool busy = false;
+    } slots_[2];
+    int slot_ready(uint32_t slot);
     std::vector<GraphEntry> graphs_;
     std::string failed_step_;
     uint64_t graph_replays_ = 0;

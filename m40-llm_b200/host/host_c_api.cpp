@@ -109,6 +109,29 @@ int m40host_layer_forward_host(void* layer, M40llmKVCache* kv, const m40host_wei
     return rc;
 }
 
+// The same call in two halves (two steps in flight, slot 0 or 1): see DecodeLayer::forward_host_begin / _end.
+int m40host_layer_forward_host_begin(void* layer, uint32_t slot, M40llmKVCache* kv, const m40host_weights* w,
+                                     const m40host_kv_cfg* kc, uint32_t n, const uint64_t* request_ids,
+                                     const uint32_t* sequence_ids, const uint32_t* kv_lens, const uint32_t* active,
+                                     const float* x_host, uint32_t use_graph) {
+    DecodeLayer* l = (DecodeLayer*)layer;
+    LayerWeights lw;
+    lw.attn_norm = w->attn_norm; lw.ffn_norm = w->ffn_norm; lw.wq = w->wq; lw.wk = w->wk; lw.wv = w->wv; lw.wo = w->wo;
+    lw.bq = w->bq; lw.bk = w->bk; lw.bv = w->bv; lw.wg = w->wg; lw.wu = w->wu; lw.wd = w->wd; lw.ffn_q80 = w->ffn_q80 != 0;
+    std::vector<DecodeRequestState> r;
+    for (uint32_t i = 0; i < n; ++i) r.push_back({request_ids[i], sequence_ids[i], kv_lens[i], active[i] != 0});
+    const int rc = l->forward_host_begin(slot, kv, lw, to_cfg(kc), r, x_host, use_graph != 0);
+    if (rc != 0) g_err = l->failed_step();
+    return rc;
+}
+
+int m40host_layer_forward_host_end(void* layer, uint32_t slot, float* out_host) {
+    DecodeLayer* l = (DecodeLayer*)layer;
+    const int rc = l->forward_host_end(slot, out_host);
+    if (rc != 0) g_err = l->failed_step();
+    return rc;
+}
+
 uint64_t m40host_layer_graph_replays(void* layer) { return ((DecodeLayer*)layer)->graph_replays(); }
 
 

@@ -219,6 +219,57 @@ def test_host_layer_driver_dense_with_graph_replay(nat, O, pkg):
     nat.free_all()
 
 
+def test_host_layer_driver_two_steps_in_flight(nat, O, pkg):
+    """forward_host in its two halves: two micro-batches (sequences 0-1 and 2-3 of one cache) ping-pong through the
+    two slots, each begun before the other is ended; three steps each, checked against the oracle layer."""
+    rng = np.random.default_rng(15)
+    H, qh, kvh, hd, F = 512, 8, 2, 64, 1024
+    cfg = O.LayerCfg(H, qh, kvh, hd, F, 1, 0, 1e-5, 1e4, 1.0)
+    w = make_weights(O, rng, H, qh, kvh, hd, F, True, False)
+    W = _host_weights(pkg, nat, w, True)
+    lens = [33, 90, 12, 140]
+    max_seq = 160
+    kv = nat.kv_dense(max_seq, 4, kvh, hd)
+    Ks = [np.zeros((max_seq, kvh, hd), np.float16) for _ in lens]
+    Vs = [np.zeros((max_seq, kvh, hd), np.float16) for _ in lens]
+    for b, n in enumerate(lens):
+        Ks[b][:n] = rng.standard_normal((n, kvh, hd)).astype(np.float16)
+        Vs[b][:n] = rng.standard_normal((n, kvh, hd)).astype(np.float16)
+        nat.kv_fill(kv, b, Ks[b][:n], Vs[b][:n])
+    layer = pkg.host.DecodeLayer(nat.ctx, pkg.host.LayerCfg(H, qh, kvh, hd, F, 0, 1e-5, 1e4, 1.0), 8)
+    kc = pkg.host.dense_kv_cfg()
+    groups = [[0, 1], [2, 3]]
+    xs = [np.ascontiguousarray(rng.standard_normal((2, H)).astype(np.float32)) for _ in groups]
+    outs = [np.zeros((2, H), np.float32) for _ in groups]
+    p = lambda a: a.ctypes.data_as(C.c_void_p)
+
+    def begin(slot, step):
+        seqs = groups[slot]
+        rid = np.array([100 + b for b in seqs], np.uint64)
+        sid = np.array(seqs, np.uint32)
+        kvl = np.array([lens[b] + step + 1 for b in seqs], np.uint32)
+        act = np.ones(2, np.uint32)
+        return layer.forward_host_begin_raw(slot, kv, W, kc, 2, p(rid), p(sid), p(kvl), p(act), p(xs[slot]), True)
+
+    assert begin(0, 0) == 0
+    # a busy slot cannot be begun again, and an idle one cannot be ended
+    assert begin(0, 0) != 0
+    assert layer.forward_host_end_raw(1, p(outs[1])) != 0
+    for step in range(3):
+        assert begin(1, step) == 0
+        for slot in (0, 1):
+            assert layer.forward_host_end_raw(slot, p(outs[slot])) == 0
+            for i, b in enumerate(groups[slot]):
+                eout, _, _ = O.decode_layer(cfg, xs[slot][i], w, Ks[b], Vs[b], lens[b] + step)
+                assert_close(outs[slot][i], eout, what=f"step {step} slot {slot} sequence {b}")
+            xs[slot][:] = outs[slot]
+            if slot == 0 and step + 1 < 3:
+                assert begin(0, step + 1) == 0
+    layer.close()
+    nat.lib.m40llm_kvcache_destroy(kv)
+    nat.free_all()
+
+
 def test_host_layer_driver_compressed_mode(nat, O, pkg):
     """Attention-mode dispatch (src/infer/kv.rs:433-765): BlockSelectExact + FP16-K/q4-V direct on a compressed cache,
     Qwen-style heads (NeoX RoPE, QKV bias). The layer appends through the ring (with eviction) and attends."""
