@@ -295,23 +295,30 @@ __global__ void __launch_bounds__(256) gemm_tc_epilogue_kernel(EpiArgs e) {
     float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f}, up[4] = {0.0f, 0.0f, 0.0f, 0.0f};
     const size_t col = (size_t)e.tile_begin[p] * BLOCK_N + n;
     const size_t col_u = (size_t)e.tile_begin[1] * BLOCK_N + n;
-    for (uint32_t sbase = 0; sbase < e.k_splits; sbase += 4u) {
+    // Every load is unconditional (row and split index clamped, the value masked afterwards): guarded loads were
+    // issued one at a time, each waiting for the previous one's trip to L2.
+    const uint32_t M = e.M, ks = e.k_splits;
+    const size_t n_total = e.n_total;
+    const float* __restrict__ part = e.partial;
+    const bool gate_up = e.mode == 1;
+    for (uint32_t sbase = 0; sbase < ks; sbase += 4u) {
         float v[4][4], w[4][4];
 #pragma unroll
         for (int i = 0; i < 4; ++i)
 #pragma unroll
             for (int k = 0; k < 4; ++k) {
-                const uint32_t m = m0 + 2u * i, sp = sbase + k;
-                const bool live = m < e.M && sp < e.k_splits;
-                v[i][k] = live ? e.partial[sp * split_stride + (size_t)m * e.n_total + col] : 0.0f;
-                w[i][k] = (live && e.mode == 1) ? e.partial[sp * split_stride + (size_t)m * e.n_total + col_u] : 0.0f;
+                const uint32_t m = min(m0 + 2u * i, M - 1u), sp = min(sbase + k, ks - 1u);
+                const size_t at = sp * split_stride + (size_t)m * n_total;
+                v[i][k] = part[at + col];
+                w[i][k] = gate_up ? part[at + col_u] : 0.0f;
             }
 #pragma unroll
         for (int i = 0; i < 4; ++i)
 #pragma unroll
             for (int k = 0; k < 4; ++k) {
-                acc[i] += v[i][k];
-                up[i] += w[i][k];
+                const bool live = sbase + k < ks;
+                acc[i] += live ? v[i][k] : 0.0f;
+                up[i] += live ? w[i][k] : 0.0f;
             }
     }
 #pragma unroll

@@ -442,29 +442,37 @@ __global__ void __launch_bounds__(256) gemm_tc_q80_epilogue_kernel(Q80EpiArgs e)
     if (threadIdx.x == 32 && e.mode == 1) q80_tile_ctas(e, e.tile_begin[1] + t, &first[1], &count[1], &seg0[1]);
     __syncthreads();
     if (n >= e.N[p]) return;
-    // a thread owns 4 activation rows; every partial of a tile is loaded before any is added (fixed order)
+    // A thread owns 4 activation rows. Every load of a round is unconditional (row and partial index clamped, the value
+    // masked afterwards) and issued before any is added: guarded loads were issued one at a time, each waiting for
+    // the previous one's trip to L2. The adds keep a fixed order.
     const uint32_t m0 = blockIdx.y * 8u + (threadIdx.x >> 7);
+    const uint32_t M = e.M, seg_max = e.seg_max;
+    const float* __restrict__ part = e.partial + tr;
     float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f}, up[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-    const int nw = e.mode == 1 ? 2 : 1;
-    for (int w = 0; w < nw; ++w) {
-        for (uint32_t i0 = 0; i0 < count[w]; i0 += 4u) {
-            float v[4][4];
+    const uint32_t c0 = count[0], c1 = e.mode == 1 ? count[1] : 0u;
+    const uint32_t cmax = c0 > c1 ? c0 : c1;
+    for (uint32_t i0 = 0; i0 < cmax; i0 += 4u) {
+        float v[2][4][4];
+#pragma unroll
+        for (int w = 0; w < 2; ++w) {
+            const uint32_t cw = w == 0 ? c0 : c1;
+            if (w == 1 && c1 == 0u) break;
 #pragma unroll
             for (int r = 0; r < 4; ++r)
 #pragma unroll
                 for (int k = 0; k < 4; ++k) {
-                    const uint32_t m = m0 + 2u * r, i = i0 + k;
-                    const size_t slot = (size_t)(first[w] + i) * e.seg_max + (i == 0 ? seg0[w] : 0u);
-                    v[r][k] = (m < e.M && i < count[w]) ? e.partial[(slot * e.M + m) * BLOCK_N + tr] : 0.0f;
-                }
-#pragma unroll
-            for (int r = 0; r < 4; ++r)
-#pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    if (w == 0) acc[r] += v[r][k];
-                    else up[r] += v[r][k];
+                    const uint32_t m = min(m0 + 2u * r, M - 1u), i = min(i0 + k, cw - 1u);
+                    const size_t slot = (size_t)(first[w] + i) * seg_max + (i == 0 ? seg0[w] : 0u);
+                    v[w][r][k] = part[(slot * M + m) * BLOCK_N];
                 }
         }
+#pragma unroll
+        for (int r = 0; r < 4; ++r)
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                acc[r] += (i0 + k < c0) ? v[0][r][k] : 0.0f;
+                if (c1 != 0u) up[r] += (i0 + k < c1) ? v[1][r][k] : 0.0f;
+            }
     }
 #pragma unroll
     for (int r = 0; r < 4; ++r) {
