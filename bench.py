@@ -639,7 +639,7 @@ def prefill_case(nat, ev, reps=10):
         b.free()
     return {"prompt_tokens": total, "sequences": [int(n) for n in lens], "ms_per_call": ms, "prompt_tokens_per_s": total / (ms * 1e-3),
             "algorithmic_tflops": tf, "frac_of_bf16_tensor_peak": tf / peak_tf,
-            "note": "mma.sync (legacy tensor path) flash-attention kernel, f32 inputs rounded to f16 tiles in shared memory; "
+            "note": "mma.sync (legacy tensor path) flash-attention kernel over f16 copies of K / V made by a pack pass of the same call; "
                     "the call also reads the lengths back to the host as the reference does"}
 
 
@@ -692,6 +692,8 @@ def main():
                     help="small case for a profiler: the layer chain at ROWS rows, context 7969")
     ap.add_argument("--compressed-only", action="store_true",
                     help="small case for a profiler: the 32K compressed attention call alone")
+    ap.add_argument("--prefill-only", action="store_true",
+                    help="small case for a profiler: the packed varlen prefill attention call alone")
     ap.add_argument("--workload", default="layer", choices=["layer", "splitk"],
                     help="layer: the batched decode layer (the contract's line); splitk: one 32K sequence, split-K over "
                          "the ranks (its own JSON line)")
@@ -730,6 +732,10 @@ def main():
     if args.compressed_only:
         print(json.dumps({"case": "compressed32k", **compressed_case(nat, Events(nat), peak, calls=4, reps=max(args.steps, 1))}),
               flush=True)
+        return
+
+    if args.prefill_only:
+        print(json.dumps({"case": "prefill_varlen", **prefill_case(nat, Events(nat), reps=max(args.steps, 1))}), flush=True)
         return
 
     if args.workload == "splitk":

@@ -5,11 +5,12 @@
 // [total_kv][kv_heads][hd]; q row i attends kv rows 0 .. kv_len - q_len + i; softmax scaled by 1/sqrt(hd); the
 // reference runs one CTA per (q row, head) with a three-pass softmax in f32.
 //
-// Here one CTA owns 64 q rows of one (sequence, q head) and walks the kv rows it may see in 64-row tiles, flash
-// attention style: K and V tiles are rounded to f16 on their way into XOR-swizzled shared memory, S = Q K^T and
-// O += P V run on mma.sync m16n8k16 with f32 accumulation (q split into f16 hi + lo so that the scores keep f32-level
-// accuracy, P rounded to f16), and the softmax is online, base 2, in registers. Every kv row is read once per
-// 64 q rows instead of once per q row.
+// Here K and V are first rounded to f16 once, by a streaming pass into stream scratch (every kv row is converted once,
+// not once per q tile and q head). Then one CTA owns 64 q rows of one (sequence, q head) and walks the kv rows it may
+// see in 64-row tiles, flash attention style: the f16 tiles arrive by cp.async into double-buffered, XOR-swizzled
+// shared memory while the previous tile is being used, S = Q K^T and O += P V run on mma.sync m16n8k16 with f32
+// accumulation (q split into f16 hi + lo so that the scores keep f32-level accuracy, P rounded to f16), and the
+// softmax is online, base 2, in registers. Every kv row is read once per 64 q rows instead of once per q row.
 #include "attention_mma.cuh"
 #include "common.cuh"
 
@@ -18,9 +19,22 @@ using namespace attn_mma;
 
 constexpr int PF_TILE = 64;  // q rows per CTA and kv rows per tile
 
+// K, V f32 [n8 * 8] -> f16, 8 values per thread and array.
+__global__ void __launch_bounds__(256) prefill_pack_kv_kernel(const float* __restrict__ K, const float* __restrict__ V,
+                                                              __half* __restrict__ Kh, __half* __restrict__ Vh, size_t n8) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += (size_t)gridDim.x * blockDim.x) {
+        const float4 k0 = *reinterpret_cast<const float4*>(K + 8 * i), k1 = *reinterpret_cast<const float4*>(K + 8 * i + 4);
+        const float4 v0 = *reinterpret_cast<const float4*>(V + 8 * i), v1 = *reinterpret_cast<const float4*>(V + 8 * i + 4);
+        *reinterpret_cast<uint4*>(Kh + 8 * i) =
+            make_uint4(pack_h2(k0.x, k0.y), pack_h2(k0.z, k0.w), pack_h2(k1.x, k1.y), pack_h2(k1.z, k1.w));
+        *reinterpret_cast<uint4*>(Vh + 8 * i) =
+            make_uint4(pack_h2(v0.x, v0.y), pack_h2(v0.z, v0.w), pack_h2(v1.x, v1.y), pack_h2(v1.z, v1.w));
+    }
+}
+
 template <int HD>
-__global__ void __launch_bounds__(128, 2) prefill_varlen_kernel(const float* __restrict__ Q, const float* __restrict__ K,
-                                                                const float* __restrict__ V,
+__global__ void __launch_bounds__(128, 2) prefill_varlen_kernel(const float* __restrict__ Q, const __half* __restrict__ K,
+                                                                const __half* __restrict__ V,
                                                                 const uint32_t* __restrict__ q_offsets,
                                                                 const uint32_t* __restrict__ kv_offsets,
                                                                 const uint32_t* __restrict__ q_lens,
@@ -29,9 +43,10 @@ __global__ void __launch_bounds__(128, 2) prefill_varlen_kernel(const float* __r
     constexpr int KS = HD / 16;      // k-steps of Q K^T
     constexpr int NT = HD / 8;       // n8 tiles of the output
     constexpr int CHUNKS = HD / 8;   // 16-byte f16 pieces per row
-    __shared__ __align__(128) __half sK[PF_TILE * HD];
-    __shared__ __align__(128) __half sV[PF_TILE * HD];
-    const uint32_t b = blockIdx.z, qh = blockIdx.y, r0 = blockIdx.x * PF_TILE;
+    extern __shared__ __align__(128) __half pf_smem[];  // [2 buffers][K tile | V tile]
+    constexpr uint32_t TILE_ELEMS = PF_TILE * HD;
+    // the last q tiles of a sequence see the most kv rows: they are scheduled first (block index reversed)
+    const uint32_t b = blockIdx.z, qh = blockIdx.y, r0 = (gridDim.x - 1u - blockIdx.x) * PF_TILE;
     const uint32_t q_len = q_lens[b], kv_len = kv_lens[b];
     if (r0 >= q_len || q_len == 0 || kv_len == 0 || q_len > kv_len) return;
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
@@ -75,27 +90,32 @@ __global__ void __launch_bounds__(128, 2) prefill_varlen_kernel(const float* __r
     const uint32_t last_q = min(r0 + PF_TILE, q_len) - 1u;
     const uint32_t kv_end = shift + last_q + 1u;
     const uint32_t n_tiles = (kv_end + PF_TILE - 1) / PF_TILE;
-    for (uint32_t tile = 0; tile < n_tiles; ++tile) {
+    // K and V rows of a tile: f16 global -> shared by cp.async (rows past the end repeat the last visible row: they are
+    // masked below, and their bytes are finite)
+    auto load_tile = [&](uint32_t tile, uint32_t buf) {
         const uint32_t base = tile * PF_TILE;
-        __syncthreads();  // the previous tile has been consumed
-        // ---- K and V rows of this tile: f32 global -> f16 shared (rows past the end hold zeros)
+        __half* dK = pf_smem + (size_t)buf * 2 * TILE_ELEMS;
+        __half* dV = dK + TILE_ELEMS;
 #pragma unroll
         for (int c = 0; c < (PF_TILE * CHUNKS) / 128; ++c) {
             const uint32_t idx = c * 128 + tid;
             const uint32_t r = idx / CHUNKS, ch = idx % CHUNKS;
             const uint32_t dst = r * HD + ((ch ^ (r & 7u)) * 8);
-            uint4 kq = make_uint4(0u, 0u, 0u, 0u), vq = kq;
-            if (base + r < kv_end) {
-                const size_t src = ((kv_row0 + base + r) * kv_heads + kvh) * HD + ch * 8;
-                const float4 k0 = *reinterpret_cast<const float4*>(K + src), k1 = *reinterpret_cast<const float4*>(K + src + 4);
-                const float4 v0 = *reinterpret_cast<const float4*>(V + src), v1 = *reinterpret_cast<const float4*>(V + src + 4);
-                kq = make_uint4(pack_h2(k0.x, k0.y), pack_h2(k0.z, k0.w), pack_h2(k1.x, k1.y), pack_h2(k1.z, k1.w));
-                vq = make_uint4(pack_h2(v0.x, v0.y), pack_h2(v0.z, v0.w), pack_h2(v1.x, v1.y), pack_h2(v1.z, v1.w));
-            }
-            *reinterpret_cast<uint4*>(sK + dst) = kq;
-            *reinterpret_cast<uint4*>(sV + dst) = vq;
+            const uint32_t row = min(base + r, kv_end - 1u);
+            const size_t src = ((kv_row0 + row) * kv_heads + kvh) * HD + ch * 8;
+            cp_async16(dK + dst, K + src);
+            cp_async16(dV + dst, V + src);
         }
-        __syncthreads();
+        cp_async_commit();
+    };
+    load_tile(0, 0);
+    for (uint32_t tile = 0; tile < n_tiles; ++tile) {
+        const uint32_t base = tile * PF_TILE;
+        cp_async_wait<0>();
+        __syncthreads();  // this tile has landed for every thread, and the other buffer's tile has been consumed
+        if (tile + 1 < n_tiles) load_tile(tile + 1, (tile + 1) & 1u);
+        const __half* sK = pf_smem + (size_t)(tile & 1u) * 2 * TILE_ELEMS;
+        const __half* sV = sK + TILE_ELEMS;
         // a warp whose 16 rows all sit before this tile's first kv row has nothing to add (causal)
         if (shift + min(r0 + warp * 16u + 15u, q_len - 1u) < base) continue;
 
@@ -208,12 +228,14 @@ int m40llm_attention_prefill_f32_gqa_varlen_async(M40llmCudaContext* ctx, const 
     cudaStream_t s = ctx->prefill_stream;
     // The grid needs the longest q run, and the reference validates every pair of lengths on the host
     // (kernels.cu:4861-4886): the lengths are read back behind whatever the prefill stream still holds.
-    uint32_t* lens = (uint32_t*)malloc((size_t)batch_size * 2 * sizeof(uint32_t));
+    uint32_t* lens = (uint32_t*)malloc((size_t)batch_size * 3 * sizeof(uint32_t));
     if (!lens) return -7;
     int rc = 0;
     uint32_t max_q = 0;
+    uint64_t total_kv = 0;  // rows of K / V the sequences reach: the extent of the f16 copies
     if (cudaMemcpyAsync(lens, d_q_lens, (size_t)batch_size * 4, cudaMemcpyDeviceToHost, s) != cudaSuccess ||
         cudaMemcpyAsync(lens + batch_size, d_kv_lens, (size_t)batch_size * 4, cudaMemcpyDeviceToHost, s) != cudaSuccess ||
+        cudaMemcpyAsync(lens + 2 * batch_size, d_kv_offsets, (size_t)batch_size * 4, cudaMemcpyDeviceToHost, s) != cudaSuccess ||
         cudaStreamSynchronize(s) != cudaSuccess) {
         cudaGetLastError();
         rc = -7;
@@ -222,19 +244,39 @@ int m40llm_attention_prefill_f32_gqa_varlen_async(M40llmCudaContext* ctx, const 
         const uint32_t ql = lens[i], kl = lens[batch_size + i];
         if (ql == 0 || kl == 0 || ql > kl || kl > 8192) rc = -8;
         if (ql > max_q) max_q = ql;
+        const uint64_t end = (uint64_t)lens[2 * batch_size + i] + kl;
+        if (end > total_kv) total_kv = end;
     }
     free(lens);
     if (rc != 0) return rc;
+    // f16 copies of K and V in the prefill stream's scratch
+    const size_t kv_elems = (size_t)total_kv * kv_heads * head_dim;
+    __half* kh = (__half*)m40_ensure_scratch(ctx, 0, 2 * kv_elems * sizeof(__half));
+    if (!kh) return -7;
+    __half* vh = kh + kv_elems;
+    {
+        const size_t n8 = kv_elems / 8;
+        const unsigned blocks = (unsigned)((n8 + 255) / 256 < (size_t)ctx->sm_count * 8 ? (n8 + 255) / 256 : (size_t)ctx->sm_count * 8);
+        prefill_pack_kv_kernel<<<blocks ? blocks : 1u, 256, 0, s>>>((const float*)d_k_f32, (const float*)d_v_f32, kh, vh, n8);
+        M40_COUNT_LAUNCH(ctx);
+    }
     dim3 grid((max_q + PF_TILE - 1) / PF_TILE, q_heads, batch_size);
     const float inv_sqrt = attn_inv_sqrt(head_dim);
+    const size_t smem = (size_t)2 * 2 * PF_TILE * head_dim * sizeof(__half);
+    static unsigned long long configured = 0ull;
+    const unsigned long long bit = 1ull << (ctx->device_id & 63);
+    if (!(configured & bit)) {
+        if (cudaFuncSetAttribute(prefill_varlen_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)(2 * 2 * PF_TILE * 128 * sizeof(__half))) != cudaSuccess)
+            return -4;
+        configured |= bit;
+    }
     if (head_dim == 128)
-        prefill_varlen_kernel<128><<<grid, 128, 0, s>>>((const float*)d_q_f32, (const float*)d_k_f32, (const float*)d_v_f32,
-                                                        d_q_offsets, d_kv_offsets, d_q_lens, d_kv_lens, q_heads, kv_heads,
-                                                        inv_sqrt, (float*)d_out_f32);
+        prefill_varlen_kernel<128><<<grid, 128, smem, s>>>((const float*)d_q_f32, kh, vh, d_q_offsets, d_kv_offsets, d_q_lens,
+                                                           d_kv_lens, q_heads, kv_heads, inv_sqrt, (float*)d_out_f32);
     else
-        prefill_varlen_kernel<64><<<grid, 128, 0, s>>>((const float*)d_q_f32, (const float*)d_k_f32, (const float*)d_v_f32,
-                                                       d_q_offsets, d_kv_offsets, d_q_lens, d_kv_lens, q_heads, kv_heads,
-                                                       inv_sqrt, (float*)d_out_f32);
+        prefill_varlen_kernel<64><<<grid, 128, smem, s>>>((const float*)d_q_f32, kh, vh, d_q_offsets, d_kv_offsets, d_q_lens,
+                                                          d_kv_lens, q_heads, kv_heads, inv_sqrt, (float*)d_out_f32);
     M40_COUNT_LAUNCH(ctx);
     return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
