@@ -283,17 +283,20 @@ void m40_attn_pick_chunk(const M40llmCudaContext* ctx, uint32_t rows, uint32_t k
     // faster per layer step with 256-token chunks than with 128-token ones, whose second wave is mostly ramp).
     // Chunks are fixed-size so that variable-length batches produce CTAs of equal cost (CTAs past a row's length
     // exit at once); never shorter than 128 tokens.
-    static int min_chunk_env = -1;
+    static int min_chunk_env = -1, max_chunk_env = -1;
     if (min_chunk_env < 0) {
         const char* e = getenv("M40LLM_ATTN_MIN_CHUNK");
         min_chunk_env = e ? atoi(e) : 0;
         if (min_chunk_env < 64) min_chunk_env = 128;
+        const char* x = getenv("M40LLM_ATTN_MAX_CHUNK");
+        max_chunk_env = x ? atoi(x) : 0;
+        if (max_chunk_env < min_chunk_env) max_chunk_env = 1024;
     }
     const uint64_t work = (uint64_t)rows * kv_heads * max_tokens;
     const uint64_t target = (uint64_t)ctx->sm_count * 2u;
     uint64_t c = (work + target - 1) / target;
     if (c < (uint64_t)min_chunk_env) c = (uint64_t)min_chunk_env;
-    if (c > 1024) c = 1024;
+    if (c > (uint64_t)max_chunk_env) c = (uint64_t)max_chunk_env;
     c = (c + 63) & ~(uint64_t)63;
     uint32_t s = (uint32_t)((max_tokens + c - 1) / c);
     if (s > 128u) {
