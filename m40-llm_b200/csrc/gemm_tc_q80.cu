@@ -433,13 +433,16 @@ __device__ __forceinline__ void q80_tile_ctas(const Q80EpiArgs& e, uint32_t tile
 // 8 activation rows.
 __global__ void __launch_bounds__(256) gemm_tc_q80_epilogue_kernel(Q80EpiArgs e) {
     __shared__ uint32_t first[2], count[2], seg0[2];
-    pdl_wait();
-    pdl_trigger();
     const uint32_t p = blockIdx.z, t = blockIdx.x, tr = threadIdx.x & 127u;
     const uint32_t n = t * BLOCK_N + tr;
+    // which CTAs hold this tile follows from the launch arguments alone: worked out while the GEMM still runs
+    if (t * BLOCK_N < e.N[p]) {
+        if (threadIdx.x == 0) q80_tile_ctas(e, e.tile_begin[p] + t, &first[0], &count[0], &seg0[0]);
+        if (threadIdx.x == 32 && e.mode == 1) q80_tile_ctas(e, e.tile_begin[1] + t, &first[1], &count[1], &seg0[1]);
+    }
+    pdl_wait();
+    pdl_trigger();
     if (t * BLOCK_N >= e.N[p]) return;
-    if (threadIdx.x == 0) q80_tile_ctas(e, e.tile_begin[p] + t, &first[0], &count[0], &seg0[0]);
-    if (threadIdx.x == 32 && e.mode == 1) q80_tile_ctas(e, e.tile_begin[1] + t, &first[1], &count[1], &seg0[1]);
     __syncthreads();
     if (n >= e.N[p]) return;
     // A thread owns 4 activation rows. Every load of a round is unconditional (row and partial index clamped, the value
