@@ -466,7 +466,7 @@ def compressed_case(nat, ev, peak, calls=16, reps=20):
             "config": "16/2/128 heads, context 32768, ring 512, block 64, top 64"}
 
 
-def splitk_case(nat, pkg, O, rank, world, dist, peak, reps=200):
+def splitk_case(nat, pkg, O, rank, world, dist, peak, reps=200, graphs=False):
     """One long sequence, split-K over the ranks (BASELINE configs[3]): Qwen2.5-3B heads (16 / 2 / 128), context 32768
     in the FP16-K / q4-V cache, 512-token ring, 64-token blocks, top 64. Every rank loads ONLY its own block range of
     old K / q4 V (the last rank also the ring); per call: local block scores -> local top-k pairs -> NCCL all-gather
@@ -530,6 +530,27 @@ def splitk_case(nat, pkg, O, rank, world, dist, peak, reps=200):
     for _ in range(reps):
         attend()
     att_ms = ev.stop_ms() / reps
+    # the same chain (kernels + both all-gathers) captured once and replayed as one CUDA graph: no per-call host work
+    graph_ms = None
+    if world > 1 and graphs:
+        replay = gout = None
+        try:  # the capture itself runs nothing, so a rank that fails here does not leave the others in a collective
+            replay, gout, _ = sk.capture_compressed(nb, ctop)
+        except Exception as exc:  # capture of the collectives is not available on every torch / NCCL build
+            record["attention_graph_error"] = f"{type(exc).__name__}: {exc}"[:200]
+        okf = torch.tensor([1.0 if replay is not None else 0.0], device="cuda", dtype=torch.float64)
+        dist.all_reduce(okf, op=dist.ReduceOp.MIN)
+        if float(okf[0]) == 1.0:  # every rank holds a graph: replays are safe
+            for _ in range(5):
+                replay()
+            nat.sync(1)
+            record["attention_graph_equals_eager"] = bool(torch.equal(gout, out))
+            dist.barrier()
+            ev.start()
+            for _ in range(reps):
+                replay()
+            graph_ms = ev.stop_ms() / reps
+            nat.sync(1)
 
     # the whole layer around it: weights replicated; the step re-appends the last token (position cL - 1) on every
     # rank, so the block ranges stay those of the loaded data (the parity check above came first)
@@ -577,15 +598,47 @@ def splitk_case(nat, pkg, O, rank, world, dist, peak, reps=200):
         layer()
     layer_ms = ev.stop_ms() / reps
     nat.sync(1)
+    layer_graph_ms = None
+    if world > 1 and graphs:  # the whole layer step (prologue, split-K attention with its collectives, Wo + FFN) as one graph
+        lreplay = None
+        try:
+            lreplay, _ = skl.capture(layer)
+        except Exception as exc:
+            record["layer_graph_error"] = f"{type(exc).__name__}: {exc}"[:200]
+        okf = torch.tensor([1.0 if lreplay is not None else 0.0], device="cuda", dtype=torch.float64)
+        dist.all_reduce(okf, op=dist.ReduceOp.MIN)
+        if float(okf[0]) == 1.0:
+            for _ in range(5):
+                lreplay()
+            nat.sync(1)
+            dist.barrier()
+            ev.start()
+            for _ in range(reps):
+                lreplay()
+            lt = torch.tensor([ev.stop_ms() / reps], device="cuda", dtype=torch.float64)
+            dist.all_reduce(lt, op=dist.ReduceOp.MAX)
+            layer_graph_ms = float(lt[0])
+            nat.sync(1)
+            record["layer_graph_ms"] = layer_graph_ms
     st = np.zeros(1, np.uint32)
     assert L_.m40llm_context_take_device_status(ctx, st.ctypes.data) == 0 and st[0] == 0, int(st[0])
     if dist is not None:
+        gflag = torch.tensor([0.0 if graph_ms is None else 1.0], device="cuda", dtype=torch.float64)
+        dist.all_reduce(gflag, op=dist.ReduceOp.MIN)
+        if float(gflag[0]) == 0.0:
+            graph_ms = None
+        else:
+            gt = torch.tensor([graph_ms], device="cuda", dtype=torch.float64)
+            dist.all_reduce(gt, op=dist.ReduceOp.MAX)
+            graph_ms = float(gt[0])
         t = torch.tensor([att_ms, layer_ms], device="cuda", dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         att_ms, layer_ms = float(t[0]), float(t[1])
     # per rank: its share of the old K (scoring), the selected q4 V + scales, the ring on the last rank
     cbytes = old_len * kvh * hd * 2 + qh * ctop * cbs * (hd // 2 + 4) + 2 * cR * kvh * hd * 2
     wbytes = sum(b.nbytes for b in W.values())
+    if graph_ms is not None:
+        record["attention_graph_ms"] = graph_ms
     record.update({"attention_ms": att_ms, "attention_calls_per_s": 1e3 / att_ms, "attention_algorithmic_bytes": cbytes,
                    "attention_frac_of_hbm_peak": cbytes / (att_ms * 1e-3) / 1e9 / (peak * world),
                    "layer_ms": layer_ms, "layer_tokens_per_s": 1e3 / layer_ms,
@@ -740,7 +793,8 @@ def main():
 
     if args.workload == "splitk":
         os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
-        rec = splitk_case(nat, pkg, O, rank, world, dist, peak)
+        # this workload also replays the chain as CUDA graphs (kernels + NCCL all-gathers captured together)
+        rec = splitk_case(nat, pkg, O, rank, world, dist, peak, graphs=True)
         if rank == 0:
             print(json.dumps({"metric": "splitk_attention_calls_per_s", "value": rec["attention_calls_per_s"], "unit": "calls/s",
                               "n_gpus": world, "higher_is_better": True, "scaling": "strong", "dtype": "f32",
