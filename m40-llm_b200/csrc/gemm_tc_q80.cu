@@ -41,16 +41,20 @@ using namespace tc;
 constexpr uint32_t UNIT_K = 256;                       // k per raw stage (8 Q8_0 blocks)
 constexpr uint32_t RAW_ROW_BYTES = UNIT_K / 32 * 34;   // 272
 constexpr uint32_t RAW_BYTES = BLOCK_N * RAW_ROW_BYTES; // 34816
-constexpr uint32_t RS = 4, TB = 2;                     // ring depths: raw stages, TMEM accumulators
+constexpr uint32_t RS = 4;                             // raw stages
 constexpr uint32_t A_COLS = BLOCK_K;                   // TMEM columns of one converted sub-block: 32 hi + 32 lo
 constexpr uint32_t TMEM_COLS = 512;
-// Two issuing threads (see above) up to 32 rows; at 64 rows the accumulators leave no room for a third column group.
-__host__ __device__ constexpr bool dual_issue(int m_pad) { return m_pad <= 32; }
+// Two issuing threads (see above), the lo.Xh products in a column group of their own. Up to 32 rows two accumulator
+// sets alternate between tile segments; at 64 rows the three column groups leave room for one set only (the issue
+// then waits at a segment boundary until the workers have read it, ~1 us per call), which still beats one thread
+// issuing all eight instructions of a sub-block.
+__host__ __device__ constexpr bool dual_issue(int m_pad) { return m_pad <= 64; }
+__host__ __device__ constexpr uint32_t acc_sets(int m_pad) { return m_pad <= 32 ? 2u : 1u; }
 __host__ __device__ constexpr uint32_t n_issuers(int m_pad) { return dual_issue(m_pad) ? 2u : 1u; }
 // dual: [hi.Xh | hi.Xl | lo.Xh]; single: [hi.Xh + lo.Xh | hi.Xl]
 __host__ __device__ constexpr uint32_t acc_cols(int m_pad) { return (dual_issue(m_pad) ? 3u : 2u) * (uint32_t)m_pad; }
-__host__ __device__ constexpr uint32_t a_stages(int m_pad) { return (TMEM_COLS - TB * acc_cols(m_pad)) / A_COLS; }  // 6, 5, 4
-// First TMEM column of accumulator buffer tb (TB == 2). Every accumulator starts at a multiple of its own width:
+__host__ __device__ constexpr uint32_t a_stages(int m_pad) { return (TMEM_COLS - acc_sets(m_pad) * acc_cols(m_pad)) / A_COLS; }  // 6, 5, 5
+// First TMEM column of accumulator set tb. Every accumulator starts at a multiple of its own width:
 // dual issue lays the two buffers out as [hi 0 | lo 0 | lo 1 | hi 1] with hi 2 m_pad and lo m_pad columns wide.
 __host__ __device__ constexpr uint32_t acc_hi_col(int m_pad, uint32_t tb) {
     return dual_issue(m_pad) ? (tb ? 4u * (uint32_t)m_pad : 0u) : tb * acc_cols(m_pad);
@@ -95,7 +99,7 @@ template <int M_PAD, int C4>
 __device__ __forceinline__ void q80_worker(const Q80Args& a, const Q80Smem& sm, uint32_t tmem_base, uint32_t u0,
                                            uint32_t u1, uint32_t lane_group, uint32_t lane) {
     constexpr int COLS = M_PAD / 4;
-    constexpr uint32_t AST = a_stages(M_PAD), BS = b_slots(M_PAD);
+    constexpr uint32_t AST = a_stages(M_PAD), BS = b_slots(M_PAD), TB = acc_sets(M_PAD);
     constexpr uint32_t A_COL0 = TB * acc_cols(M_PAD);
     const uint32_t r = lane_group * 32 + lane;  // weight row of the tile == TMEM lane
     const uint32_t tmem_lane = tmem_base + ((lane_group * 32u) << 16);
@@ -181,7 +185,8 @@ __device__ __forceinline__ void q80_worker(const Q80Args& a, const Q80Smem& sm, 
         else { tmem_ld_x16(taddr, x); tmem_ld_x16(taddr + M_PAD, y); }
         if (dual_issue(M_PAD)) {  // the lo.Xh products have their own column group
             if (COLS == 4) tmem_ld_x4(tlane + acc_lo_col(M_PAD, tb), z);
-            else tmem_ld_x8(tlane + acc_lo_col(M_PAD, tb), z);
+            else if (COLS == 8) tmem_ld_x8(tlane + acc_lo_col(M_PAD, tb), z);
+            else tmem_ld_x16(tlane + acc_lo_col(M_PAD, tb), z);
         }
         tmem_ld_wait();
         tc_fence_before();
@@ -208,7 +213,7 @@ template <int M_PAD, int ROLE>
 __device__ __forceinline__ void q80_issuer(const Q80Args& a, const Q80Smem& sm, uint32_t tmem_base, uint32_t b_smem0,
                                         uint32_t u0, uint32_t u1) {
     constexpr uint32_t B_BYTES = M_PAD * BLOCK_K * 2;
-    constexpr uint32_t BS = b_slots(M_PAD), AST = a_stages(M_PAD);
+    constexpr uint32_t BS = b_slots(M_PAD), AST = a_stages(M_PAD), TB = acc_sets(M_PAD);
     constexpr uint32_t A_COL0 = TB * acc_cols(M_PAD);
     const uint32_t idesc2 = make_idesc(2 * M_PAD), idesc1 = make_idesc(M_PAD);
     bool ok = true;
@@ -281,7 +286,7 @@ __global__ void __launch_bounds__(CTA_THREADS, 1) gemm_tc_q80_kernel(const __gri
                                                                      const __grid_constant__ CUtensorMap tmXl,
                                                                      Q80Args a) {
     constexpr uint32_t B_BYTES = M_PAD * BLOCK_K * 2;  // one of hi / lo for a 64-k sub-block
-    constexpr uint32_t BS = b_slots(M_PAD);
+    constexpr uint32_t BS = b_slots(M_PAD), TB = acc_sets(M_PAD);
     constexpr uint32_t AST = a_stages(M_PAD);
     constexpr uint32_t A_COL0 = TB * acc_cols(M_PAD);
     extern __shared__ unsigned char smem_unaligned[];
